@@ -1,0 +1,56 @@
+"""The step function, the cache manager and the batch builder on the CPU, with the
+kernels replaced by their plain twins (tests/cpu_ops.py): every way of cutting the
+same requests into steps gives the logits of the plain whole-sequence implementation."""
+import pytest
+import torch
+
+from cpu_ops import CpuOps
+from helpers import (tiny_config, make_model_dir, make_requests, PAGE_SIZE, PROMPT_LENS,
+                     trace_whole, trace_tail_decode, trace_portions, trace_mixed, run_trace, max_rel_err)
+from plain_qwen3 import PlainModel
+from tffinfer_b200.config import EngineConfig
+from tffinfer_b200.engine import ModelRunner
+
+TOL = 2e-5   # float32 activations against a float64 oracle
+
+
+def _runner(model_dir, name, pool_tokens):
+    ecfg = EngineConfig(dtype="float32", page_size=PAGE_SIZE[name], max_cache_tokens=pool_tokens,
+                        max_live_requests=4, device="cpu")
+    return ModelRunner(model_dir, ecfg, ops=CpuOps())
+
+
+@pytest.fixture(scope="module")
+def plain_logits(tmp_path_factory):
+    out = {}
+    tmp = tmp_path_factory.mktemp("models")
+    for name in ("A", "B", "C"):
+        d = make_model_dir(tmp, name)
+        reqs = make_requests(name)
+        pm = PlainModel(d)
+        out[name] = (d, reqs, {r: pm.logits(t) for r, t in reqs.items()})
+    return out
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
+def test_cut_modes_match_plain(plain_logits, name, mode):
+    d, reqs, want = plain_logits[name]
+    ps = PAGE_SIZE[name]
+    longest = max(-(-len(t) // ps) * ps for t in reqs.values())
+    if mode == "mixed":
+        pool = longest + longest // 2
+        steps = trace_mixed(reqs, PROMPT_LENS[name], max_live=4, page_size=ps, pool_tokens=pool,
+                            chunk=5 if name == "A" else 7)
+    else:
+        pool = longest
+        steps = {"whole": trace_whole, "tail": trace_tail_decode, "portions": trace_portions}[mode](reqs)
+    runner = _runner(d, name, pool)
+    got = run_trace(runner, reqs, steps)
+    for r in reqs:
+        err = max_rel_err(got[r], want[r])
+        assert err < TOL, f"{name}/{mode}/{r}: rel err {err:.3e}"
+    assert all(p.num_free == p.num_pages for p in runner.cache.pools)
+    assert runner.cache.slots.num_free == 4
+    if mode == "mixed":
+        assert any(p.high_water == p.num_pages or p.high_water > p.num_pages // 2 for p in runner.cache.pools)

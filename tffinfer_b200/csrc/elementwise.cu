@@ -1,0 +1,210 @@
+// Memory-bound kernels of the step: embedding gather, RMSNorm, SwiGLU, the rotary
+// table, and the fused per-head q/k RMSNorm + RoPE + paged K/V write.
+// Every reduction and every rotation is done in float32 whatever the storage type.
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding
+// x[t, :] = float(E[token[t], :]).  Stands where the reference gathers (and
+// de-quantises) embedding rows on the CPU: src/kernel/cpu/embedding.cpp:35-49.
+template <typename TW>
+__global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
+                             float* __restrict__ out, int hidden, int vocab) {
+    const int t = blockIdx.x;
+    const int tok = tokens[t];
+    float* o = out + (size_t)t * hidden;
+    if (tok < 0 || tok >= vocab) {             // never a wrong row: poison instead
+        for (int h = threadIdx.x; h < hidden; h += blockDim.x) o[h] = __int_as_float(0x7fc00000);
+        return;
+    }
+    const TW* row = table + (size_t)tok * hidden;
+    for (int h = threadIdx.x; h < hidden; h += blockDim.x) o[h] = to_f32<TW>(row[h]);
+}
+
+TFF_API int tff_embed(const int* tokens, const void* table, int table_is_bf16, float* out,
+                      int num_tokens, int hidden, int vocab, cudaStream_t stream) {
+    if (num_tokens <= 0) return TFF_OK;
+    if (hidden <= 0 || vocab <= 0) return TFF_ERR_BAD_ARGUMENT;
+    const int nt = hidden >= 1024 ? 256 : 128;
+    if (table_is_bf16) embed_kernel<bf16><<<num_tokens, nt, 0, stream>>>(tokens, (const bf16*)table, out, hidden, vocab);
+    else embed_kernel<float><<<num_tokens, nt, 0, stream>>>(tokens, (const float*)table, out, hidden, vocab);
+    return tff_launch_status();
+}
+
+// ------------------------------------------------------------------ RMSNorm
+// out[r, :] = (x[row, :] * rsqrt(mean(x[row]^2) + eps)) * w, row = row_index ? row_index[r] : r.
+// Formula and multiplication order of src/kernel/cuda/norm.cu:31-48.
+template <typename TO, int NT>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                               const int* __restrict__ row_index, TO* __restrict__ out,
+                               int dim, float eps) {
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const int row = row_index ? row_index[r] : r;
+    const float* xr = x + (size_t)row * dim;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < dim; i += NT) { const float v = xr[i]; ss = fmaf(v, v, ss); }
+    ss = block_sum<NT>(ss, red);
+    const float rs = rsqrtf(ss / (float)dim + eps);
+    TO* o = out + (size_t)r * dim;
+    for (int i = threadIdx.x; i < dim; i += NT) o[i] = from_f32<TO>((xr[i] * rs) * w[i]);
+}
+
+TFF_API int tff_rmsnorm(const float* x, const float* w, const int* row_index, void* out, int out_is_bf16,
+                        int rows, int dim, float eps, cudaStream_t stream) {
+    if (rows <= 0) return TFF_OK;
+    if (dim <= 0) return TFF_ERR_BAD_ARGUMENT;
+    if (dim >= 1024) {
+        if (out_is_bf16) rmsnorm_kernel<bf16, 256><<<rows, 256, 0, stream>>>(x, w, row_index, (bf16*)out, dim, eps);
+        else rmsnorm_kernel<float, 256><<<rows, 256, 0, stream>>>(x, w, row_index, (float*)out, dim, eps);
+    } else {
+        if (out_is_bf16) rmsnorm_kernel<bf16, 64><<<rows, 64, 0, stream>>>(x, w, row_index, (bf16*)out, dim, eps);
+        else rmsnorm_kernel<float, 64><<<rows, 64, 0, stream>>>(x, w, row_index, (float*)out, dim, eps);
+    }
+    return tff_launch_status();
+}
+
+// ------------------------------------------------------------------- SwiGLU
+// out[t, i] = silu(gu[t, i]) * gu[t, I + i], silu(g) = g / (1 + exp(-g))
+// (src/kernel/cuda/unary.cu:10-27: x1 = gate, x2 = up).
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total, int inter) {
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const long long t = idx / inter;
+        const int i = (int)(idx - t * inter);
+        const float g = to_f32<T>(gu[t * 2 * inter + i]);
+        const float u = to_f32<T>(gu[t * 2 * inter + inter + i]);
+        out[idx] = from_f32<T>((g / (1.0f + expf(-g))) * u);
+    }
+}
+
+TFF_API int tff_swiglu(const void* gu, void* out, int is_bf16, int rows, int inter, cudaStream_t stream) {
+    if (rows <= 0) return TFF_OK;
+    if (inter <= 0) return TFF_ERR_BAD_ARGUMENT;
+    const long long total = (long long)rows * inter;
+    const int nt = 256;
+    const int blocks = (int)((total + nt - 1) / nt < 148 * 16 ? (total + nt - 1) / nt : 148 * 16);
+    if (is_bf16) swiglu_kernel<bf16><<<blocks, nt, 0, stream>>>((const bf16*)gu, (bf16*)out, total, inter);
+    else swiglu_kernel<float><<<blocks, nt, 0, stream>>>((const float*)gu, (float*)out, total, inter);
+    return tff_launch_status();
+}
+
+// ------------------------------------------------------------- rotary table
+// table[p][i] = (cos, sin)(float(p) * inv_freq[i]), i < rot_dim/2; the angle is one
+// float32 product.  Same table as src/kernel/cuda/rope_table.cu:10-40, whose
+// frequencies are exp(-(2i/d) * ln(base)); here they arrive as an array.
+__global__ void rope_table_kernel(float2* __restrict__ table, const float* __restrict__ inv_freq,
+                                  int max_pos, int half) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)max_pos * half) return;
+    const int p = (int)(idx / half), i = (int)(idx % half);
+    const float angle = (float)p * inv_freq[i];
+    float s, c;
+    sincosf(angle, &s, &c);
+    table[idx] = make_float2(c, s);
+}
+
+TFF_API int tff_rope_table(float* table, const float* inv_freq, int max_pos, int rot_dim, cudaStream_t stream) {
+    if (max_pos <= 0 || rot_dim <= 0 || (rot_dim & 1)) return TFF_ERR_BAD_ARGUMENT;
+    const int half = rot_dim / 2;
+    const long long total = (long long)max_pos * half;
+    rope_table_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>((float2*)table, inv_freq, max_pos, half);
+    return tff_launch_status();
+}
+
+// ------------------------------- q/k RMSNorm + RoPE + paged K/V write (fused)
+// One warp per (token, head of [q heads | k heads | v heads]) of the row
+// qkv[t] = [q (nq*d) | k (nkv*d) | v (nkv*d)].
+//   q head: normalise over d with q_w (if given), rotate, write back in place;
+//   k head: normalise with k_w (if given), rotate, write to the K page of the token;
+//   v head: copy to the V page.
+// Per-head norm before RoPE: src/core/model/qwen3/QWen3Creator.cpp:93-101; rotate-half
+// pairing (i, i + rot/2): src/kernel/cuda/paged_flash_attention.cu:300-384; cache write:
+// src/kernel/cuda/set_row.cu:72-123.  Unlike the reference, keys are stored rotated.
+template <typename T>
+__global__ void qk_norm_rope_kv_write_kernel(
+    T* __restrict__ qkv, const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+    const float2* __restrict__ table, int rot_dim,
+    const int* __restrict__ positions, const int* __restrict__ tok_req,
+    const int* __restrict__ block_table, int table_width,
+    T* __restrict__ cache, KvLayout L, int layer, int write_cache,
+    int nq, int nkv, int d, int max_pos) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.y;
+    const int head = blockIdx.x * (blockDim.x >> 5) + warp;
+    const int heads = nq + 2 * nkv;
+    if (head >= heads) return;
+    const bool is_q = head < nq, is_k = !is_q && head < nq + nkv;
+    if (!is_q && !write_cache) return;
+    T* src = qkv + (size_t)t * heads * d + (size_t)head * d;
+    const int pos = positions[t];
+
+    T* dst;
+    if (is_q) {
+        dst = src;
+    } else {
+        const int kvh = is_k ? head - nq : head - nq - nkv;
+        const int b = tok_req[t];
+        const int page = block_table[(size_t)b * table_width + pos / L.page_size];
+        if (page < 0) return;                 // no page: the host never schedules this; write nothing
+        dst = cache + (size_t)page * L.page_stride + (size_t)layer * L.layer_stride +
+              (is_k ? 0 : L.kv_stride) + (size_t)kvh * L.head_stride + (size_t)(pos % L.page_size) * d;
+    }
+    if (!is_q && !is_k) {                     // V: plain copy
+        for (int i = lane; i < d; i += 32) dst[i] = src[i];
+        return;
+    }
+    const float* w = is_q ? q_w : k_w;
+    float rs = 1.f;
+    if (w) {
+        float ss = 0.f;
+        for (int i = lane; i < d; i += 32) { const float v = to_f32<T>(src[i]); ss = fmaf(v, v, ss); }
+        ss = warp_sum(ss);
+        rs = rsqrtf(ss / (float)d + eps);
+    }
+    const int half = rot_dim >> 1;
+    const bool rotate = table != nullptr && half > 0 && pos >= 0 && pos < max_pos;
+    // pairs (i, i + half), i < half; then the unrotated tail [rot_dim, d)
+    for (int i = lane; i < half; i += 32) {
+        float a = to_f32<T>(src[i]), b2 = to_f32<T>(src[i + half]);
+        if (w) { a = (a * rs) * w[i]; b2 = (b2 * rs) * w[i + half]; }
+        float ra = a, rb = b2;
+        if (rotate) {
+            const float2 cs = table[(size_t)pos * half + i];
+            ra = a * cs.x - b2 * cs.y;
+            rb = a * cs.y + b2 * cs.x;
+        }
+        // both reads of the pair happen before either write (in-place for q)
+        dst[i] = from_f32<T>(ra);
+        dst[i + half] = from_f32<T>(rb);
+    }
+    for (int i = 2 * half + lane; i < d; i += 32) {
+        float a = to_f32<T>(src[i]);
+        if (w) a = (a * rs) * w[i];
+        dst[i] = from_f32<T>(a);
+    }
+}
+
+TFF_API int tff_qk_norm_rope_kv_write(
+    void* qkv, int is_bf16, const float* q_w, const float* k_w, float eps,
+    const float* table, int rot_dim, int max_pos,
+    const int* positions, const int* tok_req, const int* block_table, int table_width,
+    void* cache, int cache_layers, int layer, int page_size, int write_cache,
+    int num_tokens, int nq, int nkv, int d, cudaStream_t stream) {
+    if (num_tokens <= 0) return TFF_OK;
+    if (nq <= 0 || nkv <= 0 || d <= 0 || rot_dim < 0 || rot_dim > d || (rot_dim & 1)) return TFF_ERR_BAD_ARGUMENT;
+    if (write_cache && (cache == nullptr || block_table == nullptr || page_size <= 0)) return TFF_ERR_BAD_ARGUMENT;
+    const KvLayout L = make_kv_layout(cache_layers, nkv, page_size > 0 ? page_size : 1, d);
+    const int heads = nq + 2 * nkv;
+    const int warps = 4;
+    dim3 grid((heads + warps - 1) / warps, num_tokens);
+    if (is_bf16)
+        qk_norm_rope_kv_write_kernel<bf16><<<grid, warps * 32, 0, stream>>>(
+            (bf16*)qkv, q_w, k_w, eps, (const float2*)table, rot_dim, positions, tok_req, block_table,
+            table_width, (bf16*)cache, L, layer, write_cache, nq, nkv, d, max_pos);
+    else
+        qk_norm_rope_kv_write_kernel<float><<<grid, warps * 32, 0, stream>>>(
+            (float*)qkv, q_w, k_w, eps, (const float2*)table, rot_dim, positions, tok_req, block_table,
+            table_width, (float*)cache, L, layer, write_cache, nq, nkv, d, max_pos);
+    return tff_launch_status();
+}

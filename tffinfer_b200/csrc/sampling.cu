@@ -1,0 +1,184 @@
+// Sampling over float32 logits [rows, vocab] on the device: one token id per row.
+//   greedy       first maximum (ties go to the lowest id), as std::max_element does in
+//                src/core/sampler/LLMSampler.cpp:43-45
+//   temperature  logits scaled by 1/T (LLMSampler.cpp:36-41), softmax in float32, then
+//                the inverse CDF at a uniform number u[row] in [0, 1) that the host
+//                derives from (seed, request, step), so a request's tokens do not
+//                depend on what else is in the batch.  Optional top-k / top-p / min-p
+//                filters (the fields of SamplingConfig, LLMSampler.h:55-63) are applied
+//                by a threshold on the scaled logit computed by a bisection.
+#include "common.cuh"
+
+namespace {
+
+constexpr int NT = 1024;
+
+__global__ void __launch_bounds__(NT)
+argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab) {
+    __shared__ float sval[32];
+    __shared__ int sidx[32];
+    const float* row = logits + (size_t)blockIdx.x * vocab;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += NT) {
+        const float v = row[i];
+        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+    if (bi == 0x7fffffff) bi = threadIdx.x < vocab ? threadIdx.x : 0;   // all NaN/-inf in this thread's share
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { sval[warp] = best; sidx[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        best = sval[lane]; bi = sidx[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        if (lane == 0) out[blockIdx.x] = bi;
+    }
+}
+
+// Each thread owns a contiguous share of the vocabulary so that the cumulative sum
+// runs in index order.
+__global__ void __launch_bounds__(NT)
+sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+              const float* __restrict__ uniform, const int* __restrict__ top_k,
+              const float* __restrict__ top_p, const float* __restrict__ min_p,
+              int* __restrict__ out, int vocab) {
+    __shared__ float red[32];
+    __shared__ float part[NT];
+    __shared__ int chosen;
+    __shared__ float sh_a, sh_b;
+    const int r = blockIdx.x;
+    const float* row = logits + (size_t)r * vocab;
+    const float T = temperature[r];
+    const int tid = threadIdx.x;
+    if (tid == 0) chosen = -1;
+
+    // maximum (also the greedy answer when T == 0)
+    float mx = -INFINITY;
+    for (int i = tid; i < vocab; i += NT) mx = fmaxf(mx, row[i]);
+    mx = block_max<NT>(mx, red);
+    if (!(T > 0.f)) {
+        int bi = 0x7fffffff;
+        for (int i = tid; i < vocab; i += NT) if (row[i] == mx && i < bi) bi = i;
+        __shared__ int smin;
+        if (tid == 0) smin = 0x7fffffff;
+        __syncthreads();
+        atomicMin(&smin, bi);
+        __syncthreads();
+        if (tid == 0) out[r] = smin == 0x7fffffff ? 0 : smin;
+        return;
+    }
+    const float invT = 1.f / T;
+    const int per = (vocab + NT - 1) / NT;
+    const int lo = tid * per, hi = min(vocab, lo + per);
+
+    // threshold on z = (x - max) / T below which tokens are dropped
+    float cut = -INFINITY;
+    const int k = top_k ? top_k[r] : 0;
+    const float tp = top_p ? top_p[r] : 1.f;
+    const float mp = min_p ? min_p[r] : 0.f;
+    if (mp > 0.f) cut = fmaxf(cut, logf(mp));             // p_i >= min_p * p_max  <=>  z_i >= ln(min_p)
+    if ((k > 0 && k < vocab) || tp < 1.f) {
+        // total mass for top-p
+        float tot = 0.f;
+        for (int i = lo; i < hi; ++i) tot += expf((row[i] - mx) * invT);
+        tot = block_sum<NT>(tot, red);
+        // bisection on the threshold: keep the largest threshold whose kept set still
+        // has >= k members (top-k) / mass >= top_p * total (top-p); 40 halvings of
+        // [zmin, 0] reach float resolution.
+        float a = -1e30f, bnd = 0.f;                       // invariant: kept(a) is enough, kept(bnd) may not be
+        float zmin = 0.f;
+        for (int i = lo; i < hi; ++i) zmin = fminf(zmin, (row[i] - mx) * invT);
+        zmin = -block_max<NT>(-zmin, red);
+        a = zmin;
+        for (int it = 0; it < 40; ++it) {
+            const float mid = 0.5f * (a + bnd);
+            float cnt = 0.f, mass = 0.f;
+            for (int i = lo; i < hi; ++i) {
+                const float z = (row[i] - mx) * invT;
+                if (z >= mid) { cnt += 1.f; mass += expf(z); }
+            }
+            cnt = block_sum<NT>(cnt, red);
+            mass = block_sum<NT>(mass, red);
+            bool enough = true;
+            if (k > 0 && k < vocab) enough = enough && cnt >= (float)k;
+            if (tp < 1.f) enough = enough && mass >= tp * tot;
+            // moving the threshold up keeps fewer tokens: do it only while each filter
+            // alone would still keep enough
+            if (tid == 0) { if (enough) sh_a = mid, sh_b = bnd; else sh_a = a, sh_b = mid; }
+            __syncthreads();
+            a = sh_a; bnd = sh_b;
+            __syncthreads();
+        }
+        cut = fmaxf(cut, a);
+    }
+
+    float s = 0.f;
+    for (int i = lo; i < hi; ++i) {
+        const float z = (row[i] - mx) * invT;
+        if (z >= cut) s += expf(z);
+    }
+    part[tid] = s;
+    __syncthreads();
+    // inclusive scan of the NT partial sums (Hillis-Steele; order fixed by NT)
+    for (int off = 1; off < NT; off <<= 1) {
+        const float v = tid >= off ? part[tid - off] : 0.f;
+        __syncthreads();
+        part[tid] += v;
+        __syncthreads();
+    }
+    const float total = part[NT - 1];
+    const float target = uniform[r] * total;
+    const float before = tid > 0 ? part[tid - 1] : 0.f;
+    if (lo < hi && before <= target && target < part[tid]) {
+        float c = before;
+        int pick = -1, last = -1;
+        for (int i = lo; i < hi; ++i) {
+            const float z = (row[i] - mx) * invT;
+            if (z < cut) continue;
+            last = i;
+            c += expf(z);
+            if (target < c) { pick = i; break; }
+        }
+        if (pick < 0) pick = last;
+        if (pick >= 0) chosen = pick;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int c = chosen;
+        if (c < 0) {                          // rounding left the target at the very end: take the maximum
+            c = 0;
+            for (int i = 0; i < vocab; ++i) if (row[i] == mx) { c = i; break; }
+        }
+        out[r] = c;
+    }
+}
+
+}  // namespace
+
+TFF_API int tff_argmax(const float* logits, int* out, int rows, int vocab, cudaStream_t stream) {
+    if (rows <= 0) return TFF_OK;
+    if (vocab <= 0) return TFF_ERR_BAD_ARGUMENT;
+    argmax_kernel<<<rows, NT, 0, stream>>>(logits, out, vocab);
+    return tff_launch_status();
+}
+
+// temperature[r] <= 0 selects greedy for that row.  top_k / top_p / min_p may be null.
+TFF_API int tff_sample(const float* logits, const float* temperature, const float* uniform,
+                       const int* top_k, const float* top_p, const float* min_p,
+                       int* out, int rows, int vocab, cudaStream_t stream) {
+    if (rows <= 0) return TFF_OK;
+    if (vocab <= 0 || temperature == nullptr || uniform == nullptr) return TFF_ERR_BAD_ARGUMENT;
+    sample_kernel<<<rows, NT, 0, stream>>>(logits, temperature, uniform, top_k, top_p, min_p, out, vocab);
+    return tff_launch_status();
+}

@@ -1,0 +1,197 @@
+"""The step function and what it owns: the model, its weights, the cache tensors and
+the cache manager.
+
+One call of :meth:`ModelRunner.step` runs exactly the tokens it is given -- portions
+of prompts beside single decoded tokens, cut anywhere -- as one batch, reading what
+earlier steps left in the cache, and returns float32 logits at the wanted places.
+It stands where the reference has ``prefill`` / ``decode``
+(src/core/runtime/InferRuntime.cu:294-381), which build and run a task graph for one
+sequence at a time and return logits of every row to the host.
+"""
+from __future__ import annotations
+
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache import CacheManager, GroupSpec
+from ..config import EngineConfig, read_config_json
+from ..parts import Model, CacheBinding, KVNeed, StateNeed
+from ..registry import get_architecture
+from ..weights import load_model_weights
+from .batch import StepEntry, StepBatch, build_step_batch
+
+_TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+_STATE_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": torch.int32}
+
+
+class OutOfPages(RuntimeError):
+    """A step needs more cache pages than are free.  Nothing was taken."""
+
+
+class RequestError(ValueError):
+    """A request the engine cannot run (unknown id, token out of range, too long)."""
+
+
+def _make_ops(device: str):
+    from ..kernels.library import CudaKernels
+    if not str(device).startswith("cuda"):
+        raise RuntimeError(f"tffinfer_b200 runs on CUDA devices only (sm_100a); got device '{device}'")
+    return CudaKernels()
+
+
+class ModelRunner:
+    def __init__(self, model_dir: Optional[str] = None, engine_config: Optional[EngineConfig] = None, *,
+                 config=None, tensors: Optional[Dict[str, torch.Tensor]] = None, ops=None):
+        """Either ``model_dir`` (config.json + safetensors) or ``config`` with ``tensors``
+        (name -> tensor, checked like a file).  ``ops`` overrides the kernel library."""
+        import tffinfer_b200.parts  # noqa: F401  registers the built-in parts
+        import tffinfer_b200.models  # noqa: F401  registers the architectures
+        self.ecfg = (engine_config or EngineConfig()).normalized()
+        self.device = torch.device(self.ecfg.device)
+        self.ops = ops if ops is not None else _make_ops(self.ecfg.device)
+        self.act_dtype = _TORCH_DTYPES[self.ecfg.dtype]
+        if model_dir is not None:
+            cj = read_config_json(model_dir)
+            archs = cj.get("architectures")
+            if not isinstance(archs, list) or not archs:
+                from ..config import ConfigError
+                raise ConfigError("config.json: 'architectures' must be a non-empty list of names")
+            arch = get_architecture(archs[0])
+            self.config = arch.read_config(cj)
+        else:
+            if config is None or tensors is None:
+                raise ValueError("give model_dir, or config together with tensors")
+            self.config = config
+            arch = get_architecture(config.architecture)
+        self.desc = arch.describe(self.config)
+        self.model = Model(self.desc)
+        expected = self.model.expected_tensors()
+        if model_dir is not None:
+            held = load_model_weights(model_dir, expected, self.act_dtype, self.device)
+        else:
+            from ..weights.loader import check_tensors
+            held = check_tensors(tensors, expected, self.act_dtype, self.device)
+        self.model.load(held, self.ops, self.act_dtype, self.device)
+        del held
+        self.max_model_len = min(self.ecfg.max_model_len or self.desc.max_position, self.desc.max_position)
+        self._build_cache()
+
+    # ------------------------------------------------------------------ cache
+    def _build_cache(self) -> None:
+        needs = self.model.cache_needs()
+        groups: List[GroupSpec] = []
+        members: List[List[int]] = []
+        self.bindings: List[CacheBinding] = [CacheBinding() for _ in needs]
+        state_specs = []
+        for e, need in enumerate(needs):
+            if isinstance(need, KVNeed):
+                key = (need.num_kv_heads, need.head_dim, need.window)
+                for g, spec in enumerate(groups):
+                    if (spec.num_kv_heads, spec.head_dim, spec.window) == key:
+                        break
+                else:
+                    groups.append(GroupSpec(0, need.num_kv_heads, need.head_dim, need.window))
+                    members.append([])
+                    g = len(groups) - 1
+                self.bindings[e] = CacheBinding(group=g, layer_in_group=len(members[g]), write=True)
+                members[g].append(e)
+            elif isinstance(need, StateNeed):
+                self.bindings[e] = CacheBinding(state_index=len(state_specs))
+                state_specs.append(need)
+        for e, entry in enumerate(self.desc.schedule):
+            if entry.cache_of is not None:
+                src = self.bindings[entry.cache_of]
+                self.bindings[e] = CacheBinding(group=src.group, layer_in_group=src.layer_in_group,
+                                                write=False, state_index=src.state_index)
+        groups = [GroupSpec(len(m), s.num_kv_heads, s.head_dim, s.window) for s, m in zip(groups, members)]
+        ps = self.ecfg.page_size
+        elt = torch.empty((), dtype=self.act_dtype).element_size()
+        page_bytes = [g.num_layers * 2 * g.num_kv_heads * ps * g.head_dim * elt for g in groups]
+        if self.ecfg.max_cache_tokens is not None:
+            n_pages = [max(1, -(-self.ecfg.max_cache_tokens // ps)) for _ in groups]
+        elif groups:
+            if self.device.type == "cuda":
+                free, _ = torch.cuda.mem_get_info(self.device)
+                budget = int(free * self.ecfg.memory_fraction)
+            else:
+                budget = 1 << 28
+            per = max(1, budget // max(1, sum(page_bytes)))
+            cap = -(-self.max_model_len // ps) * self.ecfg.max_live_requests
+            n_pages = [max(1, min(per, cap)) for _ in groups]
+        else:
+            n_pages = []
+        self.kv_caches = [
+            torch.zeros((n, g.num_layers, 2, g.num_kv_heads, ps, g.head_dim), dtype=self.act_dtype, device=self.device)
+            for n, g in zip(n_pages, groups)]
+        self.states = [torch.zeros((self.ecfg.max_live_requests,) + tuple(s.shape),
+                                   dtype=_STATE_DTYPES[s.dtype], device=self.device) for s in state_specs]
+        self.cache = CacheManager(groups, ps, n_pages, self.ecfg.max_live_requests)
+        self.groups = groups
+
+    # --------------------------------------------------------------- requests
+    def add_request(self, req: Hashable) -> bool:
+        """Make ``req`` live (a state slot, empty block tables).  False if no slot is free."""
+        slot = self.cache.admit(req)
+        if slot is None:
+            return False
+        for s in self.states:
+            s[slot].zero_()
+        return True
+
+    def finish_request(self, req: Hashable) -> None:
+        self.cache.release(req)
+
+    def num_tokens(self, req: Hashable) -> int:
+        return self.cache.num_tokens(req)
+
+    # ------------------------------------------------------------------- step
+    def make_batch(self, entries: Sequence[StepEntry]) -> StepBatch:
+        """Checks the entries, takes the pages they need (all or nothing) and builds
+        the device-side batch.  Raises OutOfPages without side effects."""
+        seen = set()
+        for e in entries:
+            if not self.cache.is_live(e.req):
+                raise RequestError(f"request {e.req!r} is not live (add_request first)")
+            if e.req in seen:
+                raise RequestError(f"request {e.req!r} appears twice in one step")
+            seen.add(e.req)
+            n = len(e.tokens)
+            if n == 0:
+                raise RequestError(f"request {e.req!r} brings no tokens")
+            if self.cache.num_tokens(e.req) + n > self.max_model_len:
+                raise RequestError(f"request {e.req!r} would exceed the maximum length {self.max_model_len}")
+            lo, hi = min(e.tokens), max(e.tokens)
+            if lo < 0 or hi >= self.desc.vocab_size:
+                raise RequestError(f"request {e.req!r}: token id outside [0, {self.desc.vocab_size})")
+        # all-or-nothing over the whole step: check first, then take
+        need = [0] * len(self.groups)
+        for e in entries:
+            for g, n in enumerate(self.cache.pages_needed(e.req, len(e.tokens))):
+                need[g] += n
+        for g, n in enumerate(need):
+            if n > self.cache.pools[g].num_free:
+                raise OutOfPages(f"step needs {n} pages in cache group {g}, {self.cache.pools[g].num_free} are free")
+        for e in entries:
+            ok = self.cache.reserve(e.req, len(e.tokens))
+            assert ok
+        starts = [self.cache.num_tokens(e.req) for e in entries]
+        slots = [self.cache.slot_of(e.req) for e in entries]
+        tables = [[self.cache.block_table(e.req, g) for e in entries] for g in range(len(self.groups))]
+        return build_step_batch(entries, starts, slots, tables, self.device,
+                                pinned=self.device.type == "cuda")
+
+    def run_batch(self, batch: StepBatch) -> torch.Tensor:
+        return self.model.forward(batch, self.ops, self.act_dtype, self.bindings, self.kv_caches,
+                                  batch.block_tables, self.ecfg.page_size, self.states)
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Runs the entries as one batch; returns float32 logits [wanted rows, vocab] in
+        the order of the entries and of their ``want`` lists."""
+        entries = list(entries)
+        batch = self.make_batch(entries)
+        logits = self.run_batch(batch)
+        for e in entries:
+            self.cache.commit(e.req, len(e.tokens))
+        return logits

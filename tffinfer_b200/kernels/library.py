@@ -1,0 +1,198 @@
+"""The kernel library as the parts see it: one method per kernel, tensors in, nothing
+out (outputs are arguments).  The methods check what the kernels cannot check for
+themselves and pass raw device pointers to the ``extern "C"`` launchers of the
+shared library built from ``csrc/``.
+
+The reference reaches its kernels through a name-keyed callback table
+("<op>_<CPU|GPU>_<dtype>", src/kernel/include/TFFOPCreatorBase.h:62-101) with a CPU
+twin for some ops.  There is one backend here: sm_100a.  If the library cannot be
+built or loaded, or a tensor is not on a CUDA device, the call fails loudly; nothing
+falls back to another implementation.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional
+
+import numpy as np
+import torch
+
+from ..csrc import build as _build
+
+_c_int = ctypes.c_int
+_c_float = ctypes.c_float
+_vp = ctypes.c_void_p
+
+_STATUS = {
+    -1: "bad argument (a size or pointer the kernel cannot take)",
+    -2: "unsupported size for this kernel",
+    -3: "kernel launch failed",
+    -4: "CUDA driver entry point unavailable",
+    -5: "a bounded wait inside a kernel ran out",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return 0
+    if t.dtype == torch.bfloat16:
+        return 1
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, got {t.dtype}")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return _vp(t.data_ptr()) if t is not None else _vp(0)
+
+
+class CudaKernels:
+    """Loads (building first if needed) the sm_100a kernel library."""
+
+    def __init__(self, verbose_build: bool = True):
+        if not torch.cuda.is_available():
+            raise KernelError("tffinfer_b200 needs a CUDA device (sm_100a): torch.cuda.is_available() is False")
+        path = _build.library_path(build=True, verbose=verbose_build)
+        try:
+            self.lib = ctypes.CDLL(path)
+        except OSError as e:
+            raise KernelError(f"cannot load the kernel library {path}: {e}") from None
+        self.path = path
+        self.launches = 0          # number of kernel launches issued through this object
+        self._inv_freq_cache = {}
+
+    # ------------------------------------------------------------- plumbing
+    @staticmethod
+    def _stream():
+        return _vp(torch.cuda.current_stream().cuda_stream)
+
+    def _check(self, status: int, what: str) -> None:
+        if status != 0:
+            raise KernelError(f"{what}: {_STATUS.get(status, f'status {status}')}")
+
+    @staticmethod
+    def _need_cuda(*tensors) -> None:
+        for t in tensors:
+            if t is not None and not t.is_cuda:
+                raise KernelError("a tensor given to a CUDA kernel is not on a CUDA device")
+            if t is not None and not t.is_contiguous():
+                raise KernelError("kernels take contiguous tensors")
+
+    # -------------------------------------------------------------- kernels
+    def embed(self, token_ids, table, out) -> None:
+        self._need_cuda(token_ids, table, out)
+        T, H = out.shape
+        assert token_ids.dtype == torch.int32 and out.dtype == torch.float32 and table.shape[1] == H
+        self._check(self.lib.tff_embed(_ptr(token_ids), _ptr(table), _c_int(_dt(table)), _ptr(out),
+                                       _c_int(T), _c_int(H), _c_int(table.shape[0]), self._stream()), "embed")
+        self.launches += 1
+
+    def rmsnorm(self, x, weight, eps: float, out, row_index=None) -> None:
+        self._need_cuda(x, weight, out, row_index)
+        rows, dim = out.shape
+        assert x.dtype == torch.float32 and weight.dtype == torch.float32 and x.shape[1] == dim
+        assert weight.numel() == dim
+        if row_index is not None:
+            assert row_index.dtype == torch.int32 and row_index.numel() == rows
+        else:
+            assert x.shape[0] == rows
+        self._check(self.lib.tff_rmsnorm(_ptr(x), _ptr(weight), _ptr(row_index), _ptr(out), _c_int(_dt(out)),
+                                         _c_int(rows), _c_int(dim), _c_float(eps), self._stream()), "rmsnorm")
+        self.launches += 1
+
+    def gemm(self, a, w, out, residual=None) -> None:
+        """out[M, N] = a[M, K] @ w[N, K]^T (+ residual, float32 [M, N]; may be ``out``)."""
+        self._need_cuda(a, w, out, residual)
+        M, K = a.shape
+        N = w.shape[0]
+        assert w.shape[1] == K and tuple(out.shape) == (M, N)
+        if residual is not None:
+            assert residual.dtype == torch.float32 and tuple(residual.shape) == (M, N)
+            assert out.dtype == torch.float32
+        self._gemm_dispatch(a, w, out, residual, M, N, K)
+
+    def _gemm_dispatch(self, a, w, out, residual, M, N, K) -> None:
+        self._check(self.lib.tff_gemm_simt(_ptr(a), _c_int(_dt(a)), _ptr(w), _c_int(_dt(w)), _ptr(out),
+                                           _c_int(_dt(out)), _ptr(residual), _c_int(M), _c_int(N), _c_int(K),
+                                           self._stream()), "gemm_simt")
+        self.launches += 1
+
+    def swiglu(self, gate_up, out) -> None:
+        self._need_cuda(gate_up, out)
+        T, I = out.shape
+        assert gate_up.shape == (T, 2 * I) and gate_up.dtype == out.dtype
+        self._check(self.lib.tff_swiglu(_ptr(gate_up), _ptr(out), _c_int(_dt(out)), _c_int(T), _c_int(I),
+                                        self._stream()), "swiglu")
+        self.launches += 1
+
+    def rope_table(self, table, theta: float, rot_dim: int) -> None:
+        """table float32 [max_pos, rot_dim/2, 2] = (cos, sin)(pos * theta^(-2i/rot_dim)).
+        The frequencies exp(-(2i/d) ln theta) (src/kernel/cuda/rope_table.cu:33) are
+        evaluated in double on the host and rounded once to float32."""
+        self._need_cuda(table)
+        half = rot_dim // 2
+        assert table.dtype == torch.float32 and tuple(table.shape[1:]) == (half, 2)
+        i = np.arange(half, dtype=np.float64)
+        inv = np.exp(-(2.0 * i / float(rot_dim)) * math.log(theta)).astype(np.float32)
+        inv_t = torch.from_numpy(inv).to(table.device)
+        self._check(self.lib.tff_rope_table(_ptr(table), _ptr(inv_t), _c_int(table.shape[0]), _c_int(rot_dim),
+                                            self._stream()), "rope_table")
+        torch.cuda.current_stream().synchronize()   # inv_t must outlive the kernel
+        self.launches += 1
+
+    def qk_norm_rope_kv_write(self, qkv, q_w, k_w, eps, table, rot_dim, batch, block_table, kv_cache,
+                              kv_layer, page_size, nq, nkv, d, write_cache) -> None:
+        self._need_cuda(qkv, q_w, k_w, table, block_table, kv_cache)
+        T = qkv.shape[0]
+        assert qkv.shape[1] == (nq + 2 * nkv) * d
+        if write_cache:
+            assert kv_cache is not None and kv_cache.dtype == qkv.dtype, "cache dtype must match activations"
+            assert tuple(kv_cache.shape[2:]) == (2, nkv, page_size, d)
+        layers = kv_cache.shape[1] if kv_cache is not None else 1
+        self._check(self.lib.tff_qk_norm_rope_kv_write(
+            _ptr(qkv), _c_int(_dt(qkv)), _ptr(q_w), _ptr(k_w), _c_float(eps),
+            _ptr(table), _c_int(rot_dim), _c_int(table.shape[0] if table is not None else 0),
+            _ptr(batch.positions), _ptr(batch.tok_req), _ptr(block_table),
+            _c_int(block_table.shape[1] if block_table is not None else 0),
+            _ptr(kv_cache), _c_int(layers), _c_int(kv_layer), _c_int(page_size), _c_int(1 if write_cache else 0),
+            _c_int(T), _c_int(nq), _c_int(nkv), _c_int(d), self._stream()), "qk_norm_rope_kv_write")
+        self.launches += 1
+
+    def attention(self, qkv, batch, block_table, kv_cache, kv_layer, page_size, out,
+                  nq, nkv, d, scale, window) -> None:
+        self._need_cuda(qkv, block_table, kv_cache, out)
+        T = qkv.shape[0]
+        assert kv_cache.dtype == qkv.dtype == out.dtype
+        assert tuple(kv_cache.shape[2:]) == (2, nkv, page_size, d) and tuple(out.shape) == (T, nq * d)
+        self._attention_dispatch(qkv, batch, block_table, kv_cache, kv_layer, page_size, out,
+                                 nq, nkv, d, scale, window)
+
+    def _attention_dispatch(self, qkv, batch, block_table, kv_cache, kv_layer, page_size, out,
+                            nq, nkv, d, scale, window) -> None:
+        T = qkv.shape[0]
+        self._check(self.lib.tff_attention_generic(
+            _ptr(qkv), _c_int(_dt(qkv)), _c_int(qkv.shape[1]),
+            _ptr(batch.positions), _ptr(batch.tok_req), _ptr(block_table), _c_int(block_table.shape[1]),
+            _ptr(kv_cache), _c_int(kv_cache.shape[1]), _c_int(kv_layer), _c_int(page_size),
+            _ptr(out), _c_int(T), _c_int(nq), _c_int(nkv), _c_int(d), _c_float(scale), _c_int(window),
+            self._stream()), "attention_generic")
+        self.launches += 1
+
+    def argmax(self, logits, out) -> None:
+        self._need_cuda(logits, out)
+        R, V = logits.shape
+        assert logits.dtype == torch.float32 and out.dtype == torch.int32 and out.numel() == R
+        self._check(self.lib.tff_argmax(_ptr(logits), _ptr(out), _c_int(R), _c_int(V), self._stream()), "argmax")
+        self.launches += 1
+
+    def sample(self, logits, temperature, uniform, out, top_k=None, top_p=None, min_p=None) -> None:
+        self._need_cuda(logits, temperature, uniform, out, top_k, top_p, min_p)
+        R, V = logits.shape
+        assert logits.dtype == torch.float32 and out.dtype == torch.int32
+        assert temperature.dtype == torch.float32 and uniform.dtype == torch.float32
+        self._check(self.lib.tff_sample(_ptr(logits), _ptr(temperature), _ptr(uniform), _ptr(top_k), _ptr(top_p),
+                                        _ptr(min_p), _ptr(out), _c_int(R), _c_int(V), self._stream()), "sample")
+        self.launches += 1

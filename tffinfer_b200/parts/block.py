@@ -1,0 +1,17 @@
+"""Arrangements of the parts around the residual stream.  ``pre_norm`` is the
+reference's Qwen3 block (src/core/model/qwen3/QWen3Creator.cpp:62-151):
+``x = x + mixer(norm(x)); x = x + ffn(norm(x))``, the stream kept in float32."""
+from __future__ import annotations
+
+from ..registry import register_part
+from .base import Block, LayerContext
+
+
+@register_part("block", "pre_norm")
+class PreNormBlock(Block):
+    def forward(self, x, ctx: LayerContext, act_dtype):
+        h = self.mixer_norm.forward(x, ctx.ops, act_dtype)
+        x = self.mixer.forward(h, ctx, residual=x)
+        h = self.ffn_norm.forward(x, ctx.ops, act_dtype)
+        x = self.feed_forward.forward(h, ctx, residual=x)
+        return x

@@ -1,0 +1,46 @@
+"""Dense gated feed-forward: ``down( silu(gate(h)) * up(h) )`` without biases, with
+``silu(g) = g / (1 + exp(-g))`` as the reference computes it
+(src/kernel/cuda/unary.cu:10-27; built by ModelCreatorBase::build_ffn,
+src/core/model/base/ModelCreatorBase.cpp:51-94), followed by the residual add
+(src/core/model/qwen3/QWen3Creator.cpp:148-151)."""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..registry import register_part
+from .base import FeedForward, WeightSpec, MATRIX
+
+
+@register_part("feed_forward", "swiglu")
+class SwiGLU(FeedForward):
+    def __init__(self, hidden_size: int, intermediate_size: int, prefix: str = ""):
+        super().__init__(prefix)
+        self.hidden_size = int(hidden_size)
+        self.intermediate_size = int(intermediate_size)
+        self.w_gate_up = self.w_down = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {
+            "gate_proj.weight": WeightSpec((self.intermediate_size, self.hidden_size), MATRIX),
+            "up_proj.weight": WeightSpec((self.intermediate_size, self.hidden_size), MATRIX),
+            "down_proj.weight": WeightSpec((self.hidden_size, self.intermediate_size), MATRIX),
+        }
+
+    def load(self, tensors, ops, act_dtype) -> None:
+        g, u = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        dt = g.dtype if g.dtype == u.dtype else torch.float32
+        # one projection instead of two: rows [gate | up]
+        self.w_gate_up = torch.cat([g.to(dt), u.to(dt)], dim=0).contiguous()
+        self.w_down = tensors["down_proj.weight"]
+
+    def forward(self, h, ctx, residual):
+        ops = ctx.ops
+        T = h.shape[0]
+        gu = torch.empty((T, 2 * self.intermediate_size), dtype=h.dtype, device=h.device)
+        ops.gemm(h, self.w_gate_up, gu)
+        act = torch.empty((T, self.intermediate_size), dtype=h.dtype, device=h.device)
+        ops.swiglu(gu, act)
+        ops.gemm(act, self.w_down, residual, residual=residual)
+        return residual
