@@ -1,0 +1,59 @@
+"""The engine on the GPU against the plain implementation, in 32-bit and in bfloat16,
+for every way of cutting the same requests into steps."""
+import pytest
+import torch
+
+from helpers import (tiny_config, make_model_dir, make_requests, PAGE_SIZE, PROMPT_LENS,
+                     trace_whole, trace_tail_decode, trace_portions, trace_mixed, run_trace,
+                     max_rel_err, first_bad)
+from plain_qwen3 import PlainModel
+from tffinfer_b200.config import EngineConfig
+from tffinfer_b200.engine import ModelRunner
+
+pytestmark = pytest.mark.gpu
+
+# largest |difference| over the row's largest |logit|
+TOL = {"float32": 2e-5, "bfloat16": 4e-2}
+
+
+@pytest.fixture(scope="module")
+def plain_logits(tmp_path_factory):
+    out = {}
+    tmp = tmp_path_factory.mktemp("models")
+    for name in ("A", "B", "C"):
+        d = make_model_dir(tmp, name)
+        reqs = make_requests(name)
+        pm = PlainModel(d)
+        out[name] = (d, reqs, {r: pm.logits(t) for r, t in reqs.items()})
+    return out
+
+
+def _steps(name, mode, reqs):
+    ps = PAGE_SIZE[name]
+    longest = max(-(-len(t) // ps) * ps for t in reqs.values())
+    if mode == "mixed":
+        pool = longest + longest // 2
+        return pool, trace_mixed(reqs, PROMPT_LENS[name], max_live=4, page_size=ps, pool_tokens=pool,
+                                 chunk=5 if name == "A" else 7)
+    return longest, {"whole": trace_whole, "tail": trace_tail_decode, "portions": trace_portions}[mode](reqs)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
+def test_cut_modes_match_plain(plain_logits, name, mode, dtype):
+    d, reqs, want = plain_logits[name]
+    pool, steps = _steps(name, mode, reqs)
+    ecfg = EngineConfig(dtype=dtype, page_size=PAGE_SIZE[name], max_cache_tokens=pool, max_live_requests=4,
+                        use_cuda_graphs=False)
+    runner = ModelRunner(d, ecfg)
+    # poison the cache: a read of a slot that was never written shows up as NaN
+    for c in runner.kv_caches:
+        c.fill_(float("nan"))
+    got = run_trace(runner, reqs, steps)
+    for r in reqs:
+        bad = first_bad(got[r], want[r], TOL[dtype])
+        assert bad is None, (f"{name}/{mode}/{dtype}/{r}: first wrong position {bad[0]} "
+                             f"(rel err {bad[1]:.3e}) of {len(reqs[r])}")
+        assert torch.isfinite(got[r]).all()
+    assert all(p.num_free == p.num_pages for p in runner.cache.pools)
