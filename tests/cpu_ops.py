@@ -115,3 +115,8 @@ class CpuOps:
                 int(top_k[r]) if top_k is not None else 0,
                 float(top_p[r]) if top_p is not None else 1.0,
                 float(min_p[r]) if min_p is not None else 0.0)
+
+    def repetition_penalty(self, logits, rows, tokens, penalty):
+        for r, t, p in zip(rows.tolist(), tokens.tolist(), penalty.tolist()):
+            v = float(logits[r, t])
+            logits[r, t] = v / p if v > 0 else v * p

@@ -5,6 +5,7 @@ from .config import EngineConfig, Qwen3Config, ConfigError
 from .registry import (register_architecture, register_part, get_architecture, get_part,
                        registered_architectures, registered_parts, RegistryError)
 from .weights import write_random_model, WeightError
-from .engine import ModelRunner, StepEntry, OutOfPages, RequestError
+from .engine import ModelRunner, StepEntry, OutOfPages, RequestError, Engine, InferRuntime
+from .sampling import SamplingParams
 
 __version__ = "0.1.0"

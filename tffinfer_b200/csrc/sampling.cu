@@ -182,3 +182,24 @@ TFF_API int tff_sample(const float* logits, const float* temperature, const floa
     sample_kernel<<<rows, NT, 0, stream>>>(logits, temperature, uniform, top_k, top_p, min_p, out, vocab);
     return tff_launch_status();
 }
+
+// logits[row[i], token[i]] is divided by penalty[i] if positive, else multiplied
+// (src/core/sampler/LLMSampler.cpp:21-34).  The (row, token) pairs are distinct.
+__global__ void repetition_penalty_kernel(float* logits, const int* __restrict__ rows,
+                                          const int* __restrict__ tokens, const float* __restrict__ penalty,
+                                          int n, int vocab) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int t = tokens[i];
+    if (t < 0 || t >= vocab) return;
+    float* p = logits + (size_t)rows[i] * vocab + t;
+    const float v = *p;
+    *p = v > 0.f ? v / penalty[i] : v * penalty[i];
+}
+
+TFF_API int tff_repetition_penalty(float* logits, const int* rows, const int* tokens, const float* penalty,
+                                   int n, int vocab, cudaStream_t stream) {
+    if (n <= 0) return TFF_OK;
+    repetition_penalty_kernel<<<(n + 255) / 256, 256, 0, stream>>>(logits, rows, tokens, penalty, n, vocab);
+    return tff_launch_status();
+}

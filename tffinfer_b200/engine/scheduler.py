@@ -1,0 +1,238 @@
+"""The scheduler: admits requests, cuts prompts into portions under a token budget,
+decodes, finishes and frees, and decides what happens when pages run out.
+
+The reference has none: ``infer`` walks the sequences one after another, a whole
+prompt and then a decode loop (src/core/runtime/InferRuntime.cu:281-292, :348-375);
+its request record is ``LLMSeq{_tokens, _is_finished, _eog_token_ids, _current_pos,
+_is_prefilled}`` (src/core/runtime/BatchManager.h:19-72) and ``split_simple`` cuts a
+flat batch every MAX_BATCH_SIZE tokens (BatchManager.cpp:135-152), the only hint of
+a token budget.  Continuous batching is named as future work in its docs.
+
+Policy
+  * every step, each running request that is decoding takes one token first; what is
+    left of ``max_tokens_per_step`` goes to running requests that still have prompt
+    to compute, in order of admission, each ``min(rest of prompt, budget left)``;
+    then waiting requests are admitted in arrival order while a slot, budget and
+    pages for their first portion are there;
+  * when a step's pages cannot all be had, the request admitted LAST is preempted:
+    its pages and slot go back, it keeps its tokens (prompt + generated) and moves to
+    the FRONT of the waiting queue, to be recomputed from the start; the draw for a
+    token depends on (seed, request, index) only, so its output does not change;
+  * a request that cannot fit even alone finishes with reason "out_of_memory";
+    a prompt longer than the model allows is refused with reason "too_long"
+    (the reference truncates with a warning, InferRuntime.cu:399-403).
+
+The scheduler touches only the cache manager's host-side accounting, so its
+decisions can be tested without a GPU.
+"""
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Deque, Dict, Hashable, List, Optional, Sequence, Tuple
+
+from ..cache import CacheManager
+from ..sampling.params import SamplingParams
+
+WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+
+
+@dataclass
+class Request:
+    id: Hashable
+    prompt: List[int]
+    params: SamplingParams
+    key: int = 0                              # enters the sampling draw; stable across preemptions
+    generated: List[int] = field(default_factory=list)
+    status: str = WAITING
+    finish_reason: Optional[str] = None
+    num_preemptions: int = 0
+    admitted_at: int = -1                     # admission counter, for choosing a victim
+
+    @property
+    def tokens(self) -> List[int]:
+        return self.prompt + self.generated
+
+    def __len__(self) -> int:
+        return len(self.prompt) + len(self.generated)
+
+
+@dataclass
+class PlanEntry:
+    request: Request
+    start: int                 # position of the first token of this portion
+    tokens: List[int]
+    samples: bool              # the portion ends at the request's last known token: a token is drawn
+
+
+@dataclass
+class StepPlan:
+    entries: List[PlanEntry]
+    preempted: List[Request]
+    finished: List[Request]    # finished without running (refused or out of memory)
+
+    @property
+    def num_tokens(self) -> int:
+        return sum(len(e.tokens) for e in self.entries)
+
+
+@dataclass
+class StepOutput:
+    request_id: Hashable
+    token: Optional[int]
+    finished: bool
+    finish_reason: Optional[str] = None
+
+
+class Scheduler:
+    def __init__(self, cache: CacheManager, max_tokens_per_step: int, max_model_len: int):
+        self.cache = cache
+        self.max_tokens_per_step = int(max_tokens_per_step)
+        self.max_model_len = int(max_model_len)
+        self.waiting: Deque[Request] = deque()
+        self.running: List[Request] = []
+        self._admissions = 0
+        self.counters = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "preemptions": 0}
+
+    # ---------------------------------------------------------------- intake
+    def add(self, req: Request) -> None:
+        req.status = WAITING
+        self.waiting.append(req)
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # -------------------------------------------------------------- planning
+    def _capacity_tokens(self) -> int:
+        return min(p.num_pages for p in self.cache.pools) * self.cache.page_size if self.cache.pools else 1 << 60
+
+    def _free_pages(self) -> List[int]:
+        return [p.num_free for p in self.cache.pools]
+
+    def _fits(self, free: List[int], need: Sequence[int]) -> bool:
+        return all(n <= f for n, f in zip(need, free))
+
+    def _preempt(self, req: Request) -> None:
+        self.cache.release(req.id)
+        self.running.remove(req)
+        req.status = WAITING
+        req.num_preemptions += 1
+        self.counters["preemptions"] += 1
+        self.waiting.appendleft(req)
+
+    def _finish(self, req: Request, reason: str, release: bool) -> None:
+        if release:
+            self.cache.release(req.id)
+        if req in self.running:
+            self.running.remove(req)
+        req.status = FINISHED
+        req.finish_reason = reason
+
+    def schedule(self) -> StepPlan:
+        """Decides the next step and takes its pages.  The plan's entries are ready to be
+        run; after the step, call :meth:`update` with the drawn tokens."""
+        preempted: List[Request] = []
+        finished: List[Request] = []
+        while True:
+            budget = self.max_tokens_per_step
+            free = self._free_pages()
+            chosen: List[Tuple[Request, int]] = []       # (request, number of tokens)
+            ok = True
+            # running requests, oldest admission first: decodes (one token), then prompt portions
+            order = sorted(self.running, key=lambda r: r.admitted_at)
+            decodes = [r for r in order if len(r) - self.cache.num_tokens(r.id) == 1]
+            prefills = [r for r in order if len(r) - self.cache.num_tokens(r.id) > 1]
+            for r in decodes + prefills:
+                if budget <= 0:
+                    break
+                n = min(len(r) - self.cache.num_tokens(r.id), budget)
+                need = self.cache.pages_needed(r.id, n)
+                if not self._fits(free, need):
+                    ok = False
+                    break
+                free = [f - x for f, x in zip(free, need)]
+                budget -= n
+                chosen.append((r, n))
+            if not ok:
+                victim = max(self.running, key=lambda r: r.admitted_at)
+                if len(self.running) == 1:
+                    # alone and still too large for the pool
+                    self._finish(victim, "out_of_memory", release=True)
+                    finished.append(victim)
+                else:
+                    self._preempt(victim)
+                    preempted.append(victim)
+                continue
+            # admissions
+            while self.waiting and budget > 0:
+                r = self.waiting[0]
+                if len(r.prompt) == 0 or len(r) > self.max_model_len:
+                    self.waiting.popleft()
+                    self._finish(r, "too_long" if len(r.prompt) else "empty_prompt", release=False)
+                    finished.append(r)
+                    continue
+                if len(r) > self._capacity_tokens():
+                    self.waiting.popleft()
+                    self._finish(r, "out_of_memory", release=False)
+                    finished.append(r)
+                    continue
+                if self.cache.slots.num_free == 0:
+                    break
+                n = min(len(r), budget)
+                blocks = -(-n // self.cache.page_size)
+                if not self._fits(free, [blocks] * len(free)):
+                    break
+                self.waiting.popleft()
+                slot = self.cache.admit(r.id)
+                assert slot is not None
+                r.status = RUNNING
+                r.admitted_at = self._admissions
+                self._admissions += 1
+                self.running.append(r)
+                free = [f - blocks for f in free]
+                budget -= n
+                chosen.append((r, n))
+            break
+        entries = []
+        for r, n in chosen:
+            start = self.cache.num_tokens(r.id)
+            got = self.cache.reserve(r.id, n)
+            assert got, "pages were counted but could not be taken"
+            toks = r.tokens[start:start + n]
+            entries.append(PlanEntry(r, start, toks, samples=(start + n == len(r))))
+        return StepPlan(entries, preempted, finished)
+
+    # ---------------------------------------------------------------- update
+    def update(self, plan: StepPlan, drawn: Dict[Hashable, int]) -> List[StepOutput]:
+        """Commits the step: tokens written, drawn tokens appended, finished requests freed.
+        ``drawn[request id]`` is the token drawn for each entry with ``samples``."""
+        outs: List[StepOutput] = []
+        self.counters["steps"] += 1
+        for r in plan.finished:
+            outs.append(StepOutput(r.id, None, True, r.finish_reason))
+        for e in plan.entries:
+            r = e.request
+            self.cache.commit(r.id, len(e.tokens))
+            if len(e.tokens) == 1 and r.generated and e.start >= len(r.prompt):
+                self.counters["decode_tokens"] += 1
+            else:
+                self.counters["prefill_tokens"] += len(e.tokens)
+            if not e.samples:
+                continue
+            reason = None
+            tok = None
+            if len(r.generated) >= r.params.max_new_tokens:
+                reason = "length"
+            else:
+                tok = int(drawn[r.id])
+                r.generated.append(tok)
+                if tok in r.params.eos_token_ids:
+                    reason = "stop"
+                elif len(r.generated) >= r.params.max_new_tokens:
+                    reason = "length"
+                elif len(r) >= self.max_model_len:
+                    reason = "max_position"
+            if reason is not None:
+                self._finish(r, reason, release=True)
+            outs.append(StepOutput(r.id, tok, reason is not None, reason))
+        return outs

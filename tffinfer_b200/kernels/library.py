@@ -196,3 +196,13 @@ class CudaKernels:
         self._check(self.lib.tff_sample(_ptr(logits), _ptr(temperature), _ptr(uniform), _ptr(top_k), _ptr(top_p),
                                         _ptr(min_p), _ptr(out), _c_int(R), _c_int(V), self._stream()), "sample")
         self.launches += 1
+
+    def repetition_penalty(self, logits, rows, tokens, penalty) -> None:
+        self._need_cuda(logits, rows, tokens, penalty)
+        n = rows.numel()
+        assert logits.dtype == torch.float32 and rows.dtype == torch.int32 and tokens.dtype == torch.int32
+        assert penalty.dtype == torch.float32 and tokens.numel() == n and penalty.numel() == n
+        self._check(self.lib.tff_repetition_penalty(_ptr(logits), _ptr(rows), _ptr(tokens), _ptr(penalty),
+                                                    _c_int(n), _c_int(logits.shape[1]), self._stream()),
+                    "repetition_penalty")
+        self.launches += 1
