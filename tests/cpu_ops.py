@@ -48,7 +48,7 @@ class CpuOps:
         table[..., 0] = torch.cos(ang).to(torch.float32)
         table[..., 1] = torch.sin(ang).to(torch.float32)
 
-    def qk_norm_rope_kv_write(self, qkv, q_w, k_w, eps, table, rot_dim, batch, block_table, kv_cache,
+    def qk_norm_rope_kv_write(self, qkv, q_out, q_w, k_w, eps, table, rot_dim, batch, block_table, kv_cache,
                               kv_layer, page_size, nq, nkv, d, write_cache):
         T = qkv.shape[0]
         x = qkv.to(F64).view(T, nq + 2 * nkv, d)
@@ -69,8 +69,7 @@ class CpuOps:
             a, b = t[..., :half], t[..., half:rot_dim]
             return torch.cat([a * c - b * s, a * s + b * c, t[..., rot_dim:]], dim=-1)
 
-        qn = rope(norm(q, q_w))
-        qkv.view(T, nq + 2 * nkv, d)[:, :nq] = qn.to(qkv.dtype)
+        q_out.copy_(rope(norm(q, q_w)).reshape(T, nq * d).to(q_out.dtype))
         if not write_cache:
             return
         kn = rope(norm(k, k_w)).to(kv_cache.dtype)
@@ -83,10 +82,10 @@ class CpuOps:
             kv_cache[page, kv_layer, 0, :, pos[t] % page_size, :] = kn[t]
             kv_cache[page, kv_layer, 1, :, pos[t] % page_size, :] = vv[t]
 
-    def attention(self, qkv, batch, block_table, kv_cache, kv_layer, page_size, out,
+    def attention(self, q_in, batch, block_table, kv_cache, kv_layer, page_size, out,
                   nq, nkv, d, scale, window):
-        T = qkv.shape[0]
-        q = qkv.view(T, -1)[:, :nq * d].to(F64).view(T, nq, d)
+        T = q_in.shape[0]
+        q = q_in.to(F64).view(T, nq, d)
         pos = batch.positions.tolist()
         req = batch.tok_req.tolist()
         G = nq // nkv
@@ -102,6 +101,12 @@ class CpuOps:
                 s = (K[:, h // G, :] @ q[t, h]) * scale
                 pr = torch.softmax(s, 0)
                 out[t, h * d:(h + 1) * d] = (pr @ V[:, h // G, :]).to(out.dtype)
+
+    def gemm_swiglu(self, a, w_gate_up, out):
+        gu = a.to(F64) @ w_gate_up.to(F64).t()
+        I = out.shape[1]
+        g, u = gu[:, :I], gu[:, I:]
+        out.copy_(((g / (1.0 + torch.exp(-g))) * u).to(out.dtype))
 
     def argmax(self, logits, out):
         for r in range(logits.shape[0]):

@@ -1,0 +1,300 @@
+"""Each kernel alone against its plain twin (tests/cpu_ops.py), at sizes other than the
+engine's: odd widths, vocabularies that are no power of two, head sizes in steps of 16,
+any number of heads and groups, single rows, page edges."""
+import math
+import random
+
+import numpy as np
+import pytest
+import torch
+
+from cpu_ops import CpuOps
+from tffinfer_b200.engine.batch import StepEntry, build_step_batch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from tffinfer_b200.kernels.library import CudaKernels
+    k = CudaKernels()
+    yield k
+    k.check_errors()
+
+
+def rel_err(got, want):
+    want = want.double().cpu(); got = got.double().cpu()
+    return float((got - want).abs().max() / want.abs().max().clamp_min(1e-30))
+
+
+def g(shape, dtype, seed, scale=1.0):
+    gen = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=gen) * scale).to(dtype)
+
+
+@pytest.mark.parametrize("T,H,V", [(1, 64, 100), (5, 96, 311), (33, 4096, 1000)])
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_embed(ops, T, H, V, dt):
+    table = g((V, H), dt, 1)
+    tok = torch.randint(0, V, (T,), dtype=torch.int32)
+    want = torch.empty(T, H); CpuOps().embed(tok, table, want)
+    out = torch.empty(T, H, device=DEV)
+    ops.embed(tok.to(DEV), table.to(DEV), out)
+    assert torch.equal(out.cpu(), want)
+
+
+@pytest.mark.parametrize("rows,dim", [(1, 48), (7, 80), (3, 4096), (2, 5120), (9, 1000)])
+@pytest.mark.parametrize("odt", [torch.float32, torch.bfloat16])
+def test_rmsnorm_with_and_without_row_index(ops, rows, dim, odt):
+    x = g((rows + 3, dim), torch.float32, 2, 3.0)
+    w = 1 + 0.1 * g((dim,), torch.float32, 3)
+    for idx in (None, torch.tensor([rows + 2] + list(range(rows - 1)), dtype=torch.int32)):
+        n = rows + 3 if idx is None else rows
+        want = torch.empty(n, dim, dtype=odt); CpuOps().rmsnorm(x, w, 1e-5, want, idx)
+        out = torch.empty(n, dim, dtype=odt, device=DEV)
+        ops.rmsnorm(x.to(DEV), w.to(DEV), 1e-5, out, None if idx is None else idx.to(DEV))
+        assert rel_err(out, want) < (1e-6 if odt == torch.float32 else 8e-3)
+
+
+@pytest.mark.parametrize("T,I", [(1, 16), (5, 112), (64, 12288), (3, 1001)])
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_swiglu(ops, T, I, dt):
+    gu = g((T, 2 * I), dt, 4, 2.0)
+    want = torch.empty(T, I, dtype=dt); CpuOps().swiglu(gu, want)
+    out = torch.empty(T, I, dtype=dt, device=DEV)
+    ops.swiglu(gu.to(DEV), out)
+    assert rel_err(out, want) < (1e-6 if dt == torch.float32 else 8e-3)
+    if dt == torch.bfloat16:                      # float32 accumulators in, bfloat16 out
+        gu32 = g((T, 2 * I), torch.float32, 4, 2.0)
+        CpuOps().swiglu(gu32, want)
+        ops.swiglu(gu32.to(DEV), out)
+        assert rel_err(out, want) < 8e-3
+
+
+@pytest.mark.parametrize("theta,rot,maxpos", [(1e4, 16, 128), (1e6, 128, 4096), (5e5, 48, 700)])
+def test_rope_table(ops, theta, rot, maxpos):
+    want = torch.empty(maxpos, rot // 2, 2); CpuOps().rope_table(want, theta, rot)
+    out = torch.empty(maxpos, rot // 2, 2, device=DEV)
+    ops.rope_table(out, theta, rot)
+    assert float((out.cpu() - want).abs().max()) < 2e-6
+
+
+SIMT_SHAPES = [(1, 64, 64), (7, 311, 80), (65, 130, 96), (3, 1000, 264), (130, 64, 17)]
+
+
+@pytest.mark.parametrize("M,N,K", SIMT_SHAPES)
+@pytest.mark.parametrize("adt,wdt,odt", [(torch.float32,) * 3, (torch.bfloat16,) * 3,
+                                         (torch.bfloat16, torch.float32, torch.bfloat16),
+                                         (torch.bfloat16, torch.bfloat16, torch.float32)])
+def test_gemm_simt(ops, M, N, K, adt, wdt, odt):
+    a, w = g((M, K), adt, 5), g((N, K), wdt, 6, 0.05)
+    for use_res in (False, True):
+        if use_res and odt != torch.float32:
+            continue
+        res = g((M, N), torch.float32, 7) if use_res else None
+        want = torch.empty(M, N, dtype=odt); CpuOps().gemm(a, w, want, res)
+        out = res.clone().to(DEV) if use_res else torch.empty(M, N, dtype=odt, device=DEV)
+        ops.gemm_simt(a.to(DEV), w.to(DEV), out, out if use_res else None)
+        assert rel_err(out, want) < (2e-6 if odt == torch.float32 else 8e-3), (M, N, K, use_res)
+
+
+def test_gemm_simt_rows_do_not_depend_on_the_batch(ops):
+    a, w = g((70, 96), torch.float32, 8).to(DEV), g((130, 96), torch.float32, 9).to(DEV)
+    full = torch.empty(70, 130, device=DEV); ops.gemm_simt(a, w, full)
+    one = torch.empty(1, 130, device=DEV); ops.gemm_simt(a[37:38].contiguous(), w, one)
+    assert torch.equal(full[37:38], one)
+
+
+TC_SHAPES = [(1, 128, 64), (8, 6144, 4096), (5, 311, 80), (16, 256, 128), (17, 384, 200), (64, 4096, 1024),
+             (100, 1000, 512), (256, 512, 4096), (257, 512, 256), (300, 311, 264), (1024, 768, 512),
+             (2048, 4096, 4096), (128, 128, 8), (130, 6144, 4096)]
+
+
+@pytest.mark.parametrize("M,N,K", TC_SHAPES)
+def test_gemm_tc_all_epilogues(ops, M, N, K):
+    a, w = g((M, K), torch.bfloat16, 10), g((N, K), torch.bfloat16, 11, 0.05)
+    ad, wd = a.to(DEV), w.to(DEV)
+    ref = a.double() @ w.double().t()
+    scale = float(ref.abs().max())
+    for odt in (torch.bfloat16, torch.float32):
+        out = torch.full((M, N), float("nan"), dtype=odt, device=DEV)
+        ops.gemm_tc(ad, wd, out)
+        err = float((out.double().cpu() - ref).abs().max()) / scale
+        assert err < (1e-5 if odt == torch.float32 else 8e-3), (M, N, K, odt, err)
+    res = g((M, N), torch.float32, 12)
+    out = res.clone().to(DEV)
+    ops.gemm_tc(ad, wd, out, out)
+    err = float((out.double().cpu() - (res.double() + ref)).abs().max()) / scale
+    assert err < 1e-5, (M, N, K, "residual", err)
+    ops.check_errors()
+
+
+@pytest.mark.parametrize("M,N,K,swap,bn,splits", [(8, 512, 4096, 1, 16, 4), (8, 512, 4096, 1, 16, 7),
+                                                  (40, 1000, 1000 // 8 * 8, 1, 64, 3), (64, 4096, 12288, 1, 64, 4),
+                                                  (200, 300, 512, 1, 256, 2), (200, 300, 512, 0, 128, 1),
+                                                  (200, 300, 512, 0, 256, 1), (16, 128, 64, 1, 32, 1)])
+def test_gemm_tc_explicit_plans(ops, M, N, K, swap, bn, splits):
+    a, w = g((M, K), torch.bfloat16, 13), g((N, K), torch.bfloat16, 14, 0.05)
+    ref = a.double() @ w.double().t()
+    res = g((M, N), torch.float32, 15)
+    out = res.clone().to(DEV)
+    ops.gemm_tc(a.to(DEV), w.to(DEV), out, out, plan=(swap, bn, splits))
+    err = float((out.double().cpu() - (res.double() + ref)).abs().max()) / float(ref.abs().max())
+    assert err < 1e-5, err
+    out = torch.full((M, N), float("nan"), device=DEV)
+    ops.gemm_tc(a.to(DEV), w.to(DEV), out, None, plan=(swap, bn, splits))
+    err = float((out.double().cpu() - ref).abs().max()) / float(ref.abs().max())
+    assert err < 1e-5, err
+    ops.check_errors()
+
+
+def _paged_case(nq, nkv, d, page, lens_new, lens_old, window, dt, seed, layers=2, layer=1, rot=None):
+    """Builds a batch of requests with ``lens_old`` tokens already cached and ``lens_new`` new ones,
+    scattered pages, and returns everything both implementations need."""
+    rng = random.Random(seed)
+    B = len(lens_new)
+    total = [o + n for o, n in zip(lens_old, lens_new)]
+    blocks = [-(-t // page) for t in total]
+    n_pages = sum(blocks) + 5
+    ids = list(range(n_pages)); rng.shuffle(ids)
+    tables, k = [], 0
+    for b in blocks:
+        tables.append(ids[k:k + b]); k += b
+    entries = [StepEntry(i, [0] * n, []) for i, n in enumerate(lens_new)]
+    cache = g((n_pages, layers, 2, nkv, page, d), dt, seed + 1)
+    T = sum(lens_new)
+    qkv = g((T, (nq + 2 * nkv) * d), dt, seed + 2)
+    return entries, tables, cache, qkv
+
+
+ATT_CASES = [
+    # nq, nkv, d, page, new, old, window
+    (4, 2, 16, 4, [1, 7, 33], [0, 0, 0], 0),
+    (8, 2, 32, 8, [1, 1, 5], [40, 7, 16], 0),
+    (6, 3, 48, 16, [3, 1, 20], [29, 100, 0], 24),
+    (5, 5, 80, 16, [2, 9], [15, 16], 0),
+    (32, 8, 128, 16, [1, 1, 64], [300, 17, 129], 0),
+    (3, 1, 112, 32, [40], [31], 10),
+]
+
+
+@pytest.mark.parametrize("case", ATT_CASES)
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_qk_norm_rope_write_then_attention(ops, case, dt):
+    nq, nkv, d, page, new, old, window = case
+    entries, tables, cache, qkv = _paged_case(nq, nkv, d, page, new, old, window, dt, seed=20)
+    cpu = CpuOps()
+    table = torch.empty(512, d // 2, 2); cpu.rope_table(table, 1e4, d)
+    qw, kw = 1 + 0.1 * g((d,), torch.float32, 30), 1 + 0.1 * g((d,), torch.float32, 31)
+    bc = build_step_batch(entries, old, list(range(len(new))), [tables], "cpu")
+    bg = build_step_batch(entries, old, list(range(len(new))), [tables], DEV)
+    # plain
+    T = qkv.shape[0]
+    for in_dt in {torch.float32, dt}:
+        qkv_in = qkv.to(in_dt)
+        q_c, cache_c = torch.empty(T, nq * d, dtype=dt), cache.clone()
+        cpu.qk_norm_rope_kv_write(qkv_in, q_c, qw, kw, 1e-6, table, d, bc, bc.block_tables[0], cache_c, 1, page,
+                                  nq, nkv, d, True)
+        q_g, cache_g = torch.empty(T, nq * d, dtype=dt, device=DEV), cache.clone().to(DEV)
+        ops.qk_norm_rope_kv_write(qkv_in.to(DEV), q_g, qw.to(DEV), kw.to(DEV), 1e-6, table.to(DEV), d, bg,
+                                  bg.block_tables[0], cache_g, 1, page, nq, nkv, d, True)
+        tol = 2e-6 if dt == torch.float32 else 1e-2
+        assert rel_err(q_g, q_c) < tol
+        assert rel_err(cache_g, cache_c) < tol
+    out_c = torch.empty(T, nq * d, dtype=dt)
+    cpu.attention(q_c, bc, bc.block_tables[0], cache_c, 1, page, out_c, nq, nkv, d, 1 / math.sqrt(d), window)
+    assert torch.equal(cache_g[:, 0].cpu(), cache[:, 0])            # the other layer is untouched
+    out_g = torch.empty(T, nq * d, dtype=dt, device=DEV)
+    # attention from the plain twin's cache, so that the two kernels are judged separately
+    ops.attention(q_c.to(DEV), bg, bg.block_tables[0], cache_c.to(DEV), 1, page, out_g, nq, nkv, d,
+                  1 / math.sqrt(d), window)
+    assert rel_err(out_g, out_c) < (3e-6 if dt == torch.float32 else 1e-2)
+
+
+def test_attention_finds_one_far_key_among_hundreds(ops):
+    """One key far back is made to dominate: a kernel that skips a page, or reads the wrong
+    one, returns something else than that key's value."""
+    nq, nkv, d, page = 4, 2, 64, 16
+    old, new = [700], [1]
+    for dt in (torch.float32, torch.bfloat16):
+        entries, tables, cache, qkv = _paged_case(nq, nkv, d, page, new, old, 0, dt, seed=40, layers=1, layer=0)
+        far = 37
+        pg, slot = tables[0][far // page], far % page
+        q = qkv.view(1, nq + 2 * nkv, d)[:, :nq].contiguous()
+        for kvh in range(nkv):
+            cache[pg, 0, 0, kvh, slot] = 0
+            cache[pg, 0, 0, kvh, slot, 3] = 60.0
+        q[0, :, 3] = 40.0
+        bg = build_step_batch(entries, old, [0], [tables], DEV)
+        # the new token's own key/value sit at position 700
+        p700 = tables[0][700 // page]
+        cache[p700, 0] = 0
+        out = torch.empty(1, nq * d, dtype=dt, device=DEV)
+        ops.attention(q.view(1, nq * d).to(DEV), bg, bg.block_tables[0], cache.to(DEV), 0, page, out, nq, nkv, d, 1 / math.sqrt(d), 0)
+        for h in range(nq):
+            want = cache[pg, 0, 1, h // 2, slot].float()
+            assert torch.allclose(out[0, h * d:(h + 1) * d].float().cpu(), want, atol=2e-2, rtol=2e-2)
+
+
+def test_window_edge_is_exact(ops):
+    """With window w the key at p-w+1 counts and the key at p-w does not."""
+    nq, nkv, d, page, w = 2, 1, 32, 8, 9
+    old, new = [30], [1]
+    entries, tables, cache, qkv = _paged_case(nq, nkv, d, page, new, old, w, torch.float32, seed=50, layers=1)
+    p = 30
+    cache[:, 0, 0] = 0
+    q = torch.zeros(1, nq, d); q[0, :, 0] = 10.0
+    def put(pos, score, val):
+        pg, sl = tables[0][pos // page], pos % page
+        cache[pg, 0, 0, 0, sl, 0] = score
+        cache[pg, 0, 1, 0, sl] = val
+    for pos in range(31):
+        put(pos, 0.0, 0.0)
+    put(p - w, 50.0, 7.0)          # just outside: must not be seen
+    put(p - w + 1, 8.0, 3.0)       # first key inside
+    bg = build_step_batch(entries, old, [0], [tables], DEV)
+    out = torch.empty(1, nq * d, device=DEV)
+    ops.attention(q.view(1, nq * d).to(DEV), bg, bg.block_tables[0], cache.to(DEV), 0, page, out, nq, nkv, d, 1 / math.sqrt(d), w)
+    assert float(out.max()) <= 3.0 + 1e-4 and float(out.max()) > 2.9
+
+
+@pytest.mark.parametrize("R,V", [(1, 100), (5, 311), (3, 151936), (64, 4097)])
+def test_argmax_first_maximum(ops, R, V):
+    logits = g((R, V), torch.float32, 60)
+    logits[0, V // 2] = 99.0; logits[0, V - 1] = 99.0          # a tie: the lower id wins
+    want = torch.empty(R, dtype=torch.int32); CpuOps().argmax(logits, want)
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    ops.argmax(logits.to(DEV), out)
+    assert out.cpu().tolist() == want.tolist() and int(out[0]) == V // 2
+
+
+@pytest.mark.parametrize("V", [311, 4097, 151936])
+def test_sampling_matches_plain_inverse_cdf(ops, V):
+    R = 24
+    logits = g((R, V), torch.float32, 61, 3.0)
+    rng = np.random.default_rng(0)
+    temp = torch.tensor([0.0 if r % 6 == 0 else 0.5 + 0.1 * r for r in range(R)])
+    u = torch.from_numpy(rng.random(R).astype(np.float32))
+    for filt in (False, True):
+        top_k = torch.tensor([0, 5, 50, 0] * 6, dtype=torch.int32) if filt else None
+        top_p = torch.tensor([1.0, 1.0, 0.9, 0.5] * 6) if filt else None
+        min_p = torch.tensor([0.0, 0.0, 0.0, 0.02] * 6) if filt else None
+        want = torch.empty(R, dtype=torch.int32)
+        CpuOps().sample(logits, temp, u, want, top_k, top_p, min_p)
+        out = torch.empty(R, dtype=torch.int32, device=DEV)
+        ops.sample(logits.to(DEV), temp.to(DEV), u.to(DEV), out,
+                   None if top_k is None else top_k.to(DEV), None if top_p is None else top_p.to(DEV),
+                   None if min_p is None else min_p.to(DEV))
+        same = sum(int(a == b) for a, b in zip(out.cpu().tolist(), want.tolist()))
+        assert same >= R - 1, (filt, out.cpu().tolist(), want.tolist())    # float32 vs float64 cumulative sums
+
+
+def test_repetition_penalty(ops):
+    logits = g((3, 50), torch.float32, 62)
+    rows = torch.tensor([0, 0, 2], dtype=torch.int32); toks = torch.tensor([3, 7, 49], dtype=torch.int32)
+    pen = torch.tensor([1.5, 1.5, 2.0])
+    want = logits.clone(); CpuOps().repetition_penalty(want, rows, toks, pen)
+    out = logits.clone().to(DEV)
+    ops.repetition_penalty(out, rows.to(DEV), toks.to(DEV), pen.to(DEV))
+    assert torch.allclose(out.cpu(), want, rtol=1e-6)

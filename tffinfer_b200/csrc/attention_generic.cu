@@ -19,7 +19,7 @@ constexpr int WARPS = 4;
 
 template <typename T>
 __global__ void __launch_bounds__(WARPS * 32)
-attention_generic_kernel(const T* __restrict__ qkv, int row_stride,
+attention_generic_kernel(const T* __restrict__ q_in, int row_stride,
                          const int* __restrict__ positions, const int* __restrict__ tok_req,
                          const int* __restrict__ block_table, int table_width,
                          const T* __restrict__ cache, KvLayout L, int layer,
@@ -35,7 +35,7 @@ attention_generic_kernel(const T* __restrict__ qkv, int row_stride,
     const int b = tok_req[t];
     const int* table = block_table + (size_t)b * table_width;
     float* q = smem + warp * d;
-    const T* qrow = qkv + (size_t)t * row_stride + (size_t)h * d;
+    const T* qrow = q_in + (size_t)t * row_stride + (size_t)h * d;
     for (int i = lane; i < d; i += 32) q[i] = to_f32<T>(qrow[i]);
     __syncwarp();
 

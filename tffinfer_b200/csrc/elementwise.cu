@@ -66,26 +66,29 @@ TFF_API int tff_rmsnorm(const float* x, const float* w, const int* row_index, vo
 // ------------------------------------------------------------------- SwiGLU
 // out[t, i] = silu(gu[t, i]) * gu[t, I + i], silu(g) = g / (1 + exp(-g))
 // (src/kernel/cuda/unary.cu:10-27: x1 = gate, x2 = up).
-template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total, int inter) {
+template <typename TIN, typename T>
+__global__ void swiglu_kernel(const TIN* __restrict__ gu, T* __restrict__ out, long long total, int inter) {
     for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (long long)gridDim.x * blockDim.x) {
         const long long t = idx / inter;
         const int i = (int)(idx - t * inter);
-        const float g = to_f32<T>(gu[t * 2 * inter + i]);
-        const float u = to_f32<T>(gu[t * 2 * inter + inter + i]);
+        const float g = to_f32<TIN>(gu[t * 2 * inter + i]);
+        const float u = to_f32<TIN>(gu[t * 2 * inter + inter + i]);
         out[idx] = from_f32<T>((g / (1.0f + expf(-g))) * u);
     }
 }
 
-TFF_API int tff_swiglu(const void* gu, void* out, int is_bf16, int rows, int inter, cudaStream_t stream) {
+// dtype codes: 0 = float32, 1 = bfloat16; the input may be float32 with a bfloat16 output.
+TFF_API int tff_swiglu(const void* gu, int in_dt, void* out, int out_dt, int rows, int inter, cudaStream_t stream) {
     if (rows <= 0) return TFF_OK;
     if (inter <= 0) return TFF_ERR_BAD_ARGUMENT;
     const long long total = (long long)rows * inter;
     const int nt = 256;
     const int blocks = (int)((total + nt - 1) / nt < 148 * 16 ? (total + nt - 1) / nt : 148 * 16);
-    if (is_bf16) swiglu_kernel<bf16><<<blocks, nt, 0, stream>>>((const bf16*)gu, (bf16*)out, total, inter);
-    else swiglu_kernel<float><<<blocks, nt, 0, stream>>>((const float*)gu, (float*)out, total, inter);
+    if (in_dt == 1 && out_dt == 1) swiglu_kernel<bf16, bf16><<<blocks, nt, 0, stream>>>((const bf16*)gu, (bf16*)out, total, inter);
+    else if (in_dt == 0 && out_dt == 1) swiglu_kernel<float, bf16><<<blocks, nt, 0, stream>>>((const float*)gu, (bf16*)out, total, inter);
+    else if (in_dt == 0 && out_dt == 0) swiglu_kernel<float, float><<<blocks, nt, 0, stream>>>((const float*)gu, (float*)out, total, inter);
+    else return TFF_ERR_BAD_ARGUMENT;
     return tff_launch_status();
 }
 
@@ -113,17 +116,19 @@ TFF_API int tff_rope_table(float* table, const float* inv_freq, int max_pos, int
 }
 
 // ------------------------------- q/k RMSNorm + RoPE + paged K/V write (fused)
-// One warp per (token, head of [q heads | k heads | v heads]) of the row
-// qkv[t] = [q (nq*d) | k (nkv*d) | v (nkv*d)].
-//   q head: normalise over d with q_w (if given), rotate, write back in place;
+// One warp per (token, head of [q heads | k heads | v heads]) of the projection row
+// qkv[t] = [q (nq*d) | k (nkv*d) | v (nkv*d)], which may be float32 (the projection's
+// accumulators, unrounded) or the activation type.
+//   q head: normalise over d with q_w (if given), rotate, write to q_out[t, head];
 //   k head: normalise with k_w (if given), rotate, write to the K page of the token;
 //   v head: copy to the V page.
 // Per-head norm before RoPE: src/core/model/qwen3/QWen3Creator.cpp:93-101; rotate-half
 // pairing (i, i + rot/2): src/kernel/cuda/paged_flash_attention.cu:300-384; cache write:
 // src/kernel/cuda/set_row.cu:72-123.  Unlike the reference, keys are stored rotated.
-template <typename T>
+template <typename TIN, typename T>
 __global__ void qk_norm_rope_kv_write_kernel(
-    T* __restrict__ qkv, const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+    const TIN* __restrict__ qkv, T* __restrict__ q_out,
+    const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
     const float2* __restrict__ table, int rot_dim,
     const int* __restrict__ positions, const int* __restrict__ tok_req,
     const int* __restrict__ block_table, int table_width,
@@ -136,12 +141,12 @@ __global__ void qk_norm_rope_kv_write_kernel(
     if (head >= heads) return;
     const bool is_q = head < nq, is_k = !is_q && head < nq + nkv;
     if (!is_q && !write_cache) return;
-    T* src = qkv + (size_t)t * heads * d + (size_t)head * d;
+    const TIN* src = qkv + (size_t)t * heads * d + (size_t)head * d;
     const int pos = positions[t];
 
     T* dst;
     if (is_q) {
-        dst = src;
+        dst = q_out + (size_t)t * nq * d + (size_t)head * d;
     } else {
         const int kvh = is_k ? head - nq : head - nq - nkv;
         const int b = tok_req[t];
@@ -151,14 +156,14 @@ __global__ void qk_norm_rope_kv_write_kernel(
               (is_k ? 0 : L.kv_stride) + (size_t)kvh * L.head_stride + (size_t)(pos % L.page_size) * d;
     }
     if (!is_q && !is_k) {                     // V: plain copy
-        for (int i = lane; i < d; i += 32) dst[i] = src[i];
+        for (int i = lane; i < d; i += 32) dst[i] = from_f32<T>(to_f32<TIN>(src[i]));
         return;
     }
     const float* w = is_q ? q_w : k_w;
     float rs = 1.f;
     if (w) {
         float ss = 0.f;
-        for (int i = lane; i < d; i += 32) { const float v = to_f32<T>(src[i]); ss = fmaf(v, v, ss); }
+        for (int i = lane; i < d; i += 32) { const float v = to_f32<TIN>(src[i]); ss = fmaf(v, v, ss); }
         ss = warp_sum(ss);
         rs = rsqrtf(ss / (float)d + eps);
     }
@@ -166,7 +171,7 @@ __global__ void qk_norm_rope_kv_write_kernel(
     const bool rotate = table != nullptr && half > 0 && pos >= 0 && pos < max_pos;
     // pairs (i, i + half), i < half; then the unrotated tail [rot_dim, d)
     for (int i = lane; i < half; i += 32) {
-        float a = to_f32<T>(src[i]), b2 = to_f32<T>(src[i + half]);
+        float a = to_f32<TIN>(src[i]), b2 = to_f32<TIN>(src[i + half]);
         if (w) { a = (a * rs) * w[i]; b2 = (b2 * rs) * w[i + half]; }
         float ra = a, rb = b2;
         if (rotate) {
@@ -174,19 +179,19 @@ __global__ void qk_norm_rope_kv_write_kernel(
             ra = a * cs.x - b2 * cs.y;
             rb = a * cs.y + b2 * cs.x;
         }
-        // both reads of the pair happen before either write (in-place for q)
         dst[i] = from_f32<T>(ra);
         dst[i + half] = from_f32<T>(rb);
     }
     for (int i = 2 * half + lane; i < d; i += 32) {
-        float a = to_f32<T>(src[i]);
+        float a = to_f32<TIN>(src[i]);
         if (w) a = (a * rs) * w[i];
         dst[i] = from_f32<T>(a);
     }
 }
 
+// in_is_f32: the projection row is float32 (else it has the activation type given by is_bf16).
 TFF_API int tff_qk_norm_rope_kv_write(
-    void* qkv, int is_bf16, const float* q_w, const float* k_w, float eps,
+    const void* qkv, int in_is_f32, void* q_out, int is_bf16, const float* q_w, const float* k_w, float eps,
     const float* table, int rot_dim, int max_pos,
     const int* positions, const int* tok_req, const int* block_table, int table_width,
     void* cache, int cache_layers, int layer, int page_size, int write_cache,
@@ -198,13 +203,15 @@ TFF_API int tff_qk_norm_rope_kv_write(
     const int heads = nq + 2 * nkv;
     const int warps = 4;
     dim3 grid((heads + warps - 1) / warps, num_tokens);
-    if (is_bf16)
-        qk_norm_rope_kv_write_kernel<bf16><<<grid, warps * 32, 0, stream>>>(
-            (bf16*)qkv, q_w, k_w, eps, (const float2*)table, rot_dim, positions, tok_req, block_table,
-            table_width, (bf16*)cache, L, layer, write_cache, nq, nkv, d, max_pos);
-    else
-        qk_norm_rope_kv_write_kernel<float><<<grid, warps * 32, 0, stream>>>(
-            (float*)qkv, q_w, k_w, eps, (const float2*)table, rot_dim, positions, tok_req, block_table,
-            table_width, (float*)cache, L, layer, write_cache, nq, nkv, d, max_pos);
+#define TFF_QK_LAUNCH(TIN, T)                                                                                  \
+    qk_norm_rope_kv_write_kernel<TIN, T><<<grid, warps * 32, 0, stream>>>(                                     \
+        (const TIN*)qkv, (T*)q_out, q_w, k_w, eps, (const float2*)table, rot_dim, positions, tok_req,          \
+        block_table, table_width, (T*)cache, L, layer, write_cache, nq, nkv, d, max_pos)
+    if (is_bf16) {
+        if (in_is_f32) TFF_QK_LAUNCH(float, bf16); else TFF_QK_LAUNCH(bf16, bf16);
+    } else {
+        TFF_QK_LAUNCH(float, float);
+    }
+#undef TFF_QK_LAUNCH
     return tff_launch_status();
 }

@@ -110,11 +110,11 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
             }
             cnt = block_sum<NT>(cnt, red);
             mass = block_sum<NT>(mass, red);
-            bool enough = true;
-            if (k > 0 && k < vocab) enough = enough && cnt >= (float)k;
-            if (tp < 1.f) enough = enough && mass >= tp * tot;
-            // moving the threshold up keeps fewer tokens: do it only while each filter
-            // alone would still keep enough
+            // the filters intersect: the final threshold is the larger of the two, i.e. the
+            // largest one at which at least one active filter is still satisfied
+            bool enough = false;
+            if (k > 0 && k < vocab) enough = enough || cnt >= (float)k;
+            if (tp < 1.f) enough = enough || mass >= tp * tot;
             if (tid == 0) { if (enough) sh_a = mid, sh_b = bnd; else sh_a = a, sh_b = mid; }
             __syncthreads();
             a = sh_a; bnd = sh_b;

@@ -115,17 +115,71 @@ class CudaKernels:
         self._gemm_dispatch(a, w, out, residual, M, N, K)
 
     def _gemm_dispatch(self, a, w, out, residual, M, N, K) -> None:
+        if (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K % 8 == 0
+                and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+            self.gemm_tc(a, w, out, residual)
+        else:
+            self.gemm_simt(a, w, out, residual)
+
+    def gemm_simt(self, a, w, out, residual=None) -> None:
+        """Plain-FMA float32-accumulate product for any mix of float32 / bfloat16 operands."""
+        M, K = a.shape
+        N = w.shape[0]
         self._check(self.lib.tff_gemm_simt(_ptr(a), _c_int(_dt(a)), _ptr(w), _c_int(_dt(w)), _ptr(out),
                                            _c_int(_dt(out)), _ptr(residual), _c_int(M), _c_int(N), _c_int(K),
                                            self._stream()), "gemm_simt")
         self.launches += 1
 
+    SWAP_MAX_M = 256          # up to this many rows the weights are the 128-row operand
+    NUM_SMS = 148
+
+    def tc_plan(self, M: int, N: int, K: int, out_is_f32: bool):
+        """(swap, bn, splits) of the tcgen05 product for a shape."""
+        if M <= self.SWAP_MAX_M:
+            bn = 16
+            while bn < M:
+                bn *= 2
+            splits = 1
+            tiles = -(-N // 128)
+            kb = -(-K // 64)
+            if out_is_f32 and tiles < self.NUM_SMS:
+                splits = max(1, min(self.NUM_SMS // tiles, kb // 4))
+            return 1, bn, splits
+        return 0, (256 if N > 128 else 128), 1
+
+    def gemm_tc(self, a, w, out, residual=None, plan=None) -> None:
+        """bfloat16 x bfloat16 product on the tensor cores (tcgen05), float32 accumulation."""
+        M, K = a.shape
+        N = w.shape[0]
+        swap, bn, splits = plan if plan is not None else self.tc_plan(M, N, K, out.dtype == torch.float32)
+        atomic = 0
+        res = residual
+        if splits > 1:
+            assert out.dtype == torch.float32
+            atomic = 1
+            if residual is None:
+                out.zero_()
+            elif residual.data_ptr() != out.data_ptr():
+                out.copy_(residual)
+            res = None
+        self._check(self.lib.tff_gemm_tc(_ptr(a), _ptr(w), _ptr(out), _c_int(_dt(out)), _ptr(res),
+                                         _c_int(M), _c_int(N), _c_int(K), _c_int(swap), _c_int(bn), _c_int(splits),
+                                         _c_int(atomic), self._stream()), "gemm_tc")
+        self.launches += 1
+
+    def check_errors(self) -> None:
+        """Synchronises and raises if a bounded wait inside a kernel ran out since the last check."""
+        v = self.lib.tff_gemm_tc_error()
+        if v != 0:
+            raise KernelError("a bounded wait inside a tcgen05 kernel ran out (or the error word could not be read)")
+
     def swiglu(self, gate_up, out) -> None:
+        """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]; gate_up float32 or of out's type."""
         self._need_cuda(gate_up, out)
         T, I = out.shape
-        assert gate_up.shape == (T, 2 * I) and gate_up.dtype == out.dtype
-        self._check(self.lib.tff_swiglu(_ptr(gate_up), _ptr(out), _c_int(_dt(out)), _c_int(T), _c_int(I),
-                                        self._stream()), "swiglu")
+        assert gate_up.shape == (T, 2 * I) and gate_up.dtype in (torch.float32, out.dtype)
+        self._check(self.lib.tff_swiglu(_ptr(gate_up), _c_int(_dt(gate_up)), _ptr(out), _c_int(_dt(out)),
+                                        _c_int(T), _c_int(I), self._stream()), "swiglu")
         self.launches += 1
 
     def rope_table(self, table, theta: float, rot_dim: int) -> None:
@@ -143,17 +197,21 @@ class CudaKernels:
         torch.cuda.current_stream().synchronize()   # inv_t must outlive the kernel
         self.launches += 1
 
-    def qk_norm_rope_kv_write(self, qkv, q_w, k_w, eps, table, rot_dim, batch, block_table, kv_cache,
+    def qk_norm_rope_kv_write(self, qkv, q_out, q_w, k_w, eps, table, rot_dim, batch, block_table, kv_cache,
                               kv_layer, page_size, nq, nkv, d, write_cache) -> None:
-        self._need_cuda(qkv, q_w, k_w, table, block_table, kv_cache)
+        """qkv [T, (nq+2nkv)*d] float32 or activation type -> q_out [T, nq*d] (normed, rotated) and the
+        token's K/V page slots."""
+        self._need_cuda(qkv, q_out, q_w, k_w, table, block_table, kv_cache)
         T = qkv.shape[0]
-        assert qkv.shape[1] == (nq + 2 * nkv) * d
+        assert qkv.shape[1] == (nq + 2 * nkv) * d and tuple(q_out.shape) == (T, nq * d)
+        assert qkv.dtype in (torch.float32, q_out.dtype)
         if write_cache:
-            assert kv_cache is not None and kv_cache.dtype == qkv.dtype, "cache dtype must match activations"
+            assert kv_cache is not None and kv_cache.dtype == q_out.dtype, "cache dtype must match activations"
             assert tuple(kv_cache.shape[2:]) == (2, nkv, page_size, d)
         layers = kv_cache.shape[1] if kv_cache is not None else 1
         self._check(self.lib.tff_qk_norm_rope_kv_write(
-            _ptr(qkv), _c_int(_dt(qkv)), _ptr(q_w), _ptr(k_w), _c_float(eps),
+            _ptr(qkv), _c_int(1 if qkv.dtype == torch.float32 else 0), _ptr(q_out), _c_int(_dt(q_out)),
+            _ptr(q_w), _ptr(k_w), _c_float(eps),
             _ptr(table), _c_int(rot_dim), _c_int(table.shape[0] if table is not None else 0),
             _ptr(batch.positions), _ptr(batch.tok_req), _ptr(block_table),
             _c_int(block_table.shape[1] if block_table is not None else 0),
@@ -161,25 +219,39 @@ class CudaKernels:
             _c_int(T), _c_int(nq), _c_int(nkv), _c_int(d), self._stream()), "qk_norm_rope_kv_write")
         self.launches += 1
 
-    def attention(self, qkv, batch, block_table, kv_cache, kv_layer, page_size, out,
+    def attention(self, q, batch, block_table, kv_cache, kv_layer, page_size, out,
                   nq, nkv, d, scale, window) -> None:
-        self._need_cuda(qkv, block_table, kv_cache, out)
-        T = qkv.shape[0]
-        assert kv_cache.dtype == qkv.dtype == out.dtype
-        assert tuple(kv_cache.shape[2:]) == (2, nkv, page_size, d) and tuple(out.shape) == (T, nq * d)
-        self._attention_dispatch(qkv, batch, block_table, kv_cache, kv_layer, page_size, out,
+        """q [T, nq*d] (normed, rotated) against the paged cache -> out [T, nq*d]."""
+        self._need_cuda(q, block_table, kv_cache, out)
+        T = q.shape[0]
+        assert kv_cache.dtype == q.dtype == out.dtype
+        assert tuple(q.shape) == (T, nq * d) and tuple(out.shape) == (T, nq * d)
+        assert tuple(kv_cache.shape[2:]) == (2, nkv, page_size, d)
+        self._attention_dispatch(q, batch, block_table, kv_cache, kv_layer, page_size, out,
                                  nq, nkv, d, scale, window)
 
-    def _attention_dispatch(self, qkv, batch, block_table, kv_cache, kv_layer, page_size, out,
+    def _attention_dispatch(self, q, batch, block_table, kv_cache, kv_layer, page_size, out,
                             nq, nkv, d, scale, window) -> None:
-        T = qkv.shape[0]
+        self.attention_generic(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, scale, window)
+
+    def attention_generic(self, q, batch, block_table, kv_cache, kv_layer, page_size, out,
+                          nq, nkv, d, scale, window) -> None:
+        T = q.shape[0]
         self._check(self.lib.tff_attention_generic(
-            _ptr(qkv), _c_int(_dt(qkv)), _c_int(qkv.shape[1]),
+            _ptr(q), _c_int(_dt(q)), _c_int(q.shape[1]),
             _ptr(batch.positions), _ptr(batch.tok_req), _ptr(block_table), _c_int(block_table.shape[1]),
             _ptr(kv_cache), _c_int(kv_cache.shape[1]), _c_int(kv_layer), _c_int(page_size),
             _ptr(out), _c_int(T), _c_int(nq), _c_int(nkv), _c_int(d), _c_float(scale), _c_int(window),
             self._stream()), "attention_generic")
         self.launches += 1
+
+    def gemm_swiglu(self, a, w_gate_up, out) -> None:
+        """out[T, I] = silu(a @ Wg^T) * (a @ Wu^T) with w_gate_up = [Wg; Wu] ([2I, K])."""
+        T, I = out.shape
+        small = (a.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and T <= self.SWAP_MAX_M)
+        gu = torch.empty((T, 2 * I), dtype=torch.float32 if small else out.dtype, device=out.device)
+        self.gemm(a, w_gate_up, gu)
+        self.swiglu(gu, out)
 
     def argmax(self, logits, out) -> None:
         self._need_cuda(logits, out)

@@ -72,16 +72,18 @@ class GQAttention(Mixer):
     def forward(self, h, ctx: LayerContext, residual):
         ops, batch = ctx.ops, ctx.batch
         T = h.shape[0]
-        qkv = torch.empty((T, self.q_width + 2 * self.kv_width), dtype=h.dtype, device=h.device)
+        # the projection's accumulators stay in float32 until q and k have been normalised
+        qkv = torch.empty((T, self.q_width + 2 * self.kv_width), dtype=torch.float32, device=h.device)
         ops.gemm(h, self.w_qkv, qkv)
+        q = torch.empty((T, self.q_width), dtype=h.dtype, device=h.device)
         rot = ctx.position.rotary() if ctx.position is not None else None
         ops.qk_norm_rope_kv_write(
-            qkv, self.q_norm_w, self.k_norm_w, self.qk_norm_eps,
+            qkv, q, self.q_norm_w, self.k_norm_w, self.qk_norm_eps,
             rot[0] if rot else None, rot[1] if rot else 0,
             batch, ctx.block_table, ctx.kv_cache, ctx.kv_layer, ctx.page_size,
             self.num_heads, self.num_kv_heads, self.head_dim, ctx.write_cache)
         attn = torch.empty((T, self.q_width), dtype=h.dtype, device=h.device)
-        ops.attention(qkv, batch, ctx.block_table, ctx.kv_cache, ctx.kv_layer, ctx.page_size,
+        ops.attention(q, batch, ctx.block_table, ctx.kv_cache, ctx.kv_layer, ctx.page_size,
                       attn, self.num_heads, self.num_kv_heads, self.head_dim, self.scale, self.window)
         ops.gemm(attn, self.w_o, residual, residual=residual)
         return residual

@@ -37,10 +37,7 @@ class SwiGLU(FeedForward):
 
     def forward(self, h, ctx, residual):
         ops = ctx.ops
-        T = h.shape[0]
-        gu = torch.empty((T, 2 * self.intermediate_size), dtype=h.dtype, device=h.device)
-        ops.gemm(h, self.w_gate_up, gu)
-        act = torch.empty((T, self.intermediate_size), dtype=h.dtype, device=h.device)
-        ops.swiglu(gu, act)
+        act = torch.empty((h.shape[0], self.intermediate_size), dtype=h.dtype, device=h.device)
+        ops.gemm_swiglu(h, self.w_gate_up, act)
         ops.gemm(act, self.w_down, residual, residual=residual)
         return residual
