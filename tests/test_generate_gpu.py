@@ -1,0 +1,131 @@
+"""Generation through the entry point on the GPU: greedy and sampled tokens against the
+plain implementation, with and without CUDA graphs, long decoding, preemption."""
+import random
+
+import pytest
+import torch
+
+from helpers import tiny_config, make_model_dir, PAGE_SIZE
+from plain_qwen3 import PlainModel, sample_greedy, sample_temperature
+from tffinfer_b200 import Engine, EngineConfig, SamplingParams
+from tffinfer_b200.sampling import uniform_for
+
+pytestmark = pytest.mark.gpu
+
+
+def _engine(d, name, dtype, **kw):
+    kw.setdefault("max_cache_tokens", 1024)
+    kw.setdefault("max_live_requests", 4)
+    return Engine(d, EngineConfig(dtype=dtype, page_size=PAGE_SIZE[name], **kw))
+
+
+def _follows_plain(pm, prompt, generated, slack):
+    """Every generated token is the plain implementation's choice, or within ``slack`` (relative
+    to the largest logit) of it -- a near tie that rounding may flip."""
+    toks = list(prompt)
+    for t in generated:
+        logits = pm.logits(toks)[-1]
+        gap = float(logits.max() - logits[t]) / float(logits.abs().max())
+        if gap > slack:
+            return False
+        toks.append(t)
+    return True
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_greedy_float32_equals_plain(tmp_path, graphs):
+    d = make_model_dir(tmp_path, "A")
+    pm = PlainModel(d)
+    rng = random.Random(5)
+    prompts = [[rng.randrange(256) for _ in range(n)] for n in (1, 7, 33)]
+    eng = _engine(d, "A", "float32", use_cuda_graphs=graphs, max_tokens_per_step=5)
+    got = eng.generate(prompts, max_new_tokens=16)
+    for p, g in zip(prompts, got):
+        assert len(g) == 16 and _follows_plain(pm, p, g, 1e-5)
+    eng.runner.ops.check_errors()
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_greedy_bfloat16_follows_plain_and_graphs_change_nothing(tmp_path, name):
+    d = make_model_dir(tmp_path, name)
+    pm = PlainModel(d)
+    cfg = tiny_config(name)
+    rng = random.Random(6)
+    prompts = [[rng.randrange(cfg.vocab_size) for _ in range(n)] for n in (2, 13, 40)]
+    outs = []
+    for graphs in (False, True):
+        eng = _engine(d, name, "bfloat16", use_cuda_graphs=graphs, max_tokens_per_step=16)
+        outs.append(eng.generate(prompts, max_new_tokens=24))
+        eng.runner.ops.check_errors()
+    assert outs[0] == outs[1]
+    for p, g in zip(prompts, outs[0]):
+        assert _follows_plain(pm, p, g, 3e-2)
+
+
+def test_temperature_sampling_float32_equals_plain_whatever_the_batching(tmp_path):
+    d = make_model_dir(tmp_path, "B")
+    pm = PlainModel(d)
+    rng = random.Random(7)
+    prompts = [[rng.randrange(320) for _ in range(n)] for n in (2, 13, 40, 64)]
+    sp = SamplingParams.make(temperature=0.7, seed=42, max_new_tokens=24)
+    want = []
+    for key, p in enumerate(prompts):
+        toks, out = list(p), []
+        for i in range(24):
+            t = sample_temperature(pm.logits(toks)[-1], 0.7, uniform_for(42, key, i))
+            out.append(t); toks.append(t)
+        want.append(out)
+    together = _engine(d, "B", "float32", max_tokens_per_step=7).generate(prompts, sp)
+    alone = _engine(d, "B", "float32", max_live_requests=1, max_tokens_per_step=64).generate(prompts, sp)
+    assert together == alone
+    agree = sum(int(a == b) for g, w in zip(together, want) for a, b in zip(g, w))
+    # a draw that lands within rounding of a boundary of the cumulative distribution may differ
+    first_diff_ok = all(g == w or g[:next(i for i in range(24) if g[i] != w[i])] == w[:next(i for i in range(24) if g[i] != w[i])]
+                        for g, w in zip(together, want))
+    assert first_diff_ok and agree >= 0.9 * 24 * len(prompts)
+
+
+def test_long_decoding_with_graphs_and_window(tmp_path):
+    d = make_model_dir(tmp_path, "C")
+    pm = PlainModel(d)
+    rng = random.Random(8)
+    prompts = [[rng.randrange(311) for _ in range(n)] for n in (5, 21)]
+    eng = _engine(d, "C", "float32", use_cuda_graphs=True, max_tokens_per_step=8)
+    got = eng.generate(prompts, max_new_tokens=300)
+    for p, g in zip(prompts, got):
+        assert len(g) == 300
+        assert _follows_plain(pm, p, g[:64], 1e-5)
+        # the last tokens, far into the decode: the whole sequence once through the plain model
+        logits = pm.logits(p + g)
+        for i in (250, 275, 299):
+            row = logits[len(p) + i - 1]
+            assert float(row.max() - row[g[i]]) / float(row.abs().max()) < 1e-5
+    assert all(pool.num_free == pool.num_pages for pool in eng.runner.cache.pools)
+
+
+def test_preemption_on_the_gpu_gives_the_same_tokens(tmp_path):
+    d = make_model_dir(tmp_path, "A")
+    rng = random.Random(9)
+    prompts = [[rng.randrange(256) for _ in range(n)] for n in (9, 17, 30)]
+    big = _engine(d, "A", "float32", max_cache_tokens=512, max_tokens_per_step=6).generate(prompts, max_new_tokens=20)
+    small_eng = _engine(d, "A", "float32", max_cache_tokens=64, max_tokens_per_step=6)
+    small = small_eng.generate(prompts, max_new_tokens=20)
+    assert small == big and small_eng.scheduler.counters["preemptions"] > 0
+
+
+def test_infer_runtime_and_cli(tmp_path, capsys):
+    from tffinfer_b200 import InferRuntime
+    from tffinfer_b200.cli import main
+    d = make_model_dir(tmp_path, "A")
+    rt = InferRuntime()
+    rt.load_model([d], use_f16=True, n_ctx=64, page_size=4, max_cache_tokens=256)
+    assert rt.init_runtime_context()
+    rt.encode([[1, 2, 3], [4, 5]])
+    out = []
+    rt.infer(6, out)
+    assert [len(o) for o in out] == [6, 6]
+    assert main([d, "--prompt-ids", "1,2,3", "--prompt-ids", "4,5", "--n-predict", "6", "--page-size", "4",
+                 "--max-cache-tokens", "256", "--json"]) == 0
+    import json
+    rec = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rec["outputs"] == out

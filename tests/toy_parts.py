@@ -1,0 +1,198 @@
+"""Toy parts defined outside the framework: a mixer with state of its own, a routed
+feed-forward, an absolute position encoding, and an architecture made of them.  They
+exist to show that parts and architectures can be registered, built and stepped
+without a change to the framework's files.  They are not a model of anyone's."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict
+
+import torch
+
+from tffinfer_b200 import register_part, register_architecture
+from tffinfer_b200.config import ModelConfig
+from tffinfer_b200.parts import (Mixer, FeedForward, PositionEncoding, WeightSpec, MATRIX, VECTOR, StateNeed,
+                                 ModelDescription, LayerSpec, PartSpec, ScheduleEntry)
+
+
+@register_part("mixer", "toy_running_mean", replace=True)
+class RunningMeanMixer(Mixer):
+    """out_t = W . mean(h_0 .. h_t).  The state is the running sum and the count."""
+    def __init__(self, hidden_size: int, prefix: str = ""):
+        super().__init__(prefix)
+        self.hidden_size = hidden_size
+
+    def cache_need(self):
+        return StateNeed((self.hidden_size + 1,), "float32")
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {"mix.weight": WeightSpec((self.hidden_size, self.hidden_size), MATRIX)}
+
+    def load(self, tensors, ops, act_dtype):
+        self.w = tensors["mix.weight"]
+
+    def forward(self, h, ctx, residual):
+        b = ctx.batch
+        H = self.hidden_size
+        q_start = b.q_start.tolist()
+        slots = b.slots.tolist()
+        mean = torch.empty(h.shape, dtype=torch.float32, device=h.device)
+        for i in range(b.num_requests):
+            rows = slice(q_start[i], q_start[i + 1])
+            st = ctx.state[slots[i]]
+            csum = torch.cumsum(h[rows].float(), 0) + st[:H]
+            cnt = st[H] + torch.arange(1, rows.stop - rows.start + 1, device=h.device, dtype=torch.float32)
+            mean[rows] = csum / cnt[:, None]
+            st[:H] = csum[-1]
+            st[H] = cnt[-1]
+        out = torch.empty_like(residual)
+        ctx.ops.gemm(mean.to(h.dtype), self.w, out)
+        residual += out
+        return residual
+
+
+@register_part("feed_forward", "toy_top1_experts", replace=True)
+class Top1Experts(FeedForward):
+    """Router logits in float32, one expert per token, each expert a single matrix."""
+    def __init__(self, hidden_size: int, num_experts: int, prefix: str = ""):
+        super().__init__(prefix)
+        self.hidden_size, self.num_experts = hidden_size, num_experts
+
+    def weight_specs(self):
+        s = {"router.weight": WeightSpec((self.num_experts, self.hidden_size), VECTOR, init="normal", init_scale=0.5)}
+        for e in range(self.num_experts):
+            s[f"experts.{e}.weight"] = WeightSpec((self.hidden_size, self.hidden_size), MATRIX)
+        return s
+
+    def load(self, tensors, ops, act_dtype):
+        self.router = tensors["router.weight"]
+        self.experts = [tensors[f"experts.{e}.weight"] for e in range(self.num_experts)]
+
+    def forward(self, h, ctx, residual):
+        choice = (h.float() @ self.router.t()).argmax(-1)
+        for e in range(self.num_experts):
+            idx = (choice == e).nonzero().flatten()
+            if idx.numel() == 0:
+                continue
+            out = torch.empty((idx.numel(), self.hidden_size), dtype=torch.float32, device=h.device)
+            ctx.ops.gemm(h[idx].contiguous(), self.experts[e], out)
+            residual[idx] += out
+        return residual
+
+
+@register_part("position", "toy_learned_absolute", replace=True)
+class LearnedAbsolute(PositionEncoding):
+    """A learned vector per position, added to the residual stream after the embedding."""
+    def __init__(self, hidden_size: int, max_position: int, prefix: str = ""):
+        super().__init__(prefix)
+        self.hidden_size, self.max_position = hidden_size, max_position
+
+    def weight_specs(self):
+        return {"weight": WeightSpec((self.max_position, self.hidden_size), VECTOR, init="normal", init_scale=0.02)}
+
+    def load(self, tensors, ops, act_dtype):
+        self.table = tensors["weight"]
+
+    def embed(self, x, batch, ops):
+        return x + self.table[batch.positions.long()]
+
+
+@dataclass(frozen=True)
+class ToyConfig(ModelConfig):
+    hidden_size: int = 48
+    vocab_size: int = 97
+    num_layers: int = 3
+    num_experts: int = 3
+    max_position: int = 128
+    eps: float = 1e-5
+
+    @staticmethod
+    def from_json_dict(d):
+        return ToyConfig(architecture=d["architectures"][0], hidden_size=d["hidden_size"], vocab_size=d["vocab_size"],
+                         num_layers=d["num_layers"], num_experts=d["num_experts"],
+                         max_position=d["max_position"], eps=d["eps"])
+
+    def to_json_dict(self):
+        return {"architectures": [self.architecture], "hidden_size": self.hidden_size, "vocab_size": self.vocab_size,
+                "num_layers": self.num_layers, "num_experts": self.num_experts, "max_position": self.max_position,
+                "eps": self.eps}
+
+
+def describe_toy(cfg: ToyConfig) -> ModelDescription:
+    H = cfg.hidden_size
+    layers = []
+    for i in range(cfg.num_layers):
+        p = f"blocks.{i}"
+        if i % 2 == 0:
+            mixer = PartSpec("toy_running_mean", dict(hidden_size=H), prefix=f"{p}.mixer")
+        else:
+            mixer = PartSpec("gqa_attention", dict(hidden_size=H, num_heads=3, num_kv_heads=1, head_dim=16,
+                                                   qk_norm=False, window=0), prefix=f"{p}.mixer")
+        ffn = (PartSpec("toy_top1_experts", dict(hidden_size=H, num_experts=cfg.num_experts), prefix=f"{p}.ffn")
+               if i % 2 == 0 else PartSpec("swiglu", dict(hidden_size=H, intermediate_size=2 * H), prefix=f"{p}.ffn"))
+        layers.append(LayerSpec(mixer=mixer, feed_forward=ffn,
+                                mixer_norm=PartSpec("rms_norm", dict(dim=H, eps=cfg.eps), prefix=f"{p}.norm1"),
+                                ffn_norm=PartSpec("rms_norm", dict(dim=H, eps=cfg.eps), prefix=f"{p}.norm2"),
+                                position=None))
+    # layer 0 runs twice (each run with a state of its own); the last run of the attention
+    # layer reads the cache of its first run instead of keeping one
+    schedule = [ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(2), ScheduleEntry(0), ScheduleEntry(1, cache_of=1)]
+    return ModelDescription(
+        hidden_size=H, vocab_size=cfg.vocab_size, max_position=cfg.max_position,
+        embed_name="embed.weight", lm_head_name="head.weight",
+        final_norm=PartSpec("rms_norm", dict(dim=H, eps=cfg.eps), prefix="final_norm"),
+        layers=layers, schedule=schedule,
+        positions={"abs": PartSpec("toy_learned_absolute", dict(hidden_size=H, max_position=cfg.max_position),
+                                   prefix="positions")})
+
+
+def register_toy():
+    register_architecture("ToyStateLM", ToyConfig.from_json_dict, describe_toy, replace=True)
+
+
+# ------------------------------------------------------------------ plain whole-sequence twin
+def toy_plain_logits(tokens, w: Dict[str, torch.Tensor], cfg: ToyConfig) -> torch.Tensor:
+    import math
+    D = torch.float64
+    w = {k: v.to(D) for k, v in w.items()}
+    H = cfg.hidden_size
+    T = len(tokens)
+
+    def norm(x, name):
+        return (x * torch.rsqrt((x * x).mean(-1, keepdim=True) + cfg.eps)) * w[name]
+
+    x = w["embed.weight"][torch.tensor(tokens)] + w["positions.weight"][:T]
+    kv_of_layer1 = None
+    for e, li in enumerate([0, 1, 2, 0, 1]):
+        p = f"blocks.{li}"
+        h = norm(x, f"{p}.norm1.weight")
+        if li % 2 == 0:
+            mean = torch.cumsum(h, 0) / torch.arange(1, T + 1, dtype=D)[:, None]
+            x = x + mean @ w[f"{p}.mixer.mix.weight"].t()
+        else:
+            q = (h @ w[f"{p}.mixer.q_proj.weight"].t()).view(T, 3, 16)
+            if e == 1:
+                k = (h @ w[f"{p}.mixer.k_proj.weight"].t()).view(T, 1, 16)
+                v = (h @ w[f"{p}.mixer.v_proj.weight"].t()).view(T, 1, 16)
+                kv_of_layer1 = (k, v)
+            else:
+                k, v = kv_of_layer1                      # the borrowed cache
+            o = torch.empty(T, 3, 16, dtype=D)
+            mask = torch.tril(torch.ones(T, T, dtype=torch.bool))
+            for hh in range(3):
+                s = (q[:, hh] @ k[:, 0].t()) / math.sqrt(16)
+                o[:, hh] = torch.softmax(s.masked_fill(~mask, float("-inf")), -1) @ v[:, 0]
+            x = x + o.reshape(T, 48) @ w[f"{p}.mixer.o_proj.weight"].t()
+        h = norm(x, f"{p}.norm2.weight")
+        if li % 2 == 0:
+            choice = (h @ w[f"{p}.ffn.router.weight"].t()).argmax(-1)
+            out = torch.zeros_like(x)
+            for ex in range(cfg.num_experts):
+                sel = choice == ex
+                out[sel] = h[sel] @ w[f"{p}.ffn.experts.{ex}.weight"].t()
+            x = x + out
+        else:
+            g = h @ w[f"{p}.ffn.gate_proj.weight"].t()
+            u = h @ w[f"{p}.ffn.up_proj.weight"].t()
+            x = x + ((g / (1 + torch.exp(-g))) * u) @ w[f"{p}.ffn.down_proj.weight"].t()
+    return norm(x, "final_norm.weight") @ w["head.weight"].t()

@@ -7,11 +7,14 @@ one contiguous run of one sequence at a time (InferRuntime.cu:429;
 QWen3Creator.cpp:267-268).  Here any mix runs as one batch.
 
 All integer arrays are packed into one host buffer and reach the device in one copy.
+A batch may be padded to a fixed number of requests and a fixed block-table width,
+so that its device arrays have fixed addresses and sizes (for CUDA graphs); padding
+requests bring one token at position 0 whose keys go to a page nobody reads.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import List, Optional, Sequence
+from typing import List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -25,6 +28,31 @@ class StepEntry:
     req: object
     tokens: Sequence[int]
     want: Sequence[int] = ()
+
+
+@dataclass(frozen=True)
+class BatchLayout:
+    """Sizes of the packed integer buffer: T tokens, B requests, R logit rows, and the
+    block-table width of each cache group."""
+    T: int
+    B: int
+    R: int
+    widths: Tuple[int, ...]
+
+    def sizes(self) -> List[int]:
+        return [self.T, self.T, self.T, self.B + 1, self.B, self.B, self.B, self.R] + \
+               [self.B * w for w in self.widths]
+
+    @property
+    def total(self) -> int:
+        return int(sum(self.sizes()))
+
+    def offsets(self) -> List[int]:
+        out, off = [], 0
+        for n in self.sizes():
+            out.append(off)
+            off += n
+        return out
 
 
 @dataclass
@@ -47,23 +75,47 @@ class StepBatch:
     h_q_lens: Optional[np.ndarray] = None
     h_pos_start: Optional[np.ndarray] = None
     all_decode: bool = False      # every request brings exactly one token
+    real_requests: int = 0        # requests that are not padding
+    real_logit_rows: int = 0
+    graph_bucket: Optional[int] = None   # set when the arrays are the fixed ones of a CUDA-graph bucket
 
 
-def build_step_batch(entries: Sequence[StepEntry], starts: Sequence[int], slots: Sequence[int],
-                     tables: Sequence[Sequence[Sequence[int]]], device, pad_width_to: int = 1,
-                     pinned: bool = False) -> StepBatch:
-    """entries[i] starts at position starts[i]; tables[g][i] is request i's block table
-    in group g (a list of page ids, -1 for pages that were given back)."""
-    B = len(entries)
+def batch_views(dev: torch.Tensor, layout: BatchLayout):
+    """Slices of the packed device buffer, in the order of BatchLayout.sizes()."""
+    offs, sizes = layout.offsets(), layout.sizes()
+    v = [dev[o:o + n] for o, n in zip(offs[:8], sizes[:8])]
+    bts = [dev[o:o + n].view(layout.B, w) for o, n, w in zip(offs[8:], sizes[8:], layout.widths)]
+    return v, bts
+
+
+def pack_step(entries: Sequence[StepEntry], starts: Sequence[int], slots: Sequence[int],
+              tables: Sequence[Sequence[Sequence[int]]], *, pad_requests: int = 0,
+              widths: Optional[Sequence[int]] = None, dummy_pages: Optional[Sequence[int]] = None, dummy_slot: int = 0,
+              out: Optional[np.ndarray] = None):
+    """Packs the step into one int32 array.  Returns (array, layout, info).
+
+    entries[i] starts at position starts[i]; tables[g][i] is request i's block table in
+    group g (page ids, -1 for pages that were given back).  With ``pad_requests`` > len(entries)
+    the batch is filled up with padding requests (one token 0 at position 0, logits asked)."""
+    nreal = len(entries)
     q_lens = np.array([len(e.tokens) for e in entries], dtype=np.int32)
-    if B == 0 or (q_lens <= 0).any():
+    if nreal == 0 or (q_lens <= 0).any():
         raise ValueError("a step needs at least one request and every request at least one token")
+    npad = max(0, pad_requests - nreal)
+    B = nreal + npad
+    if npad:
+        q_lens = np.concatenate([q_lens, np.ones(npad, dtype=np.int32)])
     T = int(q_lens.sum())
     q_start = np.zeros(B + 1, dtype=np.int32)
     np.cumsum(q_lens, out=q_start[1:])
-    pos_start = np.asarray(starts, dtype=np.int32)
+    pos_start = np.zeros(B, dtype=np.int32)
+    pos_start[:nreal] = np.asarray(starts, dtype=np.int32)
     kv_len = pos_start + q_lens
-    token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries]).astype(np.int32)
+    token_ids = np.zeros(T, dtype=np.int32)
+    if T - npad == nreal:           # every real request brings one token
+        token_ids[:nreal] = [e.tokens[0] for e in entries]
+    else:
+        token_ids[:T - npad] = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
     tok_req = np.repeat(np.arange(B, dtype=np.int32), q_lens)
     positions = (np.arange(T, dtype=np.int32) - np.repeat(q_start[:-1], q_lens) + np.repeat(pos_start, q_lens)).astype(np.int32)
     rows = []
@@ -72,41 +124,58 @@ def build_step_batch(entries: Sequence[StepEntry], starts: Sequence[int], slots:
             if not (0 <= int(w) < int(q_lens[i])):
                 raise ValueError(f"request {e.req!r}: wanted place {w} is outside its {int(q_lens[i])} tokens")
             rows.append(int(q_start[i]) + int(w))
-    logit_rows = np.asarray(rows, dtype=np.int32)
+    real_rows = len(rows)
+    rows.extend(int(q_start[nreal + j]) for j in range(npad))
     G = len(tables)
-    widths = []
+    if widths is None:
+        widths = [max(1, max((len(t) for t in tables[g]), default=0)) for g in range(G)]
+    layout = BatchLayout(T, B, len(rows), tuple(int(w) for w in widths))
+    if out is None:
+        out = np.empty(layout.total, dtype=np.int32)
+    elif out.shape[0] != layout.total:
+        raise ValueError("the given buffer does not fit the batch layout")
+    offs = layout.offsets()
+    slot_arr = np.full(B, dummy_slot, dtype=np.int32)
+    slot_arr[:nreal] = np.asarray(slots, dtype=np.int32)
+    for o, arr in zip(offs[:8], (token_ids, positions, tok_req, q_start, pos_start, kv_len, slot_arr,
+                                 np.asarray(rows, dtype=np.int32))):
+        out[o:o + arr.shape[0]] = arr
     for g in range(G):
-        w = max((len(t) for t in tables[g]), default=0)
-        w = max(1, -(-w // pad_width_to) * pad_width_to)
-        widths.append(w)
-    sizes = [T, T, T, B + 1, B, B, B, len(rows)] + [B * w for w in widths]
-    total = int(sum(sizes))
-    host = torch.empty(total, dtype=torch.int32, pin_memory=pinned)
-    hv = host.numpy()
-    off = 0
-    parts = []
-    for arr in (token_ids, positions, tok_req, q_start, pos_start, kv_len,
-                np.asarray(slots, dtype=np.int32), logit_rows):
-        n = arr.shape[0]
-        hv[off:off + n] = arr
-        parts.append((off, n))
-        off += n
-    tparts = []
-    for g in range(G):
-        w = widths[g]
-        bt = np.full((B, w), -1, dtype=np.int32)
+        w = layout.widths[g]
+        bt = out[offs[8 + g]:offs[8 + g] + B * w].reshape(B, w)
+        bt[:nreal] = -1
+        bt[nreal:] = dummy_pages[g] if dummy_pages is not None else -1
         for i, t in enumerate(tables[g]):
-            if len(t):
-                bt[i, :len(t)] = np.asarray(t, dtype=np.int32)
-        hv[off:off + B * w] = bt.reshape(-1)
-        tparts.append((off, B, w))
-        off += B * w
-    dev = host.to(device, non_blocking=pinned) if str(device) != "cpu" else host
-    v = [dev[o:o + n] for o, n in parts]
-    bts = [dev[o:o + b * w].view(b, w) for o, b, w in tparts]
+            n = len(t)
+            if n > w:
+                raise ValueError("a block table is wider than the batch layout allows")
+            if n:
+                bt[i, :n] = t
+    info = dict(max_q_len=int(q_lens.max()), max_kv_len=int(kv_len.max()), q_lens=q_lens, pos_start=pos_start,
+                all_decode=bool((q_lens == 1).all()), real_requests=nreal, real_logit_rows=real_rows)
+    return out, layout, info
+
+
+def batch_from_device(dev: torch.Tensor, layout: BatchLayout, info) -> StepBatch:
+    v, bts = batch_views(dev, layout)
     return StepBatch(
-        num_tokens=T, num_requests=B, num_logit_rows=len(rows),
-        max_q_len=int(q_lens.max()), max_kv_len=int(kv_len.max()),
+        num_tokens=layout.T, num_requests=layout.B, num_logit_rows=layout.R,
+        max_q_len=info["max_q_len"], max_kv_len=info["max_kv_len"],
         token_ids=v[0], positions=v[1], tok_req=v[2], q_start=v[3], pos_start=v[4], kv_len=v[5],
         slots=v[6], logit_rows=v[7], block_tables=bts,
-        h_q_lens=q_lens, h_pos_start=pos_start, all_decode=bool((q_lens == 1).all()))
+        h_q_lens=info["q_lens"], h_pos_start=info["pos_start"], all_decode=info["all_decode"],
+        real_requests=info["real_requests"], real_logit_rows=info["real_logit_rows"])
+
+
+def build_step_batch(entries: Sequence[StepEntry], starts: Sequence[int], slots: Sequence[int],
+                     tables: Sequence[Sequence[Sequence[int]]], device, pinned: bool = False) -> StepBatch:
+    """Packs the step and copies it to ``device`` in one transfer."""
+    arr, layout, info = pack_step(entries, starts, slots, tables)
+    host = torch.from_numpy(arr)
+    if str(device) == "cpu":
+        dev = host
+    elif pinned:
+        dev = host.pin_memory().to(device, non_blocking=True)
+    else:
+        dev = host.to(device)
+    return batch_from_device(dev, layout, info)

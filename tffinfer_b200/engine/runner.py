@@ -20,7 +20,7 @@ from ..config import EngineConfig, read_config_json
 from ..parts import Model, CacheBinding, KVNeed, StateNeed
 from ..registry import get_architecture
 from ..weights import load_model_weights
-from .batch import StepEntry, StepBatch, build_step_batch
+from .batch import StepEntry, StepBatch, build_step_batch, pack_step, batch_from_device, BatchLayout
 
 _TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 _STATE_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": torch.int32}
@@ -122,11 +122,22 @@ class ModelRunner:
             n_pages = [max(1, min(per, cap)) for _ in groups]
         else:
             n_pages = []
+        # one page and one state slot more than the pools hand out: padding rows of a
+        # fixed-size batch write there and nobody reads them
         self.kv_caches = [
-            torch.zeros((n, g.num_layers, 2, g.num_kv_heads, ps, g.head_dim), dtype=self.act_dtype, device=self.device)
+            torch.zeros((n + 1, g.num_layers, 2, g.num_kv_heads, ps, g.head_dim), dtype=self.act_dtype, device=self.device)
             for n, g in zip(n_pages, groups)]
-        self.states = [torch.zeros((self.ecfg.max_live_requests,) + tuple(s.shape),
+        self.dummy_pages = list(n_pages)
+        self.dummy_slot = self.ecfg.max_live_requests
+        self.states = [torch.zeros((self.ecfg.max_live_requests + 1,) + tuple(s.shape),
                                    dtype=_STATE_DTYPES[s.dtype], device=self.device) for s in state_specs]
+        self._graphs = {}
+        self._graph_pool = None
+        self.graph_buckets = [b for b in (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+                              if b <= self.ecfg.max_live_requests] or [self.ecfg.max_live_requests]
+        if self.graph_buckets[-1] < min(self.ecfg.max_live_requests, 256):
+            self.graph_buckets.append(min(self.ecfg.max_live_requests, 256))
+        self.table_width = max(1, -(-self.max_model_len // ps))
         self.cache = CacheManager(groups, ps, n_pages, self.ecfg.max_live_requests)
         self.groups = groups
 
@@ -179,12 +190,68 @@ class ModelRunner:
         starts = [self.cache.num_tokens(e.req) for e in entries]
         slots = [self.cache.slot_of(e.req) for e in entries]
         tables = [[self.cache.block_table(e.req, g) for e in entries] for g in range(len(self.groups))]
+        if self._graph_eligible(entries):
+            return self._make_static_batch(entries, starts, slots, tables)
         return build_step_batch(entries, starts, slots, tables, self.device,
                                 pinned=self.device.type == "cuda")
 
-    def run_batch(self, batch: StepBatch) -> torch.Tensor:
+    # ------------------------------------------------------------ CUDA graphs
+    def _graph_eligible(self, entries) -> bool:
+        return (self.ecfg.use_cuda_graphs and self.device.type == "cuda"
+                and len(entries) <= self.graph_buckets[-1]
+                and all(len(e.tokens) == 1 and len(e.want) == 1 for e in entries))
+
+    def _make_static_batch(self, entries, starts, slots, tables) -> StepBatch:
+        """Decode-only steps use device arrays of fixed address and size, one set per
+        batch-size bucket, so that the step can be replayed as a CUDA graph."""
+        bucket = next(b for b in self.graph_buckets if b >= len(entries))
+        st = self._graphs.get(bucket)
+        if st is None:
+            layout = BatchLayout(bucket, bucket, bucket, tuple(self.table_width for _ in self.groups))
+            st = {"layout": layout,
+                  "host": torch.empty(layout.total, dtype=torch.int32, pin_memory=True),
+                  "dev": torch.empty(layout.total, dtype=torch.int32, device=self.device),
+                  "graph": None, "logits": None}
+            self._graphs[bucket] = st
+        if st.get("copied") is not None:
+            st["copied"].synchronize()              # the last copy out of the staging buffer has finished
+        arr, layout, info = pack_step(entries, starts, slots, tables, pad_requests=bucket,
+                                      widths=st["layout"].widths, dummy_pages=self.dummy_pages,
+                                      dummy_slot=self.dummy_slot, out=st["host"].numpy())
+        st["dev"].copy_(st["host"], non_blocking=True)
+        if st.get("copied") is None:
+            st["copied"] = torch.cuda.Event()
+        st["copied"].record()
+        batch = batch_from_device(st["dev"], layout, info)
+        batch.graph_bucket = bucket
+        return batch
+
+    def _run_graph(self, batch: StepBatch) -> torch.Tensor:
+        st = self._graphs[batch.graph_bucket]
+        if st["graph"] is None:
+            self._forward(batch)                    # warm-up outside the capture (same writes, same values)
+            torch.cuda.current_stream().synchronize()
+            g = torch.cuda.CUDAGraph()
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            launches = getattr(self.ops, "launches", 0)
+            with torch.cuda.graph(g, pool=self._graph_pool):
+                st["logits"] = self._forward(batch)
+            st["graph"] = g
+            st["launches"] = getattr(self.ops, "launches", 0) - launches
+        st["graph"].replay()
+        if hasattr(self.ops, "launches"):
+            self.ops.launches += st["launches"]
+        return st["logits"][:batch.real_logit_rows]
+
+    def _forward(self, batch: StepBatch) -> torch.Tensor:
         return self.model.forward(batch, self.ops, self.act_dtype, self.bindings, self.kv_caches,
                                   batch.block_tables, self.ecfg.page_size, self.states)
+
+    def run_batch(self, batch: StepBatch) -> torch.Tensor:
+        if getattr(batch, "graph_bucket", None) is not None:
+            return self._run_graph(batch)
+        return self._forward(batch)
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Runs the entries as one batch; returns float32 logits [wanted rows, vocab] in
