@@ -1,0 +1,282 @@
+#!/usr/bin/env python3
+"""Benchmark of the engine on one B200: decode tokens per second at the Qwen3-8B shape
+(random bfloat16 weights, batch 8, 2048-token prompts, 16-token cache pages), with the
+prefill rate of one 2048-token prompt, decode at batch 1 and 64, the same decode
+measured end to end through the Python entry point, and roofline fractions.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" is one decode step of the whole batch.  Prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import random
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: the Qwen3-8B shape
+SHAPE = dict(num_layers=36, hidden_size=4096, num_heads=32, num_kv_heads=8, head_dim=128,
+             intermediate_size=12288, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6, max_position=40960)
+CONTEXT = 4096
+PROMPT_LEN = 2048
+PAGE_SIZE = 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(p):
+        try:
+            with open(p) as f:
+                d = json.load(f)
+            out = dict(FALLBACK_PEAKS)
+            for k in out:
+                if isinstance(d.get(k), (int, float)) and d[k] > 0:
+                    out[k] = float(d[k])
+            out["source"] = "measured"
+            return out
+        except Exception:
+            pass
+    out = dict(FALLBACK_PEAKS)
+    out["source"] = "fallback"
+    return out
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+
+        def pump():
+            for line in self.proc.stdout:
+                self.samples.append(line.strip())
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            f = [x.strip() for x in s.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_engine(layers: int, max_live: int, cache_tokens: int, seed: int = 0):
+    import torch
+    import tffinfer_b200 as tff
+    from tffinfer_b200.config import Qwen3Config
+    from tffinfer_b200.weights import random_tensors_on_device
+    cfg = Qwen3Config(architecture="Qwen3ForCausalLM", tie_word_embeddings=False,
+                      layer_types=("full_attention",) * layers, **{**SHAPE, "num_layers": layers}).validate()
+    tensors = random_tensors_on_device(cfg, seed, "cuda", "bfloat16")
+    ecfg = tff.EngineConfig(dtype="bfloat16", page_size=PAGE_SIZE, max_cache_tokens=cache_tokens,
+                            max_live_requests=max_live, max_tokens_per_step=PROMPT_LEN, max_model_len=CONTEXT)
+    runner = tff.ModelRunner(config=cfg, tensors=tensors, engine_config=ecfg)
+    del tensors
+    torch.cuda.empty_cache()
+    return tff.Engine(runner=runner), cfg
+
+
+def model_bytes(cfg) -> dict:
+    H, L, I, V = cfg.hidden_size, cfg.num_layers, cfg.intermediate_size, cfg.vocab_size
+    qw, kvw = cfg.num_heads * cfg.head_dim, cfg.num_kv_heads * cfg.head_dim
+    per_layer = (qw + 2 * kvw) * H + H * qw + 3 * I * H
+    return {"layer_params": per_layer, "weights_read_per_step": 2 * (per_layer * L + V * H),
+            "kv_bytes_per_token": 2 * L * cfg.num_kv_heads * cfg.head_dim * 2}
+
+
+def decode_run(engine, batch: int, steps: int, warmup: int, seed: int, sampler=None):
+    """Prefills ``batch`` prompts of PROMPT_LEN tokens, then times ``steps`` decode steps
+    after ``warmup`` untimed ones.  Returns device-timed and wall-clock figures."""
+    import torch
+    from tffinfer_b200 import SamplingParams
+    rng = random.Random(seed)
+    vocab = engine.runner.desc.vocab_size
+    sp = SamplingParams(max_new_tokens=warmup + steps + batch + 8)   # earlier requests decode while later ones prefill
+    ids = [engine.add_request([rng.randrange(vocab) for _ in range(PROMPT_LEN)], sp, request_id=f"b{batch}_{i}", key=i)
+           for i in range(batch)]
+    # prefill: until every request has produced its first token
+    while any(len(engine.requests[i].generated) == 0 for i in ids):
+        engine.step()
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    ops = engine.runner.ops
+    launches0 = ops.launches
+    ctx0 = sum(len(engine.requests[i]) for i in ids) / batch
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    engine.step_events = None
+    if sampler is not None:
+        sampler.start()
+    t0 = time.perf_counter()
+    for k in range(steps):
+        engine.step_events = ev[k]
+        outs = engine.step()
+        assert len(outs) == batch
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    if sampler is not None:
+        sampler.stop()
+    engine.step_events = None
+    dev_ms = sum(a.elapsed_time(b) for a, b in ev)
+    ctx1 = sum(len(engine.requests[i]) for i in ids) / batch
+    launches = ops.launches - launches0
+    ops.check_errors()
+    h2d = engine.runner.last_h2d_bytes
+    for i in ids:                                   # stop the requests and give their pages back
+        r = engine.requests.pop(i)
+        if r.status == "running":
+            engine.scheduler._finish(r, "abort", release=True)
+    return {"tok_s": batch * steps / (dev_ms / 1e3), "ms_per_step": dev_ms / steps,
+            "e2e_tok_s": batch * steps / wall, "launches": launches, "mean_context": (ctx0 + ctx1) / 2,
+            "h2d_bytes": h2d, "d2h_bytes": 4 * batch}
+
+
+def prefill_run(engine, iters: int, warmup: int, seed: int):
+    import torch
+    from tffinfer_b200 import StepEntry
+    rng = random.Random(seed)
+    vocab = engine.runner.desc.vocab_size
+    runner = engine.runner
+    times = []
+    for it in range(warmup + iters):
+        toks = [rng.randrange(vocab) for _ in range(PROMPT_LEN)]
+        rid = f"prefill{it}"
+        runner.add_request(rid)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        batch = runner.make_batch([StepEntry(rid, toks, [PROMPT_LEN - 1])])
+        torch.cuda.synchronize()
+        a.record()
+        logits = runner.run_batch(batch)
+        b.record()
+        torch.cuda.synchronize()
+        runner.cache.commit(rid, PROMPT_LEN)
+        runner.finish_request(rid)
+        if it >= warmup:
+            times.append(a.elapsed_time(b))
+        assert logits.shape[0] == 1
+    runner.ops.check_errors()
+    return statistics.median(times)
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=SHAPE["num_layers"],
+                    help="fewer layers than the shape has (both numbers are reported)")
+    ap.add_argument("--skip-points", action="store_true", help="only the headline batch (no batch 1 / 64, no prefill)")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "NKKdev/TFFinfer is a CMake C++/CUDA project without Python packaging whose dependencies "
+                          "(glog, Taskflow, libdivide) are fetched from the network; it loads GGUF Q8_0 files only and "
+                          "has no sm_100 build: it cannot be installed offline here"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    warmup = max(3, args.warmup)
+
+    import torch
+    if not torch.cuda.is_available():
+        print("bench.py: no CUDA device", file=sys.stderr)
+        return 1
+    peaks = load_peaks()
+    max_batch = args.batch if args.skip_points else max(args.batch, 64)
+    tokens_needed = max_batch * (PROMPT_LEN + warmup + args.steps + max_batch + 64)
+    engine, cfg = make_engine(args.layers, max_batch, tokens_needed)
+    mb = model_bytes(cfg)
+
+    clocks = ClockSampler()
+    main_run = decode_run(engine, args.batch, args.steps, warmup, seed=1, sampler=clocks)
+    points = {}
+    prefill = None
+    if not args.skip_points:
+        small_steps = min(args.steps, 32)
+        points["decode_b1"] = round(decode_run(engine, 1, small_steps, warmup, seed=2)["tok_s"], 1)
+        points["decode_b64"] = round(decode_run(engine, 64, small_steps, warmup, seed=3)["tok_s"], 1)
+        pms = prefill_run(engine, iters=5, warmup=3, seed=4)
+        T = PROMPT_LEN
+        flops = 2 * T * mb["layer_params"] * cfg.num_layers \
+            + 2 * T * T * cfg.head_dim * cfg.num_heads * cfg.num_layers + 2 * cfg.vocab_size * cfg.hidden_size
+        prefill = {"value": round(T / (pms / 1e3), 1), "tokens": T, "ms": round(pms, 3),
+                   "frac": round(flops / (pms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4),
+                   "tflops": round(flops / (pms / 1e3) / 1e12, 1)}
+
+    step_s = main_run["ms_per_step"] / 1e3
+    bytes_step = mb["weights_read_per_step"] + args.batch * main_run["mean_context"] * mb["kv_bytes_per_token"]
+    achieved = bytes_step / step_s / 1e9
+    out = {
+        "metric": "decode tok/s (Qwen3-8B shape, bf16, batch 8, 2048-token prompts)",
+        "value": round(main_run["tok_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded uniform token ids, random N(0,0.02) weights)",
+        "impl": "ours",
+        "config": {"model": "Qwen3-8B shape", "layers": cfg.num_layers, "layers_of_shape": SHAPE["num_layers"],
+                   "hidden": cfg.hidden_size, "heads": cfg.num_heads, "kv_heads": cfg.num_kv_heads,
+                   "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                   "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "page_size": PAGE_SIZE,
+                   "parallelism": "1 GPU", "l2": "inputs larger than L2 (15 GB of weights read per step)",
+                   "cuda_graphs": True},
+        "e2e": {"value": round(main_run["e2e_tok_s"], 1), "unit": "tok/s",
+                "h2d_bytes_per_step": main_run["h2d_bytes"], "d2h_bytes_per_step": main_run["d2h_bytes"]},
+        "gpu_launches": main_run["launches"],
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peaks["hbm_gbs"], 4), "peaks": peaks["source"]},
+        "clocks": clocks.summary(),
+    }
+    if prefill is not None:
+        out["prefill"] = prefill
+        out["points"] = points
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

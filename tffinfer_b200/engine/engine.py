@@ -35,6 +35,7 @@ class Engine:
         self.sampler = Sampler(runner.ops, runner.device)
         self.requests: Dict[Hashable, Request] = {}
         self._ids = itertools.count()
+        self.step_events = None      # optional (start, end) CUDA events recorded around the step's device work
 
     # --------------------------------------------------------------- requests
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
@@ -64,6 +65,9 @@ class Engine:
             entries = [StepEntry(e.request.id, e.tokens, [len(e.tokens) - 1] if e.samples else [])
                        for e in plan.entries]
             batch = self.runner.make_batch(entries)
+            ev = self.step_events
+            if ev is not None:
+                ev[0].record()
             logits = self.runner.run_batch(batch)
             samplers = [e.request for e in plan.entries if e.samples]
             if samplers:
@@ -72,8 +76,12 @@ class Engine:
                     logits, [r.params for r in samplers], [r.key for r in samplers],
                     [len(r.generated) for r in samplers],
                     [r.tokens for r in samplers] if need_seen else None)
+                if ev is not None:
+                    ev[1].record()
                 host = toks.cpu().tolist()
                 drawn = {r.id: t for r, t in zip(samplers, host)}
+            elif ev is not None:
+                ev[1].record()
         return self.scheduler.update(plan, drawn)
 
     # --------------------------------------------------------------- generate

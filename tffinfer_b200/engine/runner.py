@@ -132,6 +132,7 @@ class ModelRunner:
         self.states = [torch.zeros((self.ecfg.max_live_requests + 1,) + tuple(s.shape),
                                    dtype=_STATE_DTYPES[s.dtype], device=self.device) for s in state_specs]
         self._graphs = {}
+        self.last_h2d_bytes = 0
         self._graph_pool = None
         self.graph_buckets = [b for b in (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
                               if b <= self.ecfg.max_live_requests] or [self.ecfg.max_live_requests]
@@ -192,8 +193,11 @@ class ModelRunner:
         tables = [[self.cache.block_table(e.req, g) for e in entries] for g in range(len(self.groups))]
         if self._graph_eligible(entries):
             return self._make_static_batch(entries, starts, slots, tables)
-        return build_step_batch(entries, starts, slots, tables, self.device,
-                                pinned=self.device.type == "cuda")
+        batch = build_step_batch(entries, starts, slots, tables, self.device, pinned=self.device.type == "cuda")
+        self.last_h2d_bytes = batch.token_ids.numel() * 0 + 4 * (
+            3 * batch.num_tokens + 4 * batch.num_requests + 1 + batch.num_logit_rows
+            + sum(t.numel() for t in batch.block_tables))
+        return batch
 
     # ------------------------------------------------------------ CUDA graphs
     def _graph_eligible(self, entries) -> bool:
@@ -222,6 +226,7 @@ class ModelRunner:
         if st.get("copied") is None:
             st["copied"] = torch.cuda.Event()
         st["copied"].record()
+        self.last_h2d_bytes = layout.total * 4
         batch = batch_from_device(st["dev"], layout, info)
         batch.graph_bucket = bucket
         return batch

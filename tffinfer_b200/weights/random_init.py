@@ -63,3 +63,33 @@ def write_random_model(model_dir: str, cfg: ModelConfig, seed: int, store_dtype:
     write_safetensors(os.path.join(model_dir, "model.safetensors"), tensors,
                       metadata={"format": "pt", "seed": str(seed)})
     return model_dir
+
+
+def random_tensors_on_device(cfg: ModelConfig, seed: int, device, store_dtype: str = "bfloat16",
+                             norm_noise: float = 0.0) -> Dict[str, torch.Tensor]:
+    """Random weights made on the device, for shapes too large to go through a file
+    quickly (benchmarks).  Matrices are N(0, init_std); norm weights 1 + N(0, norm_noise)."""
+    arch = get_architecture(cfg.architecture)
+    desc = arch.describe(cfg)
+    model = Model(desc)
+    sd = _STORE[store_dtype]
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    out = {}
+    for name, spec in model.expected_tensors().items():
+        if spec.role == INT_TABLE:
+            out[name] = torch.zeros(spec.shape, dtype=torch.int32, device=device)
+        elif spec.init == "one_plus_normal":
+            s = norm_noise if spec.init_scale is None else spec.init_scale
+            t = torch.ones(spec.shape, dtype=torch.float32, device=device)
+            if s:
+                t += s * torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device)
+            out[name] = t.to(sd)
+        elif spec.init == "zeros":
+            out[name] = torch.zeros(spec.shape, dtype=sd, device=device)
+        else:
+            s = desc.init_std if spec.init_scale is None else spec.init_scale
+            t = torch.empty(spec.shape, dtype=sd, device=device)
+            t.normal_(0.0, s, generator=gen)
+            out[name] = t
+    return out
