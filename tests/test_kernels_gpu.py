@@ -212,6 +212,57 @@ def test_qk_norm_rope_write_then_attention(ops, case, dt):
     assert rel_err(out_g, out_c) < (3e-6 if dt == torch.float32 else 1e-2)
 
 
+FLASH_CASES = [
+    # nq, nkv, d, page, new, old, window, splits
+    (32, 8, 128, 16, [1, 1, 1], [300, 17, 2049], 0, 1),        # decode, keys mode
+    (32, 8, 128, 16, [1, 1, 1], [300, 17, 2049], 0, 4),        # decode, split keys (some splits empty)
+    (32, 8, 128, 16, [1], [5], 0, 16),                         # more splits than key blocks
+    (8, 8, 64, 8, [1, 2, 1], [63, 64, 65], 0, 3),              # no grouping, block edges
+    (16, 2, 64, 32, [1, 1], [200, 31], 0, 2),                  # 8 heads a group: 8-row tiles
+    (32, 8, 128, 16, [70, 1, 33], [0, 500, 129], 0, 1),        # portions beside a decode token (rows mode)
+    (32, 8, 128, 16, [200], [0], 0, 1),                        # a whole prompt, several tiles
+    (12, 4, 64, 16, [50, 3], [77, 10], 0, 1),                  # 3 heads a group: tiles cut through tokens
+    (8, 2, 128, 16, [40, 1], [100, 150], 48, 1),               # sliding window, rows mode
+    (8, 2, 128, 16, [1, 1], [100, 30], 48, 2),                 # sliding window, decode
+    (4, 4, 128, 16, [130], [1], 0, 2),                         # rows mode with split keys
+]
+
+
+@pytest.mark.parametrize("case", FLASH_CASES)
+def test_flash_attention_bf16(ops, case):
+    nq, nkv, d, page, new, old, window, splits = case
+    dt = torch.bfloat16
+    entries, tables, cache, qkv = _paged_case(nq, nkv, d, page, new, old, window, dt, seed=70, layers=2)
+    # slots beyond each request's tokens and unused pages hold NaN: reading them shows
+    used = torch.zeros(cache.shape[0], page, dtype=torch.bool)
+    for tb, n, o in zip(tables, new, old):
+        for pos in range(n + o):
+            used[tb[pos // page], pos % page] = True
+    cache = cache.clone()
+    cache.permute(0, 4, 1, 2, 3, 5)[~used] = float("nan")
+    if window > 0:                                             # pages a window has passed are given back
+        for i, (tb, n, o) in enumerate(zip(tables, new, old)):
+            first_needed = max(0, o - window + 1) // page
+            tables[i] = [-1] * first_needed + tb[first_needed:]
+    T = sum(new)
+    q = qkv[:, :nq * d].contiguous()
+    bc = build_step_batch(entries, old, list(range(len(new))), [tables], "cpu")
+    bg = build_step_batch(entries, old, list(range(len(new))), [tables], DEV)
+    want = torch.empty(T, nq * d, dtype=dt)
+    ctab = bc.block_tables[0].clone()
+    CpuOps().attention(q, bc, ctab.clamp_min(0) if window > 0 else ctab, torch.nan_to_num(cache, nan=1e4),
+                       1, page, want, nq, nkv, d, 1 / math.sqrt(d), window)
+    out = torch.full((T, nq * d), float("nan"), dtype=dt, device=DEV)
+    ops.attention_bf16(q.to(DEV), bg, bg.block_tables[0], cache.to(DEV), 1, page, out, nq, nkv, d, 1 / math.sqrt(d),
+                       window, num_splits=splits)
+    assert torch.isfinite(out).all()
+    assert rel_err(out, want) < 1e-2
+    gen = torch.empty(T, nq * d, dtype=dt, device=DEV)
+    ops.attention_generic(q.to(DEV), bg, bg.block_tables[0], torch.nan_to_num(cache, nan=1e4).to(DEV), 1, page, gen,
+                          nq, nkv, d, 1 / math.sqrt(d), window)
+    assert rel_err(out, gen) < 1e-2
+
+
 def test_attention_finds_one_far_key_among_hundreds(ops):
     """One key far back is made to dominate: a kernel that skips a page, or reads the wrong
     one, returns something else than that key's value."""

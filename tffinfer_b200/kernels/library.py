@@ -232,7 +232,36 @@ class CudaKernels:
 
     def _attention_dispatch(self, q, batch, block_table, kv_cache, kv_layer, page_size, out,
                             nq, nkv, d, scale, window) -> None:
-        self.attention_generic(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, scale, window)
+        if q.dtype == torch.bfloat16 and d in (64, 128):
+            self.attention_bf16(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, scale, window)
+        else:
+            self.attention_generic(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, scale, window)
+
+    def attention_splits(self, num_requests: int, max_q_len: int, nq: int, nkv: int) -> int:
+        """Shares of the key range per tile.  A function of the batch's size class only (never
+        of the context), so that a replayed CUDA graph and an eager step cut alike."""
+        if max_q_len * (nq // nkv) > 16:
+            return 1                                   # portions: enough tiles already
+        b = 1
+        while b < num_requests:
+            b *= 2
+        return max(1, min(16, -(-2 * self.NUM_SMS // (b * nkv))))
+
+    def attention_bf16(self, q, batch, block_table, kv_cache, kv_layer, page_size, out,
+                       nq, nkv, d, scale, window, num_splits=None) -> None:
+        """Flash attention over the paged cache on mma.sync (head sizes 64 and 128)."""
+        T = q.shape[0]
+        splits = num_splits if num_splits is not None else self.attention_splits(
+            batch.num_requests, batch.max_q_len, nq, nkv)
+        ws = None
+        if splits > 1:
+            ws = torch.empty(T * nq * splits * (d + 2), dtype=torch.float32, device=q.device)
+        self._check(self.lib.tff_attention_bf16(
+            _ptr(q), _ptr(batch.q_start), _ptr(batch.pos_start), _ptr(block_table), _c_int(block_table.shape[1]),
+            _ptr(kv_cache), _c_int(kv_cache.shape[1]), _c_int(kv_layer), _c_int(page_size),
+            _ptr(out), _ptr(ws), _c_int(T), _c_int(batch.num_requests), _c_int(batch.max_q_len), _c_int(splits),
+            _c_int(nq), _c_int(nkv), _c_int(d), _c_float(scale), _c_int(window), self._stream()), "attention_bf16")
+        self.launches += 2 if splits > 1 else 1
 
     def attention_generic(self, q, batch, block_table, kv_cache, kv_layer, page_size, out,
                           nq, nkv, d, scale, window) -> None:
