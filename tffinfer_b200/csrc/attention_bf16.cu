@@ -406,3 +406,45 @@ TFF_API int tff_attention_bf16(
     }
     return TFF_OK;
 }
+
+// ------------------------------------------------------- allocation-free variant
+// See no_alloc_api.h for who this is for and for its rules.
+#include "no_alloc_api.h"
+#include <mutex>
+
+namespace {
+// The scratch of the split-key merge, inside the library.  In host code this name is only
+// a stand-in for the symbol, not a device address: the address each GPU gave it is looked
+// up once per device with cudaGetSymbolAddress and that pointer is what kernels receive.
+static __device__ __align__(256) float g_noalloc_scratch[TFF_ATTENTION_NOALLOC_SCRATCH_BYTES / 4];
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {nullptr};
+std::mutex g_noalloc_mu;
+}  // namespace
+
+int tff_attention_bf16_noalloc(
+    const void* q, const int* q_start, const int* pos_start, const int* block_table, int table_width,
+    const void* cache, int cache_layers, int layer, int page_size,
+    void* out, int num_tokens, int num_requests, int max_q_len, int num_splits,
+    int nq, int nkv, int d, float scale, int window, cudaStream_t stream) {
+    if (num_tokens <= 0 || num_requests <= 0) return TFF_OK;
+    if (num_splits < 1 || nq <= 0 || d <= 0) return TFF_ERR_BAD_ARGUMENT;
+    const long long need = tff_attention_bf16_workspace(num_tokens * nq, num_splits, d);
+    if (need > (long long)TFF_ATTENTION_NOALLOC_SCRATCH_BYTES) return TFF_ERR_SCRATCH_TOO_SMALL;
+    float* scratch = nullptr;
+    if (num_splits > 1) {
+        int dev = -1;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return TFF_ERR_LAUNCH;
+        std::lock_guard<std::mutex> g(g_noalloc_mu);
+        if (g_noalloc_ptr[dev] == nullptr) {
+            // set-up, once per device, with that device current
+            void* p = nullptr;
+            if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || p == nullptr) return TFF_ERR_LAUNCH;
+            g_noalloc_ptr[dev] = static_cast<float*>(p);
+        }
+        scratch = g_noalloc_ptr[dev];
+    }
+    return tff_attention_bf16(q, q_start, pos_start, block_table, table_width, cache, cache_layers, layer, page_size,
+                              out, scratch, num_tokens, num_requests, max_q_len, num_splits, nq, nkv, d, scale,
+                              window, stream);
+}
