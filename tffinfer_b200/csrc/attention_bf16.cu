@@ -77,6 +77,8 @@ attn_fwd_kernel(const AttnParams p) {
     uint8_t* sK = sQ + BLOCK_M * D * 2;                          // [2][64][D]
     uint8_t* sV = sK + 2 * BLOCK_N * D * 2;                      // [2][64][D]
 
+    pdl_wait();
+    pdl_launch_dependents();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int b = blockIdx.z, kvh = blockIdx.y;
     // later tiles see more keys: they are issued first
@@ -320,6 +322,8 @@ attn_fwd_kernel(const AttnParams p) {
 template <int D>
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     bf16* __restrict__ out, int num_splits) {
+    pdl_wait();
+    pdl_launch_dependents();
     const size_t row = blockIdx.x;
     float M = -INFINITY;
     for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_ml[(row * num_splits + s) * 2]);
@@ -349,8 +353,7 @@ int launch_attn(const AttnParams& p, int q_tiles, int B, cudaStream_t stream) {
         configured = true;
     }
     dim3 grid(q_tiles * p.num_splits, p.nkv, B);
-    kern<<<grid, NTHREADS, smem, stream>>>(p);
-    return tff_launch_status();
+    return tff_launch_pdl(kern, grid, NTHREADS, smem, stream, p);
 }
 
 }  // namespace
@@ -400,9 +403,10 @@ TFF_API int tff_attention_bf16(
                         : launch_attn<64, false>(p, q_tiles, num_requests, stream);
     if (st != TFF_OK) return st;
     if (num_splits > 1) {
-        if (d == 128) attn_combine_kernel<128><<<(unsigned)rows, 128, 0, stream>>>(p.part_o, p.part_ml, p.out, num_splits);
-        else attn_combine_kernel<64><<<(unsigned)rows, 64, 0, stream>>>(p.part_o, p.part_ml, p.out, num_splits);
-        return tff_launch_status();
+        if (d == 128) return tff_launch_pdl(attn_combine_kernel<128>, (unsigned)rows, 128, 0, stream,
+                                            (const float*)p.part_o, (const float*)p.part_ml, p.out, num_splits);
+        return tff_launch_pdl(attn_combine_kernel<64>, (unsigned)rows, 64, 0, stream,
+                              (const float*)p.part_o, (const float*)p.part_ml, p.out, num_splits);
     }
     return TFF_OK;
 }

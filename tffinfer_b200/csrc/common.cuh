@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define TFF_API extern "C" __attribute__((visibility("default")))
 
@@ -17,6 +18,33 @@ enum TffStatus : int {
 
 static inline int tff_launch_status() {
     return cudaGetLastError() == cudaSuccess ? TFF_OK : TFF_ERR_LAUNCH;
+}
+
+// Programmatic dependent launch.  A kernel launched through tff_launch_pdl may become
+// resident while its predecessor in the stream is still running; it must call pdl_wait()
+// before it writes global memory or reads anything a predecessor wrote (constant inputs
+// such as weights may be fetched earlier), and calls pdl_launch_dependents() once it no
+// longer minds its own successor becoming resident.  TFFINFER_PDL=0 turns the launch
+// attribute off (the device-side calls are then no-ops).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+static inline bool tff_pdl_enabled() {
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("TFFINFER_PDL"); v = (e && e[0] == '0') ? 0 : 1; }
+    return v != 0;
+}
+
+template <typename Kern, typename... Args>
+static inline int tff_launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = tff_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, args...) == cudaSuccess ? TFF_OK : TFF_ERR_LAUNCH;
 }
 
 typedef __nv_bfloat16 bf16;

@@ -9,6 +9,8 @@
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
                              float* __restrict__ out, int hidden, int vocab) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int t = blockIdx.x;
     const int tok = tokens[t];
     float* o = out + (size_t)t * hidden;
@@ -25,9 +27,8 @@ TFF_API int tff_embed(const int* tokens, const void* table, int table_is_bf16, f
     if (num_tokens <= 0) return TFF_OK;
     if (hidden <= 0 || vocab <= 0) return TFF_ERR_BAD_ARGUMENT;
     const int nt = hidden >= 1024 ? 256 : 128;
-    if (table_is_bf16) embed_kernel<bf16><<<num_tokens, nt, 0, stream>>>(tokens, (const bf16*)table, out, hidden, vocab);
-    else embed_kernel<float><<<num_tokens, nt, 0, stream>>>(tokens, (const float*)table, out, hidden, vocab);
-    return tff_launch_status();
+    if (table_is_bf16) return tff_launch_pdl(embed_kernel<bf16>, num_tokens, nt, 0, stream, tokens, (const bf16*)table, out, hidden, vocab);
+    return tff_launch_pdl(embed_kernel<float>, num_tokens, nt, 0, stream, tokens, (const float*)table, out, hidden, vocab);
 }
 
 // ------------------------------------------------------------------ RMSNorm
@@ -38,6 +39,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
                                const int* __restrict__ row_index, TO* __restrict__ out,
                                int dim, float eps) {
     __shared__ float red[32];
+    pdl_wait();
+    pdl_launch_dependents();
     const int r = blockIdx.x;
     const int row = row_index ? row_index[r] : r;
     const float* xr = x + (size_t)row * dim;
@@ -54,13 +57,11 @@ TFF_API int tff_rmsnorm(const float* x, const float* w, const int* row_index, vo
     if (rows <= 0) return TFF_OK;
     if (dim <= 0) return TFF_ERR_BAD_ARGUMENT;
     if (dim >= 1024) {
-        if (out_is_bf16) rmsnorm_kernel<bf16, 256><<<rows, 256, 0, stream>>>(x, w, row_index, (bf16*)out, dim, eps);
-        else rmsnorm_kernel<float, 256><<<rows, 256, 0, stream>>>(x, w, row_index, (float*)out, dim, eps);
-    } else {
-        if (out_is_bf16) rmsnorm_kernel<bf16, 64><<<rows, 64, 0, stream>>>(x, w, row_index, (bf16*)out, dim, eps);
-        else rmsnorm_kernel<float, 64><<<rows, 64, 0, stream>>>(x, w, row_index, (float*)out, dim, eps);
+        if (out_is_bf16) return tff_launch_pdl(rmsnorm_kernel<bf16, 256>, rows, 256, 0, stream, x, w, row_index, (bf16*)out, dim, eps);
+        return tff_launch_pdl(rmsnorm_kernel<float, 256>, rows, 256, 0, stream, x, w, row_index, (float*)out, dim, eps);
     }
-    return tff_launch_status();
+    if (out_is_bf16) return tff_launch_pdl(rmsnorm_kernel<bf16, 64>, rows, 64, 0, stream, x, w, row_index, (bf16*)out, dim, eps);
+    return tff_launch_pdl(rmsnorm_kernel<float, 64>, rows, 64, 0, stream, x, w, row_index, (float*)out, dim, eps);
 }
 
 // ------------------------------------------------------------------- SwiGLU
@@ -68,6 +69,8 @@ TFF_API int tff_rmsnorm(const float* x, const float* w, const int* row_index, vo
 // (src/kernel/cuda/unary.cu:10-27: x1 = gate, x2 = up).
 template <typename TIN, typename T>
 __global__ void swiglu_kernel(const TIN* __restrict__ gu, T* __restrict__ out, long long total, int inter) {
+    pdl_wait();
+    pdl_launch_dependents();
     for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (long long)gridDim.x * blockDim.x) {
         const long long t = idx / inter;
@@ -85,11 +88,10 @@ TFF_API int tff_swiglu(const void* gu, int in_dt, void* out, int out_dt, int row
     const long long total = (long long)rows * inter;
     const int nt = 256;
     const int blocks = (int)((total + nt - 1) / nt < 148 * 16 ? (total + nt - 1) / nt : 148 * 16);
-    if (in_dt == 1 && out_dt == 1) swiglu_kernel<bf16, bf16><<<blocks, nt, 0, stream>>>((const bf16*)gu, (bf16*)out, total, inter);
-    else if (in_dt == 0 && out_dt == 1) swiglu_kernel<float, bf16><<<blocks, nt, 0, stream>>>((const float*)gu, (bf16*)out, total, inter);
-    else if (in_dt == 0 && out_dt == 0) swiglu_kernel<float, float><<<blocks, nt, 0, stream>>>((const float*)gu, (float*)out, total, inter);
-    else return TFF_ERR_BAD_ARGUMENT;
-    return tff_launch_status();
+    if (in_dt == 1 && out_dt == 1) return tff_launch_pdl(swiglu_kernel<bf16, bf16>, blocks, nt, 0, stream, (const bf16*)gu, (bf16*)out, total, inter);
+    if (in_dt == 0 && out_dt == 1) return tff_launch_pdl(swiglu_kernel<float, bf16>, blocks, nt, 0, stream, (const float*)gu, (bf16*)out, total, inter);
+    if (in_dt == 0 && out_dt == 0) return tff_launch_pdl(swiglu_kernel<float, float>, blocks, nt, 0, stream, (const float*)gu, (float*)out, total, inter);
+    return TFF_ERR_BAD_ARGUMENT;
 }
 
 // ------------------------------------------------------------- rotary table
@@ -134,6 +136,8 @@ __global__ void qk_norm_rope_kv_write_kernel(
     const int* __restrict__ block_table, int table_width,
     T* __restrict__ cache, KvLayout L, int layer, int write_cache,
     int nq, int nkv, int d, int max_pos) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.y;
     const int head = blockIdx.x * (blockDim.x >> 5) + warp;
@@ -204,14 +208,13 @@ TFF_API int tff_qk_norm_rope_kv_write(
     const int warps = 4;
     dim3 grid((heads + warps - 1) / warps, num_tokens);
 #define TFF_QK_LAUNCH(TIN, T)                                                                                  \
-    qk_norm_rope_kv_write_kernel<TIN, T><<<grid, warps * 32, 0, stream>>>(                                     \
+    tff_launch_pdl(qk_norm_rope_kv_write_kernel<TIN, T>, grid, warps * 32, 0, stream,                          \
         (const TIN*)qkv, (T*)q_out, q_w, k_w, eps, (const float2*)table, rot_dim, positions, tok_req,          \
         block_table, table_width, (T*)cache, L, layer, write_cache, nq, nkv, d, max_pos)
     if (is_bf16) {
-        if (in_is_f32) TFF_QK_LAUNCH(float, bf16); else TFF_QK_LAUNCH(bf16, bf16);
-    } else {
-        TFF_QK_LAUNCH(float, float);
+        if (in_is_f32) return TFF_QK_LAUNCH(float, bf16);
+        return TFF_QK_LAUNCH(bf16, bf16);
     }
+    return TFF_QK_LAUNCH(float, float);
 #undef TFF_QK_LAUNCH
-    return tff_launch_status();
 }

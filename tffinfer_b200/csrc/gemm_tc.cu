@@ -170,11 +170,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_lane,   // operand whose r
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_acc = *tmem_slot;
+    pdl_launch_dependents();
 
     if (warp == 0) {
         if (lane == 0) {
             // ------------------------------------------------------ TMA producer
-            for (int i = 0; i < num_kb; ++i) {
+            // The weights do not depend on the kernel before this one: the first stages'
+            // weight tiles are requested before waiting for it, the activations after.
+            const CUtensorMap* tm_w = SWAP ? &tm_lane : &tm_col;
+            const CUtensorMap* tm_x = SWAP ? &tm_col : &tm_lane;
+            const int pre = num_kb < STAGES ? num_kb : STAGES;
+            for (int i = 0; i < pre; ++i) {
+                const uint32_t a_dst = base + i * Cfg::kStageBytes;
+                mbar_expect_tx(full_bar(i), Cfg::kStageBytes);
+                tma_load_2d(SWAP ? a_dst : a_dst + BM * BK * 2, tm_w, full_bar(i), (kb_begin + i) * BK,
+                            SWAP ? lane_row0 : col_row0);
+            }
+            pdl_wait();
+            for (int i = 0; i < pre; ++i) {
+                const uint32_t a_dst = base + i * Cfg::kStageBytes;
+                tma_load_2d(SWAP ? a_dst + BM * BK * 2 : a_dst, tm_x, full_bar(i), (kb_begin + i) * BK,
+                            SWAP ? col_row0 : lane_row0);
+            }
+            for (int i = pre; i < num_kb; ++i) {
                 const int s = i % STAGES;
                 const uint32_t round = i / STAGES;
                 if (round > 0 && !mbar_wait(empty_bar(s), (round - 1) & 1, abort_flag)) break;
@@ -213,6 +231,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_lane,   // operand whose r
     } else {
         // ------------------------------------------------------------ epilogue
         const int q = warp & 3;                     // TMEM lane quarter this warp may read
+        pdl_wait();                                 // nothing is written before the kernel ahead has finished
         const bool ok = mbar_wait(tmem_full_bar, 0, abort_flag);
         tc_fence_after();
         if (ok) {
@@ -347,9 +366,8 @@ int launch_tc(const CUtensorMap& tl, const CUtensorMap& tc, void* out, const flo
     const int per = (total_kb + splits - 1) / splits;
     const int real_splits = (total_kb + per - 1) / per;        // no empty split
     dim3 grid((rows_lane + BM - 1) / BM, (rows_col + BN - 1) / BN, real_splits);
-    kern<<<grid, NUM_THREADS, Cfg::kSmemBytes, stream>>>(tl, tc, (TC*)out, residual, rows_lane, rows_col, K, ldo,
-                                                          per, g_error_flag);
-    return tff_launch_status();
+    return tff_launch_pdl(kern, grid, NUM_THREADS, Cfg::kSmemBytes, stream, tl, tc, (TC*)out, residual, rows_lane,
+                          rows_col, K, ldo, per, g_error_flag);
 }
 
 template <int BN, bool SWAP>

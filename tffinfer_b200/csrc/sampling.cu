@@ -17,6 +17,8 @@ __global__ void __launch_bounds__(NT)
 argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab) {
     __shared__ float sval[32];
     __shared__ int sidx[32];
+    pdl_wait();
+    pdl_launch_dependents();
     const float* row = logits + (size_t)blockIdx.x * vocab;
     float best = -INFINITY;
     int bi = 0x7fffffff;
@@ -169,8 +171,7 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
 TFF_API int tff_argmax(const float* logits, int* out, int rows, int vocab, cudaStream_t stream) {
     if (rows <= 0) return TFF_OK;
     if (vocab <= 0) return TFF_ERR_BAD_ARGUMENT;
-    argmax_kernel<<<rows, NT, 0, stream>>>(logits, out, vocab);
-    return tff_launch_status();
+    return tff_launch_pdl(argmax_kernel, rows, NT, 0, stream, logits, out, vocab);
 }
 
 // temperature[r] <= 0 selects greedy for that row.  top_k / top_p / min_p may be null.
