@@ -130,11 +130,15 @@ def test_gemm_tc_all_epilogues(ops, M, N, K):
     ops.check_errors()
 
 
-@pytest.mark.parametrize("M,N,K,swap,bn,splits", [(8, 512, 4096, 1, 16, 4), (8, 512, 4096, 1, 16, 7),
-                                                  (40, 1000, 1000 // 8 * 8, 1, 64, 3), (64, 4096, 12288, 1, 64, 4),
-                                                  (200, 300, 512, 1, 256, 2), (200, 300, 512, 0, 128, 1),
-                                                  (200, 300, 512, 0, 256, 1), (16, 128, 64, 1, 32, 1)])
+@pytest.mark.parametrize("M,N,K,swap,bn,splits", [(8, 512, 4096, 1, 16, 1), (8, 512, 4096, 1, 16, 0),
+                                                  (40, 1000, 1000 // 8 * 8, 1, 64, 1), (64, 4096, 12288, 1, 64, 1),
+                                                  (200, 300, 512, 1, 256, 1), (200, 300, 512, 0, 128, 0),
+                                                  (200, 300, 512, 0, 256, 0), (16, 128, 64, 1, 32, 0),
+                                                  (1, 24576, 4096, 1, 16, 1), (3, 40000, 256, 1, 16, 1),
+                                                  (700, 1030, 520, 0, 128, 0), (700, 1030, 520, 0, 256, 0),
+                                                  (130, 24576, 128, 0, 256, 0), (128, 64, 4096, 1, 128, 1)])
 def test_gemm_tc_explicit_plans(ops, M, N, K, swap, bn, splits):
+    """splits: 1 = stream-K shares with float32 adds, 0 = whole tiles"""
     a, w = g((M, K), torch.bfloat16, 13), g((N, K), torch.bfloat16, 14, 0.05)
     ref = a.double() @ w.double().t()
     res = g((M, N), torch.float32, 15)

@@ -1,26 +1,32 @@
 // bfloat16 matrix product on the 5th-generation tensor cores:
 //   out[M, N] = A[M, K] * W[N, K]^T  (+ residual), float32 accumulation in tensor memory.
 //
-// One CTA computes one 128 x BN tile of accumulators.  Both operands are K-major
-// ([rows, K] row-major), brought to shared memory by TMA in 128-byte-swizzled tiles
-// of 64 K-elements, multiplied by tcgen05.mma (M = 128, N = BN, K = 16) issued by one
-// thread, accumulated in TMEM and read back with tcgen05.ld by four epilogue warps.
+// A persistent kernel: each CTA walks a list of segments, a segment being a range of
+// 64-element K blocks of one 128 x BN accumulator tile.  Both operands are K-major
+// ([rows, K] row-major) and come to shared memory by TMA in 128-byte-swizzled tiles;
+// tcgen05.mma (M = 128, N = BN, K = 16), issued by one thread, accumulates in TMEM; two
+// accumulator buffers alternate, so the epilogue of one segment overlaps the mainloop of
+// the next.
 //   warp 0      TMA producer       (one lane)
 //   warp 1      TMEM allocation, MMA issue (one lane), TMEM release
-//   warps 2-5   epilogue: TMEM -> registers -> global memory
+//   warps 2-5   epilogue: TMEM -> registers -> (shared memory -> TMA store | global memory)
 // Two orientations share the kernel:
-//   normal   the 128-row operand is the activations (M on TMEM lanes), the BN-row
-//            operand the weights; used when M is large (prompt portions);
-//   swapped  the 128-row operand is the weights (N on TMEM lanes), the BN-row operand
-//            the activations, BN = M rounded up to 16; used for decode-sized M, where
-//            the product is a stream of the weights through the SMs.  The K range may
-//            be split over blockIdx.z, the partial sums then meet in float32 atomics.
+//   normal   the 128-row operand is the activations (M on TMEM lanes), the BN-row operand
+//            the weights; for prompt portions.  Tiles go round-robin over the CTAs, rows of
+//            tiles fastest, so that CTAs running together share a weight tile in L2.  The
+//            epilogue stages 32-row slabs in swizzled shared memory and writes them with
+//            TMA stores (TMA float32 add-reductions when the product is added to ``out``).
+//   swapped  the 128-row operand is the weights (N on TMEM lanes), the BN-row operand the
+//            activations, BN = M rounded up to 16; for decode-sized M, where the product is
+//            one pass of the weights through the SMs.  With few tiles the (tile, K block)
+//            units are dealt to the CTAs in equal contiguous shares ("stream-K"), every CTA
+//            streaming the same number of bytes; partial tiles meet in float32 atomics.
 // It replaces the reference's int8 dp4a product (src/kernel/cuda/quant/quant_q_8_0_mat_mul.cu:338-447)
 // and its unfinished dense product (src/kernel/cuda/mat_mul.cu:151-660) on the serving path.
 //
-// Every wait on an mbarrier is bounded; when one runs out the CTA raises a flag in
-// global memory, stops issuing work, lets its copies in flight land, frees its
-// tensor memory and returns.
+// Every wait on an mbarrier is bounded; when one runs out the CTA raises a flag in global
+// memory, stops issuing work, lets its copies in flight land, frees its tensor memory and
+// returns.
 #include "common.cuh"
 #include <cuda.h>
 #include <mutex>
@@ -34,7 +40,7 @@ constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
-enum Epilogue : int { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_ATOMIC = 2 };
+enum Epilogue : int { EPI_STORE = 0, EPI_ADD = 1 };   // write the product | add it to what ``out`` holds
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -44,6 +50,9 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
@@ -71,6 +80,20 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm,
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(tm), "r"(bar), "r"(x), "r"(y) : "memory");
 }
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tm, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(tm), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* tm, uint32_t src, int x, int y) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(tm), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -121,157 +144,261 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
          | ((uint32_t)(m >> 4) << 24);                // m_dim
 }
 
-template <int BN> struct TileCfg {
+template <int BN, bool TMA_OUT> struct TileCfg {
     static constexpr int kStageBytes = BM * BK * 2 + BN * BK * 2;
-    static constexpr int kStages = BN >= 256 ? 4 : BN >= 128 ? 6 : (BN >= 64 ? 4 : 5);
+    static constexpr int kStages = BN >= 256 ? 4 : BN >= 128 ? 5 : (BN >= 64 ? 4 : 5);
     static constexpr int kCtasPerSm = BN >= 128 ? 1 : 2;
-    static constexpr int kTmemCols = BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256;
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int kAccCols = BN < 32 ? 32 : BN;              // columns of one accumulator buffer
+    static constexpr int kTmemCols = 2 * kAccCols;                  // 64 .. 512, a power of two
+    static constexpr int kStagingBytes = TMA_OUT ? 4 * 2 * 4096 : 0;   // 4 warps x 2 buffers x (32 rows x 128 B)
+    static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+// The segments of one CTA.  tiles mode: whole tiles c, c+G, c+2G, ...; stream-K mode: the
+// contiguous share [c*U/G, (c+1)*U/G) of the U = tiles * kb_per_tile (tile, K block) units.
+struct SegIter {
+    int kbt, stream_k, n_tiles, stride;
+    long long u, u_end;
+    int tile, kb0, kb1;
+    __device__ SegIter(int n_tiles_, int kbt_, int stream_k_, int cta, int n_ctas)
+        : kbt(kbt_), stream_k(stream_k_), n_tiles(n_tiles_), stride(n_ctas) {
+        if (stream_k) {
+            const long long U = (long long)n_tiles * kbt;
+            u = U * cta / n_ctas;
+            u_end = U * (cta + 1) / n_ctas;
+        } else {
+            u = cta;
+            u_end = n_tiles;
+        }
+    }
+    __device__ bool next() {
+        if (u >= u_end) return false;
+        if (stream_k) {
+            tile = (int)(u / kbt);
+            kb0 = (int)(u % kbt);
+            const long long left = u_end - u;
+            kb1 = (long long)(kbt - kb0) < left ? kbt : kb0 + (int)left;
+            u += kb1 - kb0;
+        } else {
+            tile = (int)u; kb0 = 0; kb1 = kbt;
+            u += stride;
+        }
+        return true;
+    }
 };
 
 // out element (m, n): normal -> lane operand row = m, column operand row = n; swapped -> the reverse.
-template <int BN, bool SWAP, int EPI, typename TC>
-__global__ void __launch_bounds__(NUM_THREADS, TileCfg<BN>::kCtasPerSm)
+// TMA_OUT (normal orientation only): the epilogue goes through shared memory and TMA.
+template <int BN, bool SWAP, int EPI, typename TC, bool TMA_OUT>
+__global__ void __launch_bounds__(NUM_THREADS, TileCfg<BN, TMA_OUT>::kCtasPerSm)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_lane,   // operand whose rows land on TMEM lanes (box 64 x 128)
                const __grid_constant__ CUtensorMap tm_col,    // operand whose rows land on TMEM columns (box 64 x BN)
-               TC* __restrict__ out, const float* residual,
-               int rows_lane, int rows_col, int K, int ldo, int kblocks_per_split, int* error_flag) {
-    using Cfg = TileCfg<BN>;
+               const __grid_constant__ CUtensorMap tm_out,    // output, boxes of 128 bytes x 32 rows (TMA_OUT only)
+               TC* __restrict__ out, int rows_lane, int rows_col, int K, int ldo, int stream_k, int* error_flag) {
+    using Cfg = TileCfg<BN, TMA_OUT>;
     constexpr int STAGES = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
-    const uint32_t bars = base + STAGES * Cfg::kStageBytes;           // 8-byte aligned
-    // barrier layout: full[STAGES], empty[STAGES], tmem_full, then the TMEM address word and the abort flag
+    const uint32_t staging = base + STAGES * Cfg::kStageBytes;          // 1024-aligned (stage sizes are multiples of 1024)
+    const uint32_t bars = staging + Cfg::kStagingBytes;
+    // barriers: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]; then the TMEM address word and the abort flag
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
-    const uint32_t tmem_full_bar = bars + 8u * (2 * STAGES);
-    volatile uint32_t* tmem_slot = (volatile uint32_t*)(gen_base + STAGES * Cfg::kStageBytes + 8 * (2 * STAGES + 1));
+    auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
+    auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
+    volatile uint32_t* tmem_slot =
+        (volatile uint32_t*)(gen_base + STAGES * Cfg::kStageBytes + Cfg::kStagingBytes + 8 * (2 * STAGES + 4));
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int lane_row0 = blockIdx.x * BM;
-    const int col_row0 = blockIdx.y * BN;
-    const int total_kb = (K + BK - 1) / BK;
-    const int kb_begin = blockIdx.z * kblocks_per_split;
-    const int kb_end = min(total_kb, kb_begin + kblocks_per_split);
-    const int num_kb = kb_end - kb_begin;                   // >= 1 by construction of the grid
+    const int kbt = (K + BK - 1) / BK;
+    const int n_lane_tiles = (rows_lane + BM - 1) / BM;
+    const int n_col_tiles = (rows_col + BN - 1) / BN;
+    const int n_tiles = n_lane_tiles * n_col_tiles;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        mbar_init(tmem_full_bar, 1);
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_lane) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_col) : "memory");
+        if (TMA_OUT) asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_out) : "memory");
     }
     if (warp == 1) tmem_alloc(smem_u32((const void*)tmem_slot), Cfg::kTmemCols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_acc = *tmem_slot;
+    const uint32_t tmem_base = *tmem_slot;
     pdl_launch_dependents();
 
     if (warp == 0) {
         if (lane == 0) {
             // ------------------------------------------------------ TMA producer
-            // The weights do not depend on the kernel before this one: the first stages'
-            // weight tiles are requested before waiting for it, the activations after.
+            // The weights do not depend on the kernel before this one: the weight tiles of
+            // the first ring of stages are requested before waiting for it, the activations
+            // after.
             const CUtensorMap* tm_w = SWAP ? &tm_lane : &tm_col;
             const CUtensorMap* tm_x = SWAP ? &tm_col : &tm_lane;
-            const int pre = num_kb < STAGES ? num_kb : STAGES;
+            const uint32_t w_off = SWAP ? 0u : (uint32_t)(BM * BK * 2);
+            const uint32_t x_off = SWAP ? (uint32_t)(BM * BK * 2) : 0u;
+            int pre_k[STAGES], pre_wrow[STAGES], pre_xrow[STAGES];
+            int pre = 0;
+            {
+                SegIter it(n_tiles, kbt, stream_k, blockIdx.x, gridDim.x);
+                while (pre < STAGES && it.next()) {
+                    const int lrow = (it.tile % n_lane_tiles) * BM, crow = (it.tile / n_lane_tiles) * BN;
+                    for (int kb = it.kb0; kb < it.kb1 && pre < STAGES; ++kb, ++pre) {
+                        pre_k[pre] = kb * BK;
+                        pre_wrow[pre] = SWAP ? lrow : crow;
+                        pre_xrow[pre] = SWAP ? crow : lrow;
+                    }
+                }
+            }
             for (int i = 0; i < pre; ++i) {
-                const uint32_t a_dst = base + i * Cfg::kStageBytes;
                 mbar_expect_tx(full_bar(i), Cfg::kStageBytes);
-                tma_load_2d(SWAP ? a_dst : a_dst + BM * BK * 2, tm_w, full_bar(i), (kb_begin + i) * BK,
-                            SWAP ? lane_row0 : col_row0);
+                tma_load_2d(base + i * Cfg::kStageBytes + w_off, tm_w, full_bar(i), pre_k[i], pre_wrow[i]);
             }
             pdl_wait();
-            for (int i = 0; i < pre; ++i) {
-                const uint32_t a_dst = base + i * Cfg::kStageBytes;
-                tma_load_2d(SWAP ? a_dst + BM * BK * 2 : a_dst, tm_x, full_bar(i), (kb_begin + i) * BK,
-                            SWAP ? col_row0 : lane_row0);
-            }
-            for (int i = pre; i < num_kb; ++i) {
-                const int s = i % STAGES;
-                const uint32_t round = i / STAGES;
-                if (round > 0 && !mbar_wait(empty_bar(s), (round - 1) & 1, abort_flag)) break;
-                const uint32_t a_dst = base + s * Cfg::kStageBytes;
-                const uint32_t b_dst = a_dst + BM * BK * 2;
-                mbar_expect_tx(full_bar(s), Cfg::kStageBytes);
-                const int k = (kb_begin + i) * BK;
-                tma_load_2d(a_dst, &tm_lane, full_bar(s), k, lane_row0);
-                tma_load_2d(b_dst, &tm_col, full_bar(s), k, col_row0);
+            for (int i = 0; i < pre; ++i)
+                tma_load_2d(base + i * Cfg::kStageBytes + x_off, tm_x, full_bar(i), pre_k[i], pre_xrow[i]);
+            SegIter it(n_tiles, kbt, stream_k, blockIdx.x, gridDim.x);
+            uint32_t n = 0;
+            bool ok = true;
+            while (ok && it.next()) {
+                const int lrow = (it.tile % n_lane_tiles) * BM, crow = (it.tile / n_lane_tiles) * BN;
+                for (int kb = it.kb0; kb < it.kb1; ++kb, ++n) {
+                    if (n < (uint32_t)pre) continue;                 // already requested above
+                    const int s = n % STAGES;
+                    const uint32_t round = n / STAGES;
+                    if (!mbar_wait(empty_bar(s), (round - 1) & 1, abort_flag)) { ok = false; break; }
+                    const uint32_t a_dst = base + s * Cfg::kStageBytes;
+                    mbar_expect_tx(full_bar(s), Cfg::kStageBytes);
+                    tma_load_2d(a_dst, &tm_lane, full_bar(s), kb * BK, lrow);
+                    tma_load_2d(a_dst + BM * BK * 2, &tm_col, full_bar(s), kb * BK, crow);
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             // -------------------------------------------------------- MMA issuer
             constexpr uint32_t idesc = make_idesc(BM, BN);
+            SegIter it(n_tiles, kbt, stream_k, blockIdx.x, gridDim.x);
+            uint32_t n = 0, seg = 0;
             bool ok = true;
-            for (int i = 0; i < num_kb && ok; ++i) {
-                const int s = i % STAGES;
-                const uint32_t round = i / STAGES;
-                ok = mbar_wait(full_bar(s), round & 1, abort_flag);
-                if (!ok) break;
+            while (ok && it.next()) {
+                const uint32_t acc = seg & 1, use = seg >> 1;
+                if (use > 0 && !mbar_wait(tempty_bar(acc), (use - 1) & 1, abort_flag)) break;   // epilogue has drained it
                 tc_fence_after();
-                const uint32_t a_addr = base + s * Cfg::kStageBytes;
-                const uint64_t adesc = make_smem_desc(a_addr);
-                const uint64_t bdesc = make_smem_desc(a_addr + BM * BK * 2);
+                const uint32_t d_tmem = tmem_base + acc * Cfg::kAccCols;
+                for (int kb = it.kb0; kb < it.kb1; ++kb, ++n) {
+                    const int s = n % STAGES;
+                    const uint32_t round = n / STAGES;
+                    if (!mbar_wait(full_bar(s), round & 1, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = base + s * Cfg::kStageBytes;
+                    const uint64_t adesc = make_smem_desc(a_addr);
+                    const uint64_t bdesc = make_smem_desc(a_addr + BM * BK * 2);
 #pragma unroll
-                for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-                    // 16 K-elements = 32 bytes = 2 descriptor units further along the swizzled row
-                    umma_bf16(tmem_acc, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc,
-                              (i > 0 || kk > 0) ? 1u : 0u);
+                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                        // 16 K-elements = 32 bytes = 2 descriptor units further along the swizzled row
+                        umma_bf16(d_tmem, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc,
+                                  (kb > it.kb0 || kk > 0) ? 1u : 0u);
+                    }
+                    umma_commit(empty_bar(s));          // the stage is free once these MMAs have read it
                 }
-                umma_commit(empty_bar(s));          // the stage is free once these MMAs have read it
+                if (ok) umma_commit(tfull_bar(acc));    // this segment's accumulators are complete
+                ++seg;
             }
-            if (ok) umma_commit(tmem_full_bar);     // accumulators complete
         }
     } else {
         // ------------------------------------------------------------ epilogue
         const int q = warp & 3;                     // TMEM lane quarter this warp may read
         pdl_wait();                                 // nothing is written before the kernel ahead has finished
-        const bool ok = mbar_wait(tmem_full_bar, 0, abort_flag);
-        tc_fence_after();
-        if (ok) {
-            const int lr = lane_row0 + q * 32 + lane;          // row of the lane operand
+        SegIter it(n_tiles, kbt, stream_k, blockIdx.x, gridDim.x);
+        uint32_t seg = 0, chunk_no = 0;
+        while (it.next()) {
+            const uint32_t acc = seg & 1, use = seg >> 1;
+            if (!mbar_wait(tfull_bar(acc), use & 1, abort_flag)) break;
+            tc_fence_after();
+            const int lane_row0 = (it.tile % n_lane_tiles) * BM, col_row0 = (it.tile / n_lane_tiles) * BN;
+            const uint32_t t_addr = tmem_base + acc * Cfg::kAccCols + ((uint32_t)(q * 32) << 16);
+            const bool partial = stream_k && (it.kb1 - it.kb0) < kbt;   // a share of the tile's K range: add
+            if constexpr (TMA_OUT) {
+                // 128-byte-wide column chunks: 32 float32 or 64 bfloat16 per row
+                constexpr int CW = 128 / (int)sizeof(TC);
+                const uint32_t my_stage = staging + (uint32_t)((warp - 2) * 2) * 4096u;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                uint32_t v[16];
-                tmem_ld16(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
-                tmem_ld_wait();
-                if (lr >= rows_lane) continue;
-                if constexpr (!SWAP) {
-                    // thread owns out[lr, col_row0 + c0 .. +16)
-                    const int n0 = col_row0 + c0;
-                    TC* o = out + (size_t)lr * ldo + n0;
-                    const float* r = (EPI == EPI_RESIDUAL) ? residual + (size_t)lr * ldo + n0 : nullptr;
+                for (int c0 = 0; c0 < BN; c0 += CW, ++chunk_no) {
+                    const uint32_t buf = my_stage + (chunk_no & 1) * 4096u;
+                    if (chunk_no >= 2) {                       // the store that last used this buffer has read it
+                        if (lane == 0) bulk_wait_read<1>();
+                        __syncwarp();
+                    }
+                    uint32_t packed[32];                       // this thread's row: 128 bytes
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        if (n0 + j < rows_col) {
-                            float x = __uint_as_float(v[j]);
-                            if constexpr (EPI == EPI_RESIDUAL) x = r[j] + x;
-                            if constexpr (EPI == EPI_ATOMIC) atomicAdd((float*)&o[j], x);
-                            else o[j] = from_f32<TC>(x);
+                    for (int h = 0; h < CW / 16; ++h) {
+                        uint32_t v[16];
+                        tmem_ld16(t_addr + (uint32_t)(c0 + h * 16), v);
+                        tmem_ld_wait();
+                        if constexpr (sizeof(TC) == 4) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) packed[h * 16 + j] = v[j];
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+                                packed[h * 8 + j] = *reinterpret_cast<uint32_t*>(&b2);
+                            }
                         }
                     }
-                } else {
-                    // thread owns out[col_row0 + c0 .. +16, lr]: a warp writes 32 consecutive n
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {              // 16-byte chunk c of row ``lane`` at chunk c ^ (lane % 8)
+                        const uint32_t dst = buf + (uint32_t)lane * 128u + (uint32_t)((c ^ (lane & 7)) << 4);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[4 * c]),
+                                     "r"(packed[4 * c + 1]), "r"(packed[4 * c + 2]), "r"(packed[4 * c + 3]) : "memory");
+                    }
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (EPI == EPI_ADD || partial) tma_reduce_add_2d(&tm_out, buf, col_row0 + c0, lane_row0 + q * 32);
+                        else tma_store_2d(&tm_out, buf, col_row0 + c0, lane_row0 + q * 32);
+                        bulk_commit();
+                    }
+                }
+            } else {
+                const int lr = lane_row0 + q * 32 + lane;          // row of the lane operand
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    uint32_t v[16];
+                    tmem_ld16(t_addr + (uint32_t)c0, v);
+                    tmem_ld_wait();
+                    if (lr >= rows_lane) continue;
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        const int m = col_row0 + c0 + j;
-                        if (m < rows_col) {
-                            float x = __uint_as_float(v[j]);
-                            const size_t idx = (size_t)m * ldo + lr;
-                            if constexpr (EPI == EPI_RESIDUAL) x = residual[idx] + x;
-                            if constexpr (EPI == EPI_ATOMIC) atomicAdd((float*)&out[idx], x);
-                            else out[idx] = from_f32<TC>(x);
+                        const int cr = col_row0 + c0 + j;
+                        if (cr < rows_col) {
+                            const float x = __uint_as_float(v[j]);
+                            // normal: out[lr, cr]; swapped: out[cr, lr] (a warp then writes 32 consecutive n)
+                            const size_t idx = SWAP ? (size_t)cr * ldo + lr : (size_t)lr * ldo + cr;
+                            if constexpr (sizeof(TC) == 4) {
+                                if (EPI == EPI_ADD || partial) atomicAdd(reinterpret_cast<float*>(&out[idx]), x);
+                                else out[idx] = from_f32<TC>(x);
+                            } else {
+                                out[idx] = from_f32<TC>(x);
+                            }
                         }
                     }
                 }
             }
+            // the accumulator buffer may be overwritten
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(acc));
+            ++seg;
         }
+        if (TMA_OUT && lane == 0) bulk_wait_read<0>();       // staged rows must have been read before the CTA leaves
     }
     // ------------------------------------------------------------------ teardown
     tc_fence_before();
@@ -283,8 +410,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_lane,   // operand whose r
         __syncthreads();
     }
     if (warp == 1) {
+        __syncwarp();
         tc_fence_after();
-        tmem_dealloc(tmem_acc, Cfg::kTmemCols);
+        tmem_dealloc(tmem_base, Cfg::kTmemCols);
     }
 }
 
@@ -307,23 +435,26 @@ EncodeTiledFn get_encode_fn() {
 }
 
 struct MapKey {
-    const void* ptr; int rows; int K; int box_rows;
-    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && K == o.K && box_rows == o.box_rows; }
+    const void* ptr; int rows; int cols; int box_rows; int box_cols; int elt;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows && box_cols == o.box_cols && elt == o.elt;
+    }
 };
 struct MapKeyHash {
     size_t operator()(const MapKey& k) const {
         size_t h = (size_t)k.ptr;
-        h ^= (size_t)k.rows * 0x9E3779B97F4A7C15ull; h ^= (size_t)k.K * 0xC2B2AE3D27D4EB4Full; h ^= (size_t)k.box_rows << 48;
+        h ^= (size_t)k.rows * 0x9E3779B97F4A7C15ull; h ^= (size_t)k.cols * 0xC2B2AE3D27D4EB4Full;
+        h ^= ((size_t)k.box_rows << 48) ^ ((size_t)k.box_cols << 40) ^ ((size_t)k.elt << 36);
         return h;
     }
 };
 
-// Tensor map of a row-major bf16 matrix [rows, K]: boxes of 64 K-elements x box_rows rows,
-// 128-byte swizzle, zero fill outside the matrix.
-bool get_tensor_map(const void* ptr, int rows, int K, int box_rows, CUtensorMap* out) {
+// Tensor map of a row-major matrix [rows, cols] of 2-byte (bf16) or 4-byte (float32) elements:
+// boxes of box_cols x box_rows with 128-byte swizzle (box_cols * elt = 128), zero fill outside.
+bool get_tensor_map(const void* ptr, int rows, int cols, int box_rows, int box_cols, int elt, CUtensorMap* out) {
     static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
     static std::mutex mu;
-    const MapKey key{ptr, rows, K, box_rows};
+    const MapKey key{ptr, rows, cols, box_rows, box_cols, elt};
     {
         std::lock_guard<std::mutex> g(mu);
         auto it = cache.find(key);
@@ -331,13 +462,14 @@ bool get_tensor_map(const void* ptr, int rows, int K, int box_rows, CUtensorMap*
     }
     EncodeTiledFn enc = get_encode_fn();
     if (!enc) return false;
-    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * elt};
+    const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     CUtensorMap m;
-    if (enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+    if (enc(&m, elt == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+            const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return false;
     {
@@ -350,39 +482,36 @@ bool get_tensor_map(const void* ptr, int rows, int K, int box_rows, CUtensorMap*
 }
 
 int* g_error_flag = nullptr;
+int g_num_sms = 0;
 
-template <int BN, bool SWAP, int EPI, typename TC>
-int launch_tc(const CUtensorMap& tl, const CUtensorMap& tc, void* out, const float* residual,
-              int rows_lane, int rows_col, int K, int ldo, int splits, cudaStream_t stream) {
-    using Cfg = TileCfg<BN>;
-    auto kern = gemm_tc_kernel<BN, SWAP, EPI, TC>;
+template <int BN, bool SWAP, int EPI, typename TC, bool TMA_OUT>
+int launch_tc(const CUtensorMap& tl, const CUtensorMap& tc, const CUtensorMap& to, void* out,
+              int rows_lane, int rows_col, int K, int ldo, int stream_k, cudaStream_t stream) {
+    using Cfg = TileCfg<BN, TMA_OUT>;
+    auto kern = gemm_tc_kernel<BN, SWAP, EPI, TC, TMA_OUT>;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
             return TFF_ERR_LAUNCH;
         configured = true;
     }
-    const int total_kb = (K + BK - 1) / BK;
-    const int per = (total_kb + splits - 1) / splits;
-    const int real_splits = (total_kb + per - 1) / per;        // no empty split
-    dim3 grid((rows_lane + BM - 1) / BM, (rows_col + BN - 1) / BN, real_splits);
-    return tff_launch_pdl(kern, grid, NUM_THREADS, Cfg::kSmemBytes, stream, tl, tc, (TC*)out, residual, rows_lane,
-                          rows_col, K, ldo, per, g_error_flag);
+    const long long n_tiles = (long long)((rows_lane + BM - 1) / BM) * ((rows_col + BN - 1) / BN);
+    const long long units = stream_k ? n_tiles * ((K + BK - 1) / BK) : n_tiles;
+    long long ctas = (long long)g_num_sms * Cfg::kCtasPerSm;
+    if (ctas > units) ctas = units;
+    return tff_launch_pdl(kern, dim3((unsigned)ctas), dim3(NUM_THREADS), (size_t)Cfg::kSmemBytes, stream, tl, tc, to,
+                          (TC*)out, rows_lane, rows_col, K, ldo, stream_k, g_error_flag);
 }
 
-template <int BN, bool SWAP>
-int dispatch_epi(const CUtensorMap& tl, const CUtensorMap& tc, void* out, int out_is_bf16, const float* residual,
-                 int atomic, int rows_lane, int rows_col, int K, int ldo, int splits, cudaStream_t s) {
-    if (atomic) {
-        if (out_is_bf16) return TFF_ERR_BAD_ARGUMENT;
-        return launch_tc<BN, SWAP, EPI_ATOMIC, float>(tl, tc, out, nullptr, rows_lane, rows_col, K, ldo, splits, s);
+template <int BN, bool SWAP, bool TMA_OUT>
+int dispatch_epi(const CUtensorMap& tl, const CUtensorMap& tc, const CUtensorMap& to, void* out, int out_is_bf16,
+                 int add, int rows_lane, int rows_col, int K, int ldo, int stream_k, cudaStream_t s) {
+    if (out_is_bf16) {
+        if (add || stream_k) return TFF_ERR_BAD_ARGUMENT;
+        return launch_tc<BN, SWAP, EPI_STORE, bf16, TMA_OUT>(tl, tc, to, out, rows_lane, rows_col, K, ldo, 0, s);
     }
-    if (residual) {
-        if (out_is_bf16) return TFF_ERR_BAD_ARGUMENT;
-        return launch_tc<BN, SWAP, EPI_RESIDUAL, float>(tl, tc, out, residual, rows_lane, rows_col, K, ldo, 1, s);
-    }
-    if (out_is_bf16) return launch_tc<BN, SWAP, EPI_STORE, bf16>(tl, tc, out, nullptr, rows_lane, rows_col, K, ldo, 1, s);
-    return launch_tc<BN, SWAP, EPI_STORE, float>(tl, tc, out, nullptr, rows_lane, rows_col, K, ldo, 1, s);
+    if (add) return launch_tc<BN, SWAP, EPI_ADD, float, TMA_OUT>(tl, tc, to, out, rows_lane, rows_col, K, ldo, stream_k, s);
+    return launch_tc<BN, SWAP, EPI_STORE, float, TMA_OUT>(tl, tc, to, out, rows_lane, rows_col, K, ldo, stream_k, s);
 }
 
 }  // namespace
@@ -391,6 +520,10 @@ int dispatch_epi(const CUtensorMap& tl, const CUtensorMap& tc, void* out, int ou
 TFF_API int tff_gemm_tc_init() {
     if (g_error_flag) return TFF_OK;
     if (!get_encode_fn()) return TFF_ERR_DRIVER;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return TFF_ERR_LAUNCH;
+    if (cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || g_num_sms <= 0)
+        return TFF_ERR_LAUNCH;
     if (cudaMalloc(&g_error_flag, sizeof(int)) != cudaSuccess) return TFF_ERR_LAUNCH;
     if (cudaMemset(g_error_flag, 0, sizeof(int)) != cudaSuccess) return TFF_ERR_LAUNCH;
     return TFF_OK;
@@ -407,28 +540,35 @@ TFF_API int tff_gemm_tc_error() {
 }
 
 // out[M, N] (+)= A[M, K] * W[N, K]^T; A, W bfloat16.
-//   swap    0: A rows on TMEM lanes (tiles 128 x bn over M x N); 1: W rows on lanes (tiles 128 x bn over N x M)
-//   bn      16, 32, 64, 128 or 256
-//   splits  number of K ranges (> 1 only with atomic = 1)
-//   atomic  1: float32 atomic adds into ``out`` (which the caller has initialised); residual must be null
-//   residual float32 [M, N] added to the product (may alias ``out``); out must be float32
-TFF_API int tff_gemm_tc(const void* A, const void* W, void* out, int out_is_bf16, const float* residual,
-                        int M, int N, int K, int swap, int bn, int splits, int atomic, cudaStream_t stream) {
+//   swap      0: A rows on TMEM lanes (tiles 128 x bn over M x N); 1: W rows on lanes (tiles 128 x bn over N x M)
+//   bn        16, 32, 64, 128 or 256
+//   add       1: the product is added to what ``out`` (float32) holds -- a residual stream in place
+//   stream_k  1: (tile, K block) units are dealt in equal shares; tiles that are split between CTAs
+//             are accumulated with float32 adds, so ``out`` (float32) must hold the initial value
+//             (zero, or the residual with add = 1) before the call
+TFF_API int tff_gemm_tc(const void* A, const void* W, void* out, int out_is_bf16, int add,
+                        int M, int N, int K, int swap, int bn, int stream_k, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return TFF_OK;
-    if (K <= 0 || splits < 1 || (splits > 1 && !atomic) || (atomic && residual)) return TFF_ERR_BAD_ARGUMENT;
+    if (K <= 0 || ((add || stream_k) && out_is_bf16)) return TFF_ERR_BAD_ARGUMENT;
     if (K % 8 != 0) return TFF_ERR_UNSUPPORTED;                         // TMA row pitch must be a multiple of 16 bytes
     if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return TFF_ERR_UNSUPPORTED;
     if (!g_error_flag) { const int st = tff_gemm_tc_init(); if (st != TFF_OK) return st; }
     const void* lane_ptr = swap ? W : A;
     const void* col_ptr = swap ? A : W;
     const int rows_lane = swap ? N : M, rows_col = swap ? M : N;
-    CUtensorMap tl, tc;
-    if (!get_tensor_map(lane_ptr, rows_lane, K, BM, &tl)) return TFF_ERR_DRIVER;
-    if (!get_tensor_map(col_ptr, rows_col, K, bn, &tc)) return TFF_ERR_DRIVER;
+    CUtensorMap tl, tc, to;
+    if (!get_tensor_map(lane_ptr, rows_lane, K, BM, BK, 2, &tl)) return TFF_ERR_DRIVER;
+    if (!get_tensor_map(col_ptr, rows_col, K, bn, BK, 2, &tc)) return TFF_ERR_DRIVER;
+    // TMA output: normal orientation, row pitch a multiple of 16 bytes, 16-byte aligned base
+    const int elt = out_is_bf16 ? 2 : 4;
+    const bool tma_out = !swap && ((long long)N * elt) % 16 == 0 && ((uintptr_t)out & 15) == 0 && bn >= 128 / elt;
+    to = tl;
+    if (tma_out && !get_tensor_map(out, M, N, 32, 128 / elt, elt, &to)) return TFF_ERR_DRIVER;
 #define TFF_CASE(BN_)                                                                                              \
     case BN_:                                                                                                      \
-        return swap ? dispatch_epi<BN_, true>(tl, tc, out, out_is_bf16, residual, atomic, rows_lane, rows_col, K, N, splits, stream) \
-                    : dispatch_epi<BN_, false>(tl, tc, out, out_is_bf16, residual, atomic, rows_lane, rows_col, K, N, splits, stream);
+        if (swap) return dispatch_epi<BN_, true, false>(tl, tc, to, out, out_is_bf16, add, rows_lane, rows_col, K, N, stream_k, stream); \
+        if (tma_out) return dispatch_epi<BN_, false, true>(tl, tc, to, out, out_is_bf16, add, rows_lane, rows_col, K, N, stream_k, stream); \
+        return dispatch_epi<BN_, false, false>(tl, tc, to, out, out_is_bf16, add, rows_lane, rows_col, K, N, stream_k, stream);
     switch (bn) {
         TFF_CASE(16)
         TFF_CASE(32)

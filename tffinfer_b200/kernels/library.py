@@ -134,37 +134,33 @@ class CudaKernels:
     NUM_SMS = 148
 
     def tc_plan(self, M: int, N: int, K: int, out_is_f32: bool):
-        """(swap, bn, splits) of the tcgen05 product for a shape."""
+        """(swap, bn, stream_k) of the tcgen05 product for a shape."""
         if M <= self.SWAP_MAX_M:
             bn = 16
             while bn < M:
                 bn *= 2
-            splits = 1
             tiles = -(-N // 128)
-            kb = -(-K // 64)
-            if out_is_f32 and tiles < self.NUM_SMS:
-                splits = max(1, min(self.NUM_SMS // tiles, kb // 4))
-            return 1, bn, splits
-        return 0, (256 if N > 128 else 128), 1
+            stream_k = 1 if (out_is_f32 and tiles < 4 * self.NUM_SMS) else 0
+            return 1, bn, stream_k
+        return 0, (256 if N > 128 else 128), 0
 
     def gemm_tc(self, a, w, out, residual=None, plan=None) -> None:
         """bfloat16 x bfloat16 product on the tensor cores (tcgen05), float32 accumulation."""
         M, K = a.shape
         N = w.shape[0]
-        swap, bn, splits = plan if plan is not None else self.tc_plan(M, N, K, out.dtype == torch.float32)
-        atomic = 0
-        res = residual
-        if splits > 1:
+        swap, bn, stream_k = plan if plan is not None else self.tc_plan(M, N, K, out.dtype == torch.float32)
+        add = 0
+        if residual is not None:
             assert out.dtype == torch.float32
-            atomic = 1
-            if residual is None:
-                out.zero_()
-            elif residual.data_ptr() != out.data_ptr():
+            if residual.data_ptr() != out.data_ptr():
                 out.copy_(residual)
-            res = None
-        self._check(self.lib.tff_gemm_tc(_ptr(a), _ptr(w), _ptr(out), _c_int(_dt(out)), _ptr(res),
-                                         _c_int(M), _c_int(N), _c_int(K), _c_int(swap), _c_int(bn), _c_int(splits),
-                                         _c_int(atomic), self._stream()), "gemm_tc")
+            add = 1
+        elif stream_k:
+            assert out.dtype == torch.float32
+            out.zero_()                       # shares of a split tile are added to it
+        self._check(self.lib.tff_gemm_tc(_ptr(a), _ptr(w), _ptr(out), _c_int(_dt(out)), _c_int(add),
+                                         _c_int(M), _c_int(N), _c_int(K), _c_int(swap), _c_int(bn), _c_int(stream_k),
+                                         self._stream()), "gemm_tc")
         self.launches += 1
 
     def check_errors(self) -> None:
