@@ -20,6 +20,7 @@
 // (src/kernel/cuda/paged_flash_attention.cu:877-1055: 8 queries x 32 keys x one GQA group,
 // scale 1/sqrt(d) at :1158, online softmax :696-792), which is instantiated for 32/8/128 only.
 #include "common.cuh"
+#include "attention_common.h"
 
 namespace {
 
@@ -77,8 +78,8 @@ attn_fwd_kernel(const AttnParams p) {
     uint8_t* sK = sQ + BLOCK_M * D * 2;                          // [2][64][D]
     uint8_t* sV = sK + 2 * BLOCK_N * D * 2;                      // [2][64][D]
 
+    pdl_launch_dependents();          // the next kernel may become resident (it waits before it reads or writes)
     pdl_wait();
-    pdl_launch_dependents();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int b = blockIdx.z, kvh = blockIdx.y;
     // later tiles see more keys: they are issued first
@@ -322,8 +323,8 @@ attn_fwd_kernel(const AttnParams p) {
 template <int D>
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     bf16* __restrict__ out, int num_splits) {
+    pdl_launch_dependents();          // the next kernel may become resident (it waits before it reads or writes)
     pdl_wait();
-    pdl_launch_dependents();
     const size_t row = blockIdx.x;
     float M = -INFINITY;
     for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_ml[(row * num_splits + s) * 2]);
@@ -368,9 +369,9 @@ TFF_API long long tff_attention_bf16_workspace(int rows, int num_splits, int d) 
 //   max_q_len   largest number of new tokens any request brings (sizes the grid)
 //   num_splits  shares of the key range per tile (> 1 needs ``workspace``)
 // Returns TFF_ERR_UNSUPPORTED for head sizes other than 64 and 128.
-TFF_API int tff_attention_bf16(
+static int attention_bf16_impl(
     const void* q, const int* q_start, const int* pos_start, const int* block_table, int table_width,
-    const void* cache, int cache_layers, int layer, int page_size,
+    const void* cache, long long cache_pages, int cache_layers, int layer, int page_size,
     void* out, void* workspace, int num_tokens, int num_requests, int max_q_len, int num_splits,
     int nq, int nkv, int d, float scale, int window, cudaStream_t stream) {
     if (num_tokens <= 0 || num_requests <= 0) return TFF_OK;
@@ -396,11 +397,17 @@ TFF_API int tff_attention_bf16(
     const bool keys_mode = (long long)max_q_len * G <= 16;
     const int block_m = keys_mode ? 16 : 64;
     const int q_tiles = (max_q_len * G + block_m - 1) / block_m;
-    int st;
-    if (d == 128) st = keys_mode ? launch_attn<128, true>(p, q_tiles, num_requests, stream)
-                                 : launch_attn<128, false>(p, q_tiles, num_requests, stream);
-    else st = keys_mode ? launch_attn<64, true>(p, q_tiles, num_requests, stream)
-                        : launch_attn<64, false>(p, q_tiles, num_requests, stream);
+    int st = TFF_ERR_UNSUPPORTED;
+    if (keys_mode && cache_pages > 0)      // decode: keys streamed by TMA (attention_decode.cu), when it takes the shape
+        st = tff_attention_decode_launch(q, q_start, pos_start, block_table, table_width, cache, cache_pages,
+                                         cache_layers, layer, page_size, out, p.part_o, p.part_ml, num_requests,
+                                         max_q_len, num_splits, nq, nkv, d, scale, window, stream);
+    if (st == TFF_ERR_UNSUPPORTED) {
+        if (d == 128) st = keys_mode ? launch_attn<128, true>(p, q_tiles, num_requests, stream)
+                                     : launch_attn<128, false>(p, q_tiles, num_requests, stream);
+        else st = keys_mode ? launch_attn<64, true>(p, q_tiles, num_requests, stream)
+                            : launch_attn<64, false>(p, q_tiles, num_requests, stream);
+    }
     if (st != TFF_OK) return st;
     if (num_splits > 1) {
         if (d == 128) return tff_launch_pdl(attn_combine_kernel<128>, (unsigned)rows, 128, 0, stream,
@@ -409,6 +416,28 @@ TFF_API int tff_attention_bf16(
                               (const float*)p.part_o, (const float*)p.part_ml, p.out, num_splits);
     }
     return TFF_OK;
+}
+
+TFF_API int tff_attention_bf16(
+    const void* q, const int* q_start, const int* pos_start, const int* block_table, int table_width,
+    const void* cache, int cache_layers, int layer, int page_size,
+    void* out, void* workspace, int num_tokens, int num_requests, int max_q_len, int num_splits,
+    int nq, int nkv, int d, float scale, int window, cudaStream_t stream) {
+    return attention_bf16_impl(q, q_start, pos_start, block_table, table_width, cache, 0, cache_layers, layer,
+                               page_size, out, workspace, num_tokens, num_requests, max_q_len, num_splits, nq, nkv, d,
+                               scale, window, stream);
+}
+
+// The same with the number of pages of the cache tensor given, which lets decode-sized calls
+// stream the keys with TMA (a tensor map needs the extent of what it describes).
+TFF_API int tff_attention_bf16_paged(
+    const void* q, const int* q_start, const int* pos_start, const int* block_table, int table_width,
+    const void* cache, long long cache_pages, int cache_layers, int layer, int page_size,
+    void* out, void* workspace, int num_tokens, int num_requests, int max_q_len, int num_splits,
+    int nq, int nkv, int d, float scale, int window, cudaStream_t stream) {
+    return attention_bf16_impl(q, q_start, pos_start, block_table, table_width, cache, cache_pages, cache_layers,
+                               layer, page_size, out, workspace, num_tokens, num_requests, max_q_len, num_splits, nq,
+                               nkv, d, scale, window, stream);
 }
 
 // ------------------------------------------------------- allocation-free variant

@@ -9,8 +9,8 @@
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
                              float* __restrict__ out, int hidden, int vocab) {
+    pdl_launch_dependents();          // the next kernel may become resident (it waits before it reads or writes)
     pdl_wait();
-    pdl_launch_dependents();
     const int t = blockIdx.x;
     const int tok = tokens[t];
     float* o = out + (size_t)t * hidden;
@@ -39,8 +39,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
                                const int* __restrict__ row_index, TO* __restrict__ out,
                                int dim, float eps) {
     __shared__ float red[32];
+    pdl_launch_dependents();          // the next kernel may become resident (it waits before it reads or writes)
     pdl_wait();
-    pdl_launch_dependents();
     const int r = blockIdx.x;
     const int row = row_index ? row_index[r] : r;
     const float* xr = x + (size_t)row * dim;
@@ -69,8 +69,8 @@ TFF_API int tff_rmsnorm(const float* x, const float* w, const int* row_index, vo
 // (src/kernel/cuda/unary.cu:10-27: x1 = gate, x2 = up).
 template <typename TIN, typename T>
 __global__ void swiglu_kernel(const TIN* __restrict__ gu, T* __restrict__ out, long long total, int inter) {
+    pdl_launch_dependents();          // the next kernel may become resident (it waits before it reads or writes)
     pdl_wait();
-    pdl_launch_dependents();
     for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (long long)gridDim.x * blockDim.x) {
         const long long t = idx / inter;
@@ -136,8 +136,8 @@ __global__ void qk_norm_rope_kv_write_kernel(
     const int* __restrict__ block_table, int table_width,
     T* __restrict__ cache, KvLayout L, int layer, int write_cache,
     int nq, int nkv, int d, int max_pos) {
+    pdl_launch_dependents();          // the next kernel may become resident (it waits before it reads or writes)
     pdl_wait();
-    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.y;
     const int head = blockIdx.x * (blockDim.x >> 5) + warp;
@@ -217,4 +217,26 @@ TFF_API int tff_qk_norm_rope_kv_write(
     }
     return TFF_QK_LAUNCH(float, float);
 #undef TFF_QK_LAUNCH
+}
+
+// --------------------------------------------------------------------- zero fill
+// Clears a float32 buffer that a following product adds its partial sums to.  A kernel of
+// this library rather than a memset, so that the dependent-launch chain is not broken.
+__global__ void zero_f32_kernel(float4* __restrict__ p4, float* __restrict__ tail, long long n4, int ntail) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x)
+        p4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (blockIdx.x == 0 && (int)threadIdx.x < ntail) tail[threadIdx.x] = 0.f;
+}
+
+TFF_API int tff_zero_f32(float* p, long long n, cudaStream_t stream) {
+    if (n <= 0) return TFF_OK;
+    if ((uintptr_t)p & 15) return TFF_ERR_BAD_ARGUMENT;
+    const long long n4 = n / 4;
+    const int ntail = (int)(n - n4 * 4);
+    long long blocks = (n4 + 255) / 256;
+    if (blocks < 1) blocks = 1;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    return tff_launch_pdl(zero_f32_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, (float4*)p, p + n4 * 4, n4, ntail);
 }

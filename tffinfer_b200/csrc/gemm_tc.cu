@@ -28,9 +28,7 @@
 // memory, stops issuing work, lets its copies in flight land, frees its tensor memory and
 // returns.
 #include "common.cuh"
-#include <cuda.h>
-#include <mutex>
-#include <unordered_map>
+#include "tma_host.h"
 
 namespace {
 
@@ -417,73 +415,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_lane,   // operand whose r
 }
 
 // ------------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    });
-    return fn;
-}
-
-struct MapKey {
-    const void* ptr; int rows; int cols; int box_rows; int box_cols; int elt;
-    bool operator==(const MapKey& o) const {
-        return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows && box_cols == o.box_cols && elt == o.elt;
-    }
-};
-struct MapKeyHash {
-    size_t operator()(const MapKey& k) const {
-        size_t h = (size_t)k.ptr;
-        h ^= (size_t)k.rows * 0x9E3779B97F4A7C15ull; h ^= (size_t)k.cols * 0xC2B2AE3D27D4EB4Full;
-        h ^= ((size_t)k.box_rows << 48) ^ ((size_t)k.box_cols << 40) ^ ((size_t)k.elt << 36);
-        return h;
-    }
-};
-
-// Tensor map of a row-major matrix [rows, cols] of 2-byte (bf16) or 4-byte (float32) elements:
-// boxes of box_cols x box_rows with 128-byte swizzle (box_cols * elt = 128), zero fill outside.
-bool get_tensor_map(const void* ptr, int rows, int cols, int box_rows, int box_cols, int elt, CUtensorMap* out) {
-    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-    static std::mutex mu;
-    const MapKey key{ptr, rows, cols, box_rows, box_cols, elt};
-    {
-        std::lock_guard<std::mutex> g(mu);
-        auto it = cache.find(key);
-        if (it != cache.end()) { *out = it->second; return true; }
-    }
-    EncodeTiledFn enc = get_encode_fn();
-    if (!enc) return false;
-    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)cols * elt};
-    const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
-    const cuuint32_t estr[2] = {1, 1};
-    CUtensorMap m;
-    if (enc(&m, elt == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
-            const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return false;
-    {
-        std::lock_guard<std::mutex> g(mu);
-        if (cache.size() > 4096) cache.clear();
-        cache[key] = m;
-    }
-    *out = m;
-    return true;
-}
-
-int* g_error_flag = nullptr;
-int g_num_sms = 0;
-
 template <int BN, bool SWAP, int EPI, typename TC, bool TMA_OUT>
 int launch_tc(const CUtensorMap& tl, const CUtensorMap& tc, const CUtensorMap& to, void* out,
               int rows_lane, int rows_col, int K, int ldo, int stream_k, cudaStream_t stream) {
@@ -497,10 +428,11 @@ int launch_tc(const CUtensorMap& tl, const CUtensorMap& tc, const CUtensorMap& t
     }
     const long long n_tiles = (long long)((rows_lane + BM - 1) / BM) * ((rows_col + BN - 1) / BN);
     const long long units = stream_k ? n_tiles * ((K + BK - 1) / BK) : n_tiles;
-    long long ctas = (long long)g_num_sms * Cfg::kCtasPerSm;
+    long long ctas = (long long)tff_num_sms() * Cfg::kCtasPerSm;
+    if (ctas <= 0) return TFF_ERR_LAUNCH;
     if (ctas > units) ctas = units;
     return tff_launch_pdl(kern, dim3((unsigned)ctas), dim3(NUM_THREADS), (size_t)Cfg::kSmemBytes, stream, tl, tc, to,
-                          (TC*)out, rows_lane, rows_col, K, ldo, stream_k, g_error_flag);
+                          (TC*)out, rows_lane, rows_col, K, ldo, stream_k, tff_device_error_flag());
 }
 
 template <int BN, bool SWAP, bool TMA_OUT>
@@ -516,29 +448,6 @@ int dispatch_epi(const CUtensorMap& tl, const CUtensorMap& tc, const CUtensorMap
 
 }  // namespace
 
-// One-time set-up of this translation unit on the current device: the error word.
-TFF_API int tff_gemm_tc_init() {
-    if (g_error_flag) return TFF_OK;
-    if (!get_encode_fn()) return TFF_ERR_DRIVER;
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return TFF_ERR_LAUNCH;
-    if (cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || g_num_sms <= 0)
-        return TFF_ERR_LAUNCH;
-    if (cudaMalloc(&g_error_flag, sizeof(int)) != cudaSuccess) return TFF_ERR_LAUNCH;
-    if (cudaMemset(g_error_flag, 0, sizeof(int)) != cudaSuccess) return TFF_ERR_LAUNCH;
-    return TFF_OK;
-}
-
-// Reads (and clears) the error word: non-zero when a bounded wait inside a kernel ran out.
-// Synchronises the device.
-TFF_API int tff_gemm_tc_error() {
-    if (!g_error_flag) return 0;
-    int v = 0;
-    if (cudaMemcpy(&v, g_error_flag, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
-    if (v) cudaMemset(g_error_flag, 0, sizeof(int));
-    return v;
-}
-
 // out[M, N] (+)= A[M, K] * W[N, K]^T; A, W bfloat16.
 //   swap      0: A rows on TMEM lanes (tiles 128 x bn over M x N); 1: W rows on lanes (tiles 128 x bn over N x M)
 //   bn        16, 32, 64, 128 or 256
@@ -552,18 +461,18 @@ TFF_API int tff_gemm_tc(const void* A, const void* W, void* out, int out_is_bf16
     if (K <= 0 || ((add || stream_k) && out_is_bf16)) return TFF_ERR_BAD_ARGUMENT;
     if (K % 8 != 0) return TFF_ERR_UNSUPPORTED;                         // TMA row pitch must be a multiple of 16 bytes
     if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return TFF_ERR_UNSUPPORTED;
-    if (!g_error_flag) { const int st = tff_gemm_tc_init(); if (st != TFF_OK) return st; }
+    if (tff_device_error_flag() == nullptr) return TFF_ERR_LAUNCH;
     const void* lane_ptr = swap ? W : A;
     const void* col_ptr = swap ? A : W;
     const int rows_lane = swap ? N : M, rows_col = swap ? M : N;
     CUtensorMap tl, tc, to;
-    if (!get_tensor_map(lane_ptr, rows_lane, K, BM, BK, 2, &tl)) return TFF_ERR_DRIVER;
-    if (!get_tensor_map(col_ptr, rows_col, K, bn, BK, 2, &tc)) return TFF_ERR_DRIVER;
+    if (!tff_tensor_map_2d(lane_ptr, rows_lane, K, BM, BK, 2, &tl)) return TFF_ERR_DRIVER;
+    if (!tff_tensor_map_2d(col_ptr, rows_col, K, bn, BK, 2, &tc)) return TFF_ERR_DRIVER;
     // TMA output: normal orientation, row pitch a multiple of 16 bytes, 16-byte aligned base
     const int elt = out_is_bf16 ? 2 : 4;
     const bool tma_out = !swap && ((long long)N * elt) % 16 == 0 && ((uintptr_t)out & 15) == 0 && bn >= 128 / elt;
     to = tl;
-    if (tma_out && !get_tensor_map(out, M, N, 32, 128 / elt, elt, &to)) return TFF_ERR_DRIVER;
+    if (tma_out && !tff_tensor_map_2d(out, M, N, 32, 128 / elt, elt, &to)) return TFF_ERR_DRIVER;
 #define TFF_CASE(BN_)                                                                                              \
     case BN_:                                                                                                      \
         if (swap) return dispatch_epi<BN_, true, false>(tl, tc, to, out, out_is_bf16, add, rows_lane, rows_col, K, N, stream_k, stream); \

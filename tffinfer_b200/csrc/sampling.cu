@@ -17,8 +17,8 @@ __global__ void __launch_bounds__(NT)
 argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab) {
     __shared__ float sval[32];
     __shared__ int sidx[32];
+    pdl_launch_dependents();          // the next kernel may become resident (it waits before it reads or writes)
     pdl_wait();
-    pdl_launch_dependents();
     const float* row = logits + (size_t)blockIdx.x * vocab;
     float best = -INFINITY;
     int bi = 0x7fffffff;

@@ -157,15 +157,20 @@ class CudaKernels:
             add = 1
         elif stream_k:
             assert out.dtype == torch.float32
-            out.zero_()                       # shares of a split tile are added to it
+            self.zero_f32(out)                # shares of a split tile are added to it
         self._check(self.lib.tff_gemm_tc(_ptr(a), _ptr(w), _ptr(out), _c_int(_dt(out)), _c_int(add),
                                          _c_int(M), _c_int(N), _c_int(K), _c_int(swap), _c_int(bn), _c_int(stream_k),
                                          self._stream()), "gemm_tc")
         self.launches += 1
 
+    def zero_f32(self, t) -> None:
+        assert t.dtype == torch.float32 and t.is_contiguous()
+        self._check(self.lib.tff_zero_f32(_ptr(t), ctypes.c_longlong(t.numel()), self._stream()), "zero_f32")
+        self.launches += 1
+
     def check_errors(self) -> None:
         """Synchronises and raises if a bounded wait inside a kernel ran out since the last check."""
-        v = self.lib.tff_gemm_tc_error()
+        v = self.lib.tff_kernel_error()
         if v != 0:
             raise KernelError("a bounded wait inside a tcgen05 kernel ran out (or the error word could not be read)")
 
@@ -241,7 +246,7 @@ class CudaKernels:
         b = 1
         while b < num_requests:
             b *= 2
-        return max(1, min(16, -(-2 * self.NUM_SMS // (b * nkv))))
+        return max(1, min(16, 2 * self.NUM_SMS // (b * nkv)))     # one wave of two CTAs per SM
 
     def attention_bf16(self, q, batch, block_table, kv_cache, kv_layer, page_size, out,
                        nq, nkv, d, scale, window, num_splits=None) -> None:
@@ -252,9 +257,10 @@ class CudaKernels:
         ws = None
         if splits > 1:
             ws = torch.empty(T * nq * splits * (d + 2), dtype=torch.float32, device=q.device)
-        self._check(self.lib.tff_attention_bf16(
+        self._check(self.lib.tff_attention_bf16_paged(
             _ptr(q), _ptr(batch.q_start), _ptr(batch.pos_start), _ptr(block_table), _c_int(block_table.shape[1]),
-            _ptr(kv_cache), _c_int(kv_cache.shape[1]), _c_int(kv_layer), _c_int(page_size),
+            _ptr(kv_cache), ctypes.c_longlong(kv_cache.shape[0]), _c_int(kv_cache.shape[1]), _c_int(kv_layer),
+            _c_int(page_size),
             _ptr(out), _ptr(ws), _c_int(T), _c_int(batch.num_requests), _c_int(batch.max_q_len), _c_int(splits),
             _c_int(nq), _c_int(nkv), _c_int(d), _c_float(scale), _c_int(window), self._stream()), "attention_bf16")
         self.launches += 2 if splits > 1 else 1
