@@ -102,7 +102,7 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def make_engine(layers: int, max_live: int, cache_tokens: int, seed: int = 0):
+def make_engine(layers: int, max_live: int, cache_tokens: int, seed: int = 0, graphs: bool = True):
     import torch
     import tffinfer_b200 as tff
     from tffinfer_b200.config import Qwen3Config
@@ -111,7 +111,8 @@ def make_engine(layers: int, max_live: int, cache_tokens: int, seed: int = 0):
                       layer_types=("full_attention",) * layers, **{**SHAPE, "num_layers": layers}).validate()
     tensors = random_tensors_on_device(cfg, seed, "cuda", "bfloat16")
     ecfg = tff.EngineConfig(dtype="bfloat16", page_size=PAGE_SIZE, max_cache_tokens=cache_tokens,
-                            max_live_requests=max_live, max_tokens_per_step=PROMPT_LEN, max_model_len=CONTEXT)
+                            max_live_requests=max_live, max_tokens_per_step=PROMPT_LEN, max_model_len=CONTEXT,
+                            use_cuda_graphs=graphs)
     runner = tff.ModelRunner(config=cfg, tensors=tensors, engine_config=ecfg)
     del tensors
     torch.cuda.empty_cache()
@@ -210,6 +211,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=SHAPE["num_layers"],
                     help="fewer layers than the shape has (both numbers are reported)")
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (no batch 1 / 64, no prefill)")
+    ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel (for profilers)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -230,7 +232,7 @@ def main() -> int:
     peaks = load_peaks()
     max_batch = args.batch if args.skip_points else max(args.batch, 64)
     tokens_needed = max_batch * (PROMPT_LEN + warmup + args.steps + max_batch + 64)
-    engine, cfg = make_engine(args.layers, max_batch, tokens_needed)
+    engine, cfg = make_engine(args.layers, max_batch, tokens_needed, graphs=not args.no_graphs)
     mb = model_bytes(cfg)
 
     clocks = ClockSampler()
@@ -263,7 +265,7 @@ def main() -> int:
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
                    "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "page_size": PAGE_SIZE,
                    "parallelism": "1 GPU", "l2": "inputs larger than L2 (15 GB of weights read per step)",
-                   "cuda_graphs": True},
+                   "cuda_graphs": not args.no_graphs},
         "e2e": {"value": round(main_run["e2e_tok_s"], 1), "unit": "tok/s",
                 "h2d_bytes_per_step": main_run["h2d_bytes"], "d2h_bytes_per_step": main_run["d2h_bytes"]},
         "gpu_launches": main_run["launches"],

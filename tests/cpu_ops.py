@@ -34,9 +34,16 @@ class CpuOps:
             acc = residual.to(F64) + acc
         out.copy_(acc.to(out.dtype))
 
-    def swiglu(self, gate_up, out):
+    def merge_gate_up(self, gate_w, up_w):
+        return torch.cat([gate_w, up_w], dim=0).contiguous()
+
+    def swiglu(self, gate_up, out, block=0):
         I = out.shape[1]
-        g, u = gate_up[:, :I].to(F64), gate_up[:, I:].to(F64)
+        if block:
+            v = gate_up.view(gate_up.shape[0], I // block, 2, block)
+            g, u = v[:, :, 0].reshape(-1, I).to(F64), v[:, :, 1].reshape(-1, I).to(F64)
+        else:
+            g, u = gate_up[:, :I].to(F64), gate_up[:, I:].to(F64)
         out.copy_(((g / (1.0 + torch.exp(-g))) * u).to(out.dtype))
 
     def rope_table(self, table, theta, rot_dim):

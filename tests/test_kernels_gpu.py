@@ -70,6 +70,29 @@ def test_swiglu(ops, T, I, dt):
         CpuOps().swiglu(gu32, want)
         ops.swiglu(gu32.to(DEV), out)
         assert rel_err(out, want) < 8e-3
+    if I % 16 == 0:                               # gate and up alternating in blocks
+        CpuOps().swiglu(gu, want, 16)
+        ops.swiglu(gu.to(DEV), out, 16)
+        assert rel_err(out, want) < (1e-6 if dt == torch.float32 else 8e-3)
+
+
+@pytest.mark.parametrize("T,I,K", [(1, 64, 64), (8, 12288, 4096), (300, 192, 264), (700, 1024, 520), (2048, 12288, 256),
+                                   (257, 112, 80), (40, 160, 96)])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32])
+def test_gemm_swiglu_merged_weights(ops, T, I, K, dt):
+    """Every path of gemm_swiglu (fused tensor-core epilogue, split product + kernel, float32) from the
+    library's own merged layout."""
+    a = g((T, K), dt, 40)
+    wg, wu = g((I, K), dt, 41, 0.06), g((I, K), dt, 42, 0.06)
+    gate, up = a.double() @ wg.double().t(), a.double() @ wu.double().t()
+    want = (gate / (1 + torch.exp(-gate))) * up
+    merged = ops.merge_gate_up(wg.to(DEV), wu.to(DEV))
+    assert merged.shape == (2 * I, K)
+    out = torch.full((T, I), float("nan"), dtype=dt, device=DEV)
+    ops.gemm_swiglu(a.to(DEV), merged, out)
+    err = float((out.double().cpu() - want).abs().max() / want.abs().max())
+    assert err < (1e-5 if dt == torch.float32 else 1.2e-2), err
+    ops.check_errors()
 
 
 @pytest.mark.parametrize("theta,rot,maxpos", [(1e4, 16, 128), (1e6, 128, 4096), (5e5, 48, 700)])

@@ -67,30 +67,35 @@ TFF_API int tff_rmsnorm(const float* x, const float* w, const int* row_index, vo
 // ------------------------------------------------------------------- SwiGLU
 // out[t, i] = silu(gu[t, i]) * gu[t, I + i], silu(g) = g / (1 + exp(-g))
 // (src/kernel/cuda/unary.cu:10-27: x1 = gate, x2 = up).
+// ``block`` = 0: gu[t] = [gate (I) | up (I)]; ``block`` = b > 0: gate and up alternate in blocks of b
+// columns, gate feature i at column (i / b) * 2b + i % b and its up feature b columns further.
 template <typename TIN, typename T>
-__global__ void swiglu_kernel(const TIN* __restrict__ gu, T* __restrict__ out, long long total, int inter) {
+__global__ void swiglu_kernel(const TIN* __restrict__ gu, T* __restrict__ out, long long total, int inter, int block) {
     pdl_launch_dependents();          // the next kernel may become resident (it waits before it reads or writes)
     pdl_wait();
     for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (long long)gridDim.x * blockDim.x) {
         const long long t = idx / inter;
         const int i = (int)(idx - t * inter);
-        const float g = to_f32<TIN>(gu[t * 2 * inter + i]);
-        const float u = to_f32<TIN>(gu[t * 2 * inter + inter + i]);
+        const int gc = block > 0 ? (i / block) * 2 * block + i % block : i;
+        const int uc = block > 0 ? gc + block : inter + i;
+        const float g = to_f32<TIN>(gu[t * 2 * inter + gc]);
+        const float u = to_f32<TIN>(gu[t * 2 * inter + uc]);
         out[idx] = from_f32<T>((g / (1.0f + expf(-g))) * u);
     }
 }
 
 // dtype codes: 0 = float32, 1 = bfloat16; the input may be float32 with a bfloat16 output.
-TFF_API int tff_swiglu(const void* gu, int in_dt, void* out, int out_dt, int rows, int inter, cudaStream_t stream) {
+TFF_API int tff_swiglu(const void* gu, int in_dt, void* out, int out_dt, int rows, int inter, int block,
+                       cudaStream_t stream) {
     if (rows <= 0) return TFF_OK;
-    if (inter <= 0) return TFF_ERR_BAD_ARGUMENT;
+    if (inter <= 0 || block < 0 || (block > 0 && inter % block != 0)) return TFF_ERR_BAD_ARGUMENT;
     const long long total = (long long)rows * inter;
     const int nt = 256;
     const int blocks = (int)((total + nt - 1) / nt < 148 * 16 ? (total + nt - 1) / nt : 148 * 16);
-    if (in_dt == 1 && out_dt == 1) return tff_launch_pdl(swiglu_kernel<bf16, bf16>, blocks, nt, 0, stream, (const bf16*)gu, (bf16*)out, total, inter);
-    if (in_dt == 0 && out_dt == 1) return tff_launch_pdl(swiglu_kernel<float, bf16>, blocks, nt, 0, stream, (const float*)gu, (bf16*)out, total, inter);
-    if (in_dt == 0 && out_dt == 0) return tff_launch_pdl(swiglu_kernel<float, float>, blocks, nt, 0, stream, (const float*)gu, (float*)out, total, inter);
+    if (in_dt == 1 && out_dt == 1) return tff_launch_pdl(swiglu_kernel<bf16, bf16>, blocks, nt, 0, stream, (const bf16*)gu, (bf16*)out, total, inter, block);
+    if (in_dt == 0 && out_dt == 1) return tff_launch_pdl(swiglu_kernel<float, bf16>, blocks, nt, 0, stream, (const float*)gu, (bf16*)out, total, inter, block);
+    if (in_dt == 0 && out_dt == 0) return tff_launch_pdl(swiglu_kernel<float, float>, blocks, nt, 0, stream, (const float*)gu, (float*)out, total, inter, block);
     return TFF_ERR_BAD_ARGUMENT;
 }
 

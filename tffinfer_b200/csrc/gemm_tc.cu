@@ -38,7 +38,9 @@ constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
-enum Epilogue : int { EPI_STORE = 0, EPI_ADD = 1 };   // write the product | add it to what ``out`` holds
+// write the product | add it to what ``out`` holds | write silu(gate) * up of a product whose columns
+// alternate between 64 gate and 64 up features (normal orientation, bfloat16 out, through TMA)
+enum Epilogue : int { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2 };
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -325,29 +327,50 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_lane,   // operand whose r
             const bool partial = stream_k && (it.kb1 - it.kb0) < kbt;   // a share of the tile's K range: add
             if constexpr (TMA_OUT) {
                 // 128-byte-wide column chunks: 32 float32 or 64 bfloat16 per row
-                constexpr int CW = 128 / (int)sizeof(TC);
+                constexpr int CW = 128 / (int)sizeof(TC);      // output columns per chunk
+                constexpr int AW = EPI == EPI_SWIGLU ? 128 : CW;   // accumulator columns per chunk
                 const uint32_t my_stage = staging + (uint32_t)((warp - 2) * 2) * 4096u;
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += CW, ++chunk_no) {
+                for (int c0 = 0; c0 < BN; c0 += AW, ++chunk_no) {
                     const uint32_t buf = my_stage + (chunk_no & 1) * 4096u;
                     if (chunk_no >= 2) {                       // the store that last used this buffer has read it
                         if (lane == 0) bulk_wait_read<1>();
                         __syncwarp();
                     }
                     uint32_t packed[32];                       // this thread's row: 128 bytes
+                    if constexpr (EPI == EPI_SWIGLU) {
+                        // columns [c0, c0+64) are the gate, [c0+64, c0+128) the up projection of the
+                        // same 64 features: silu(g) * u, silu(g) = g / (1 + exp(-g))
 #pragma unroll
-                    for (int h = 0; h < CW / 16; ++h) {
-                        uint32_t v[16];
-                        tmem_ld16(t_addr + (uint32_t)(c0 + h * 16), v);
-                        tmem_ld_wait();
-                        if constexpr (sizeof(TC) == 4) {
-#pragma unroll
-                            for (int j = 0; j < 16; ++j) packed[h * 16 + j] = v[j];
-                        } else {
+                        for (int h = 0; h < 4; ++h) {
+                            uint32_t g[16], u[16];
+                            tmem_ld16(t_addr + (uint32_t)(c0 + h * 16), g);
+                            tmem_ld16(t_addr + (uint32_t)(c0 + 64 + h * 16), u);
+                            tmem_ld_wait();
 #pragma unroll
                             for (int j = 0; j < 8; ++j) {
-                                __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+                                const float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
+                                const float a0 = (g0 / (1.0f + __expf(-g0))) * __uint_as_float(u[2 * j]);
+                                const float a1 = (g1 / (1.0f + __expf(-g1))) * __uint_as_float(u[2 * j + 1]);
+                                __nv_bfloat162 b2 = __floats2bfloat162_rn(a0, a1);
                                 packed[h * 8 + j] = *reinterpret_cast<uint32_t*>(&b2);
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int h = 0; h < CW / 16; ++h) {
+                            uint32_t v[16];
+                            tmem_ld16(t_addr + (uint32_t)(c0 + h * 16), v);
+                            tmem_ld_wait();
+                            if constexpr (sizeof(TC) == 4) {
+#pragma unroll
+                                for (int j = 0; j < 16; ++j) packed[h * 16 + j] = v[j];
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) {
+                                    __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+                                    packed[h * 8 + j] = *reinterpret_cast<uint32_t*>(&b2);
+                                }
                             }
                         }
                     }
@@ -360,7 +383,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_lane,   // operand whose r
                     fence_async_smem();
                     __syncwarp();
                     if (lane == 0) {
-                        if (EPI == EPI_ADD || partial) tma_reduce_add_2d(&tm_out, buf, col_row0 + c0, lane_row0 + q * 32);
+                        if (EPI == EPI_SWIGLU) tma_store_2d(&tm_out, buf, (col_row0 + c0) / 2, lane_row0 + q * 32);
+                        else if (EPI == EPI_ADD || partial) tma_reduce_add_2d(&tm_out, buf, col_row0 + c0, lane_row0 + q * 32);
                         else tma_store_2d(&tm_out, buf, col_row0 + c0, lane_row0 + q * 32);
                         bulk_commit();
                     }
@@ -487,4 +511,22 @@ TFF_API int tff_gemm_tc(const void* A, const void* W, void* out, int out_is_bf16
     }
 #undef TFF_CASE
     return TFF_ERR_BAD_ARGUMENT;
+}
+
+// out[M, I] = silu(A Wg^T) * (A Wu^T), with W [2I, K] holding the gate and up rows alternating in
+// blocks of 64: rows [128 b, 128 b + 64) = gate features [64 b, 64 b + 64), rows [128 b + 64, 128 b + 128)
+// = the same up features.  Normal orientation only (prompt-sized M); I must be a multiple of 64.
+// TFF_ERR_UNSUPPORTED for shapes it does not take.
+TFF_API int tff_gemm_tc_swiglu(const void* A, const void* W, void* out, int M, int I, int K, int bn, cudaStream_t stream) {
+    if (M <= 0 || I <= 0) return TFF_OK;
+    if (K <= 0) return TFF_ERR_BAD_ARGUMENT;
+    if (K % 8 != 0 || I % 64 != 0 || (bn != 128 && bn != 256)) return TFF_ERR_UNSUPPORTED;
+    if (((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ((uintptr_t)out & 15)) return TFF_ERR_UNSUPPORTED;
+    if (tff_device_error_flag() == nullptr) return TFF_ERR_LAUNCH;
+    CUtensorMap tl, tc, to;
+    if (!tff_tensor_map_2d(A, M, K, BM, BK, 2, &tl)) return TFF_ERR_DRIVER;
+    if (!tff_tensor_map_2d(W, 2ll * I, K, bn, BK, 2, &tc)) return TFF_ERR_DRIVER;
+    if (!tff_tensor_map_2d(out, M, I, 32, 64, 2, &to)) return TFF_ERR_DRIVER;
+    if (bn == 256) return launch_tc<256, false, EPI_SWIGLU, bf16, true>(tl, tc, to, out, M, 2 * I, K, I, 0, stream);
+    return launch_tc<128, false, EPI_SWIGLU, bf16, true>(tl, tc, to, out, M, 2 * I, K, I, 0, stream);
 }

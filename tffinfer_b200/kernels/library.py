@@ -174,13 +174,28 @@ class CudaKernels:
         if v != 0:
             raise KernelError("a bounded wait inside a tcgen05 kernel ran out (or the error word could not be read)")
 
-    def swiglu(self, gate_up, out) -> None:
-        """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]; gate_up float32 or of out's type."""
+    @staticmethod
+    def gate_up_block(inter: int) -> int:
+        """Layout of a merged gate/up weight: 64 = gate and up rows alternate in blocks of 64 (what the
+        fused tensor-core epilogue wants), 0 = all gate rows, then all up rows."""
+        return 64 if inter % 64 == 0 else 0
+
+    def merge_gate_up(self, gate_w, up_w):
+        """One weight [2I, K] from the gate and up projections, in the layout gemm_swiglu expects."""
+        I, K = gate_w.shape
+        b = self.gate_up_block(I)
+        if b == 0:
+            return torch.cat([gate_w, up_w], dim=0).contiguous()
+        return torch.stack([gate_w.view(I // b, b, K), up_w.view(I // b, b, K)], dim=1).reshape(2 * I, K).contiguous()
+
+    def swiglu(self, gate_up, out, block: int = 0) -> None:
+        """out[t, i] = silu(gate[t, i]) * up[t, i]; gate_up float32 or of out's type, [gate | up] (block = 0) or
+        alternating in blocks of ``block`` columns."""
         self._need_cuda(gate_up, out)
         T, I = out.shape
         assert gate_up.shape == (T, 2 * I) and gate_up.dtype in (torch.float32, out.dtype)
         self._check(self.lib.tff_swiglu(_ptr(gate_up), _c_int(_dt(gate_up)), _ptr(out), _c_int(_dt(out)),
-                                        _c_int(T), _c_int(I), self._stream()), "swiglu")
+                                        _c_int(T), _c_int(I), _c_int(block), self._stream()), "swiglu")
         self.launches += 1
 
     def rope_table(self, table, theta: float, rot_dim: int) -> None:
@@ -277,13 +292,23 @@ class CudaKernels:
         self.launches += 1
 
     def gemm_swiglu(self, a, w_gate_up, out) -> None:
-        """out[T, I] = silu(a @ Wg^T) * (a @ Wu^T) with w_gate_up = [Wg; Wu] ([2I, K])."""
+        """out[T, I] = silu(a @ Wg^T) * (a @ Wu^T), w_gate_up being merge_gate_up(Wg, Wu)."""
+        self._need_cuda(a, w_gate_up, out)
         T, I = out.shape
-        small = (a.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and T <= self.SWAP_MAX_M)
+        K = a.shape[1]
+        block = self.gate_up_block(I)
+        tc = (a.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and K % 8 == 0
+              and a.data_ptr() % 16 == 0 and w_gate_up.data_ptr() % 16 == 0)
+        if tc and T > self.SWAP_MAX_M and block == 64 and out.dtype == torch.bfloat16 and out.data_ptr() % 16 == 0:
+            # prompt-sized: the activation is applied in the product's epilogue
+            self._check(self.lib.tff_gemm_tc_swiglu(_ptr(a), _ptr(w_gate_up), _ptr(out), _c_int(T), _c_int(I),
+                                                    _c_int(K), _c_int(256), self._stream()), "gemm_tc_swiglu")
+            self.launches += 1
+            return
+        small = tc and T <= self.SWAP_MAX_M
         gu = torch.empty((T, 2 * I), dtype=torch.float32 if small else out.dtype, device=out.device)
         self.gemm(a, w_gate_up, gu)
-        self.swiglu(gu, out)
-
+        self.swiglu(gu, out, block)
     def argmax(self, logits, out) -> None:
         self._need_cuda(logits, out)
         R, V = logits.shape

@@ -31,8 +31,8 @@ class SwiGLU(FeedForward):
     def load(self, tensors, ops, act_dtype) -> None:
         g, u = tensors["gate_proj.weight"], tensors["up_proj.weight"]
         dt = g.dtype if g.dtype == u.dtype else torch.float32
-        # one projection instead of two: rows [gate | up]
-        self.w_gate_up = torch.cat([g.to(dt), u.to(dt)], dim=0).contiguous()
+        # one projection instead of two; the kernel library chooses how gate and up rows are laid out
+        self.w_gate_up = ops.merge_gate_up(g.to(dt), u.to(dt))
         self.w_down = tensors["down_proj.weight"]
 
     def forward(self, h, ctx, residual):
