@@ -290,6 +290,35 @@ def test_flash_attention_bf16(ops, case):
     assert rel_err(out, gen) < 1e-2
 
 
+@pytest.mark.parametrize("nq,nkv,d,page,new,old", [(32, 8, 128, 16, [700], [300]), (8, 2, 64, 32, [333, 40], [0, 1000]),
+                                                   (8, 8, 128, 8, [129, 2], [65, 3])])
+def test_prompt_attention_when_the_running_maximum_jumps_late(ops, nq, nkv, d, page, new, old):
+    """Keys whose scores tower over everything before them, planted deep into the sequence: the
+    running maximum grows by far more than the lazy-rescale threshold, so the output accumulated
+    so far must be scaled down, more than once, and many key blocks go round the stage ring."""
+    dt = torch.bfloat16
+    entries, tables, cache, qkv = _paged_case(nq, nkv, d, page, new, old, 0, dt, seed=90, layers=1)
+    q = qkv[:, :nq * d].contiguous().view(-1, nq, d)
+    q[:, :, 5] = 6.0
+    G = nq // nkv
+    for i, (tb, n, o) in enumerate(zip(tables, new, old)):
+        total = n + o
+        for frac, boost in ((0.35, 8.0), (0.6, 16.0), (0.9, 30.0)):
+            pos = int(total * frac)
+            cache[tb[pos // page], 0, 0, :, pos % page, 5] = boost          # score ~ 6 * boost / sqrt(d)
+    q = q.view(-1, nq * d)
+    T = q.shape[0]
+    bc = build_step_batch(entries, old, list(range(len(new))), [tables], "cpu")
+    bg = build_step_batch(entries, old, list(range(len(new))), [tables], DEV)
+    want = torch.empty(T, nq * d, dtype=dt)
+    CpuOps().attention(q, bc, bc.block_tables[0], cache, 0, page, want, nq, nkv, d, 1 / math.sqrt(d), 0)
+    out = torch.full((T, nq * d), float("nan"), dtype=dt, device=DEV)
+    ops.attention_bf16(q.to(DEV), bg, bg.block_tables[0], cache.to(DEV), 0, page, out, nq, nkv, d, 1 / math.sqrt(d), 0)
+    assert torch.isfinite(out).all()
+    assert rel_err(out, want) < 1e-2
+    ops.check_errors()
+
+
 def test_attention_finds_one_far_key_among_hundreds(ops):
     """One key far back is made to dominate: a kernel that skips a page, or reads the wrong
     one, returns something else than that key's value."""

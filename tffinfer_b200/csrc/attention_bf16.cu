@@ -402,6 +402,10 @@ static int attention_bf16_impl(
         st = tff_attention_decode_launch(q, q_start, pos_start, block_table, table_width, cache, cache_pages,
                                          cache_layers, layer, page_size, out, p.part_o, p.part_ml, num_requests,
                                          max_q_len, num_splits, nq, nkv, d, scale, window, stream);
+    if (!keys_mode && num_splits == 1 && cache_pages > 0)   // portions: tcgen05 kernel (attention_prefill.cu)
+        st = tff_attention_prefill_launch(q, q_start, pos_start, block_table, table_width, cache, cache_pages,
+                                          cache_layers, layer, page_size, out, num_requests, max_q_len, nq, nkv, d,
+                                          scale, window, stream);
     if (st == TFF_ERR_UNSUPPORTED) {
         if (d == 128) st = keys_mode ? launch_attn<128, true>(p, q_tiles, num_requests, stream)
                                      : launch_attn<128, false>(p, q_tiles, num_requests, stream);

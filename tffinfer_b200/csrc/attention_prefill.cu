@@ -1,0 +1,474 @@
+// Prompt-portion attention over the paged cache on the 5th-generation tensor cores.
+//
+// A CTA takes 128 packed query rows (row R of a request = token R / G, head kvh*G + R % G) of
+// one (request, kv head) and walks the keys in blocks of 64:
+//   S = Q K^T     tcgen05.mma, M = 128, N = 64, K = head size; both operands K-major in
+//                 128-byte-swizzled shared memory; S (float32) in tensor memory, two buffers
+//   softmax       four warps, one thread per row: S row from TMEM, causal/window mask by
+//                 position, running maximum and sum in float32, probabilities to shared memory
+//                 as bfloat16 (K-major, swizzled: the A operand of the next product)
+//   O += P V      tcgen05.mma, M = 128, N = head size, K = 64; V is the B operand in
+//                 MN-major form, exactly as TMA lays the pages down; O (float32) stays in
+//                 tensor memory for the whole key walk
+// O is rescaled only when a row's maximum has grown by more than 2^8 since the value the
+// exponentials use (the probabilities then stay below 2^8, harmless in float32/bfloat16), so
+// the read-modify-write of O in tensor memory is rare.
+//   warp 0      TMA producer: one box per (page, 64-column half, K or V) into a ring of stages
+//   warp 1      TMEM allocation, MMA issue (one lane)
+//   warps 2-5   softmax, rescale, epilogue (TMEM lane quarter = warp % 4)
+// Same contract as the rows mode of attention_bf16.cu, which it replaces when the page size
+// is 8/16/32/64.  Every mbarrier wait is bounded; a timeout raises the library's error word.
+#include "common.cuh"
+#include "tma_host.h"
+#include "attention_common.h"
+
+namespace {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_N = 64;
+constexpr int NSTAGES = 4;
+constexpr int NTHREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr float RESCALE_THRESHOLD = 8.0f;       // in log2 units
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (i >= 64) {
+            __nanosleep(32);
+            if (*abort_flag) return false;
+        }
+    }
+    *abort_flag = 1;
+    return false;
+}
+// the same for a whole warp: every lane gets the same answer
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(tm), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle, 8-row groups 1024 bytes apart.  ``lbo_bytes`` is
+// the distance between successive 64-element blocks along the M/N extent of an MN-major operand
+// (not used by K-major operands).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// kind::f16 instruction descriptor: float32 accumulate, bfloat16 operands, A K-major; B K-major or MN-major.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n, int b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) |
+           ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+struct PrefillParams {
+    const bf16* q; int q_row_stride;
+    const int* q_start; const int* pos_start;
+    const int* block_table; int table_width;
+    int cache_layers, layer, page_shift;
+    bf16* out;
+    int nq, nkv; float scale_log2; int window;
+    int* error_flag;
+};
+
+template <int D>
+__global__ void __launch_bounds__(NTHREADS, 1)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const PrefillParams p) {
+    constexpr int HF = D / 64;                                   // 64-column halves of a head
+    constexpr int CH = D / 8;                                    // 16-byte chunks per row
+    constexpr int KV_BYTES = BLOCK_N * D * 2;                    // K (or V) of one stage: [half][64 keys][128 B]
+    constexpr int STAGE_BYTES = 2 * KV_BYTES;
+    constexpr int Q_BYTES = BLOCK_M * D * 2;                     // [half][128 rows][128 B]
+    constexpr int P_BYTES = BLOCK_M * BLOCK_N * 2;               // [128 rows][128 B]
+    constexpr int TMEM_COLS = 256;                               // O: [0, D), S buffers at 128 and 192
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t sQ = base + NSTAGES * STAGE_BYTES;
+    const uint32_t sP = sQ + Q_BYTES;                            // two buffers
+    const uint32_t bars = sP + 2 * P_BYTES;
+    uint8_t* gQ = gbase + NSTAGES * STAGE_BYTES;
+    uint8_t* gP = gQ + Q_BYTES;
+    // barriers: kv_full[NS], kv_empty[NS], s_full[2], s_empty[2], p_full[2], pv_done[2], q_ready
+    auto kv_full = [&](int s) { return bars + 8u * s; };
+    auto kv_empty = [&](int s) { return bars + 8u * (NSTAGES + s); };
+    auto s_full = [&](int b) { return bars + 8u * (2 * NSTAGES + b); };
+    auto s_empty = [&](int b) { return bars + 8u * (2 * NSTAGES + 2 + b); };
+    auto p_full = [&](int b) { return bars + 8u * (2 * NSTAGES + 4 + b); };
+    auto pv_done = [&](int b) { return bars + 8u * (2 * NSTAGES + 6 + b); };
+    const uint32_t q_ready = bars + 8u * (2 * NSTAGES + 8);
+    volatile uint32_t* tmem_slot = (volatile uint32_t*)(gP + 2 * P_BYTES + 8 * (2 * NSTAGES + 9));
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int b = blockIdx.z, kvh = blockIdx.y;
+    const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;        // later tiles see more keys: issued first
+    const int G = p.nq / p.nkv;
+    const int ps = 1 << p.page_shift;
+
+    // request geometry: q_start and pos_start come with the step's batch (an earlier copy), not from
+    // the kernel ahead, but they are read after the dependency wait all the same
+    if (tid == 0) {
+        for (int s = 0; s < NSTAGES; ++s) { mbar_init(kv_full(s), 1); mbar_init(kv_empty(s), 1); }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(s_full(i), 1); mbar_init(s_empty(i), 4); mbar_init(p_full(i), 4); mbar_init(pv_done(i), 1);
+        }
+        mbar_init(q_ready, 4);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_cache) : "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32((const void*)tmem_slot), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();
+    pdl_wait();
+
+    const int q0 = p.q_start[b];
+    const int q_len = p.q_start[b + 1] - q0;
+    const int rows_total = q_len * G;
+    const bool active = tile * BLOCK_M < rows_total;              // uniform over the CTA
+    const int pos0 = p.pos_start[b];
+    const int first_tok = (tile * BLOCK_M) / G;
+    const int last_tok = min(q_len - 1, (tile * BLOCK_M + BLOCK_M - 1) / G);
+    const int hi = pos0 + last_tok;
+    const int lo_tile = p.window > 0 ? max(0, pos0 + first_tok - p.window + 1) : 0;
+    const int kb_lo = lo_tile / BLOCK_N, kb_hi = hi / BLOCK_N;
+    const int nb = active ? kb_hi - kb_lo + 1 : 0;
+    const int* table = p.block_table + (size_t)b * p.table_width;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        const int ppb = BLOCK_N >> p.page_shift;
+        const int nloads = ppb * HF * 2;                          // boxes per stage (<= 32)
+        const int j = lane / (HF * 2), rem = lane % (HF * 2);
+        const int kv = rem / HF, hf = rem % HF;
+        for (int i = 0; i < nb; ++i) {
+            const int s = i % NSTAGES;
+            const uint32_t round = i / NSTAGES;
+            bool ok = true;
+            if (round > 0) {
+                if (lane == 0) ok = mbar_wait(kv_empty(s), (round - 1) & 1, abort_flag);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+            }
+            if (!ok) break;
+            const int n0 = (kb_lo + i) * BLOCK_N + (j << p.page_shift);
+            int page = -1;
+            if (lane < nloads && n0 <= hi) page = table[n0 >> p.page_shift];
+            const bool valid = page >= 0;
+            const unsigned mask = __ballot_sync(0xffffffffu, valid);
+            if (lane == 0) mbar_expect_tx(kv_full(s), (uint32_t)__popc(mask) * (uint32_t)(ps * 128));
+            __syncwarp();
+            if (valid) {
+                const long long row = ((((long long)page * p.cache_layers + p.layer) * 2 + kv) * p.nkv + kvh) << p.page_shift;
+                // stage layout: K then V, each [half][64 keys][128 B]
+                const uint32_t dst = base + s * STAGE_BYTES + kv * KV_BYTES + hf * (BLOCK_N * 128) +
+                                     (uint32_t)((j << p.page_shift) * 128);
+                tma_load_2d(dst, &tm_cache, kv_full(s), hf * 64, (int)row);
+            }
+        }
+    } else if (warp == 1) {
+        // -------------------------------------------------------------- MMA issuer
+        if (lane == 0 && nb > 0) {
+            constexpr uint32_t idesc_s = make_idesc(BLOCK_M, BLOCK_N, 0);
+            constexpr uint32_t idesc_pv = make_idesc(BLOCK_M, D, 1);
+            bool ok = mbar_wait(q_ready, 0, abort_flag);
+            auto issue_pv = [&](int jj) {                          // O += P_jj V_jj
+                const int sb = jj & 1, st = jj % NSTAGES;
+                if (!mbar_wait(p_full(sb), (jj >> 1) & 1, abort_flag)) return false;
+                tc_fence_after();
+                const uint32_t v_addr = base + st * STAGE_BYTES + KV_BYTES;
+                const uint32_t p_addr = sP + sb * P_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
+                    const uint64_t adesc = make_smem_desc(p_addr + kk * 32, 16);
+                    const uint64_t bdesc = make_smem_desc(v_addr + kk * 16 * 128, BLOCK_N * 128);
+                    umma_bf16(tmem_base, adesc, bdesc, idesc_pv, (jj > 0 || kk > 0) ? 1u : 0u);
+                }
+                umma_commit(kv_empty(st));                         // K and V of the stage have been read
+                umma_commit(pv_done(sb));                          // O holds block jj; the P buffer is free
+                return true;
+            };
+            for (int j = 0; j < nb && ok; ++j) {
+                const int sb = j & 1, st = j % NSTAGES;
+                ok = mbar_wait(kv_full(st), (j / NSTAGES) & 1, abort_flag);
+                if (ok && j >= 2) ok = mbar_wait(s_empty(sb), ((j >> 1) - 1) & 1, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t k_addr = base + st * STAGE_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off = (kk / 4) * (BLOCK_M * 128) + (kk % 4) * 32;      // Q: [half][128 rows][128 B]
+                    const uint32_t koff = (kk / 4) * (BLOCK_N * 128) + (kk % 4) * 32;     // K: [half][64 keys][128 B]
+                    umma_bf16(tmem_base + 128 + sb * 64, make_smem_desc(sQ + off, 16), make_smem_desc(k_addr + koff, 16),
+                              idesc_s, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(s_full(sb));
+                if (j > 0) ok = issue_pv(j - 1);                   // overlaps the softmax of block j
+            }
+            if (ok) issue_pv(nb - 1);
+        }
+    } else {
+        // ------------------------------------------------- softmax / rescale / epilogue
+        const int q = warp & 3;
+        const int r = q * 32 + lane;                               // row of the tile = TMEM lane
+        const int R = tile * BLOCK_M + r;
+        const bool rv = active && R < rows_total;
+        const int pr = pos0 + R / G;
+        const int lo_r = p.window > 0 ? max(0, pr - p.window + 1) : 0;
+        const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
+        // the query tile: this thread's row, 16-byte chunks XOR-swizzled by row % 8, one [128 x 128 B] block per half
+        if (active) {
+            const bf16* src = p.q + (size_t)(q0 + R / G) * p.q_row_stride + (size_t)(kvh * G + R % G) * D;
+#pragma unroll
+            for (int c = 0; c < CH; ++c) {
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (rv) v = *reinterpret_cast<const uint4*>(src + c * 8);
+                *reinterpret_cast<uint4*>(gQ + (c >> 3) * (BLOCK_M * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(q_ready);
+        }
+        float m_used = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < nb && ok; ++j) {
+            const int sb = j & 1, st = j % NSTAGES;
+            const int blk = kb_lo + j;
+            if (blk == kb_hi || blk == kb_lo) {
+                // value rows no query row may see (beyond the last key, before the window): cleared, since
+                // page slots and unfetched shared memory may hold anything.  The stage has landed first.
+                ok = mbar_wait_warp(kv_full(st), (j / NSTAGES) & 1, abort_flag);
+                if (!ok) break;
+                uint8_t* gV = gbase + st * STAGE_BYTES + KV_BYTES;
+                for (int idx = tid - 64; idx < BLOCK_N * CH; idx += 128) {
+                    const int kr = idx / CH, c = idx % CH;
+                    const int n = blk * BLOCK_N + kr;
+                    if (n > hi || n < lo_tile)
+                        *reinterpret_cast<uint4*>(gV + (c >> 3) * (BLOCK_N * 128) + kr * 128 + (((c & 7) ^ (kr & 7)) << 4)) =
+                            make_uint4(0u, 0u, 0u, 0u);
+                }
+                fence_async_smem();
+            }
+            ok = mbar_wait_warp(s_full(sb), (j >> 1) & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            float s[BLOCK_N];
+#pragma unroll
+            for (int h = 0; h < BLOCK_N / 16; ++h) {
+                uint32_t v[16];
+                tmem_ld16(t_row + 128 + sb * 64 + h * 16, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 16; ++i) s[h * 16 + i] = __uint_as_float(v[i]);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_empty(sb));               // the S buffer may be overwritten
+            float m_blk = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < BLOCK_N; ++i) {
+                const int n = blk * BLOCK_N + i;
+                const bool vis = rv && n <= pr && n >= lo_r;
+                s[i] = vis ? s[i] * p.scale_log2 : -INFINITY;
+                m_blk = fmaxf(m_blk, s[i]);
+            }
+            // lazy rescale: only when the maximum has grown by more than the threshold (warp-uniform decision)
+            const bool grow = m_blk > m_used + RESCALE_THRESHOLD || (m_used == -INFINITY && m_blk > -INFINITY);
+            if (__any_sync(0xffffffffu, grow)) {
+                const float m_new = grow ? m_blk : m_used;
+                const float alpha = (m_used == -INFINITY) ? 0.f : exp2f(m_used - m_new);
+                if (j > 0) {
+                    // O must hold every earlier block before it is rescaled
+                    ok = mbar_wait_warp(pv_done((j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll 1
+                    for (int c0 = 0; c0 < D; c0 += 16) {
+                        uint32_t v[16];
+                        tmem_ld16(t_row + c0, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * (grow ? alpha : 1.f));
+                        tmem_st16(t_row + c0, v);
+                    }
+                    tmem_st_wait();
+                    tc_fence_before();
+                }
+                if (grow) { l *= alpha; m_used = m_new; }
+            }
+            // the P buffer must have been read by the PV product of two blocks ago
+            if (j >= 2) {
+                ok = mbar_wait_warp(pv_done(sb), ((j >> 1) - 1) & 1, abort_flag);
+                if (!ok) break;
+            }
+            const float ms = m_used == -INFINITY ? 0.f : m_used;
+            uint8_t* prow = gP + sb * P_BYTES + r * 128;
+            float lsum = 0.f;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                uint32_t w[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float e0 = exp2f(s[c * 8 + 2 * i] - ms), e1 = exp2f(s[c * 8 + 2 * i + 1] - ms);
+                    __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
+                    // the sum uses the rounded values, which are what the PV product multiplies
+                    lsum += __bfloat162float(b2.x) + __bfloat162float(b2.y);
+                    w[i] = *reinterpret_cast<uint32_t*>(&b2);
+                }
+                *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            l += lsum;
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full(sb));
+        }
+        // ---------------------------------------------------------------- epilogue
+        if (ok && nb > 0) ok = mbar_wait_warp(pv_done((nb - 1) & 1), ((nb - 1) >> 1) & 1, abort_flag);
+        if (ok && nb > 0) {
+            tc_fence_after();
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            bf16* orow = p.out + ((size_t)(q0 + R / G) * p.nq + (kvh * G + R % G)) * D;
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 16) {
+                uint32_t v[16];
+                tmem_ld16(t_row + c0, v);
+                tmem_ld_wait();
+                if (rv) {
+                    uint32_t w[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[2 * i]) * inv, __uint_as_float(v[2 * i + 1]) * inv);
+                        w[i] = *reinterpret_cast<uint32_t*>(&b2);
+                    }
+                    *reinterpret_cast<uint4*>(orow + c0) = make_uint4(w[0], w[1], w[2], w[3]);
+                    *reinterpret_cast<uint4*>(orow + c0 + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+                }
+            }
+        }
+    }
+    // ------------------------------------------------------------------ teardown
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+        if (tid == 0) atomicExch(p.error_flag, 1);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+template <int D>
+int launch_prefill(const CUtensorMap& tm, const PrefillParams& p, int q_tiles, int B, cudaStream_t stream) {
+    constexpr int smem = NSTAGES * 2 * BLOCK_N * D * 2 + BLOCK_M * D * 2 + 2 * BLOCK_M * BLOCK_N * 2 +
+                         8 * (2 * NSTAGES + 9) + 16 + 1024;
+    auto kern = attn_prefill_tc_kernel<D>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return TFF_ERR_LAUNCH;
+        configured = true;
+    }
+    return tff_launch_pdl(kern, dim3(q_tiles, p.nkv, B), dim3(NTHREADS), (size_t)smem, stream, tm, p);
+}
+
+}  // namespace
+
+// Prompt-portion attention on tcgen05.  TFF_ERR_UNSUPPORTED when the shape is not one it takes
+// (head size 64/128, page size 8/16/32/64).
+int tff_attention_prefill_launch(
+    const void* q, const int* q_start, const int* pos_start, const int* block_table, int table_width,
+    const void* cache, long long cache_pages, int cache_layers, int layer, int page_size,
+    void* out, int num_requests, int max_q_len, int nq, int nkv, int d, float scale, int window, cudaStream_t stream) {
+    if (d != 64 && d != 128) return TFF_ERR_UNSUPPORTED;
+    if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64) return TFF_ERR_UNSUPPORTED;
+    if (cache_pages <= 0) return TFF_ERR_UNSUPPORTED;
+    if (((uintptr_t)cache & 15) || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) || (nq * d) % 8) return TFF_ERR_UNSUPPORTED;
+    const long long rows = cache_pages * cache_layers * 2 * nkv * page_size;
+    if (rows >= (1ll << 31) || num_requests > 65535 || nkv > 65535) return TFF_ERR_UNSUPPORTED;
+    CUtensorMap tm;
+    if (!tff_tensor_map_2d(cache, rows, d, page_size, 64, 2, &tm)) return TFF_ERR_DRIVER;
+    PrefillParams p;
+    p.q = (const bf16*)q; p.q_row_stride = nq * d;
+    p.q_start = q_start; p.pos_start = pos_start;
+    p.block_table = block_table; p.table_width = table_width;
+    p.cache_layers = cache_layers; p.layer = layer;
+    p.page_shift = page_size == 8 ? 3 : page_size == 16 ? 4 : page_size == 32 ? 5 : 6;
+    p.out = (bf16*)out;
+    p.nq = nq; p.nkv = nkv; p.scale_log2 = scale * 1.4426950408889634f; p.window = window;
+    p.error_flag = tff_device_error_flag();
+    if (p.error_flag == nullptr) return TFF_ERR_LAUNCH;
+    const int G = nq / nkv;
+    const int q_tiles = (max_q_len * G + BLOCK_M - 1) / BLOCK_M;
+    return d == 128 ? launch_prefill<128>(tm, p, q_tiles, num_requests, stream)
+                    : launch_prefill<64>(tm, p, q_tiles, num_requests, stream);
+}
