@@ -20,7 +20,7 @@ TOL = {"float32": 2e-5, "bfloat16": 4e-2}
 def plain_logits(tmp_path_factory):
     out = {}
     tmp = tmp_path_factory.mktemp("models")
-    for name in ("A", "B", "C"):
+    for name in ("A", "B", "C", "D"):
         d = make_model_dir(tmp, name)
         reqs = make_requests(name)
         pm = PlainModel(d)
@@ -39,7 +39,7 @@ def _steps(name, mode, reqs):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
 def test_cut_modes_match_plain(plain_logits, name, mode, dtype):
     d, reqs, want = plain_logits[name]

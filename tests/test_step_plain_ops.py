@@ -24,7 +24,7 @@ def _runner(model_dir, name, pool_tokens):
 def plain_logits(tmp_path_factory):
     out = {}
     tmp = tmp_path_factory.mktemp("models")
-    for name in ("A", "B", "C"):
+    for name in ("A", "B", "C", "D"):
         d = make_model_dir(tmp, name)
         reqs = make_requests(name)
         pm = PlainModel(d)
@@ -32,7 +32,7 @@ def plain_logits(tmp_path_factory):
     return out
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
 def test_cut_modes_match_plain(plain_logits, name, mode):
     d, reqs, want = plain_logits[name]

@@ -60,7 +60,7 @@ template <int D> __device__ __forceinline__ uint32_t swz(int row, int chunk) {
 
 struct AttnParams {
     const bf16* q; int q_row_stride;
-    const int* q_start; const int* pos_start;
+    const int* q_start; const int* pos_start; const int* req_ids;   // req_ids: rows of the per-request arrays (or null)
     const int* block_table; int table_width;
     const bf16* cache; KvLayout L; int layer;
     bf16* out; float* part_o; float* part_ml; int num_splits;
@@ -81,7 +81,7 @@ attn_fwd_kernel(const AttnParams p) {
     pdl_launch_dependents();          // the next kernel may become resident (it waits before it reads or writes)
     pdl_wait();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int b = blockIdx.z, kvh = blockIdx.y;
+    const int b = p.req_ids ? p.req_ids[blockIdx.z] : (int)blockIdx.z, kvh = blockIdx.y;
     // later tiles see more keys: they are issued first
     const int tile = (int)(gridDim.x / p.num_splits) - 1 - (int)(blockIdx.x / p.num_splits);
     const int split = blockIdx.x % p.num_splits;
@@ -319,13 +319,19 @@ attn_fwd_kernel(const AttnParams p) {
     }
 }
 
-// out[row, :] = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s, M = max_s m_s
+// out[row, :] = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s, M = max_s m_s, for the rows
+// (token, head) of the requests the launch covered: grid (nq * max_q_len, requests).
 template <int D>
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                    bf16* __restrict__ out, int num_splits) {
+                                    bf16* __restrict__ out, int num_splits, const int* __restrict__ q_start,
+                                    const int* __restrict__ req_ids, int nq) {
     pdl_launch_dependents();          // the next kernel may become resident (it waits before it reads or writes)
     pdl_wait();
-    const size_t row = blockIdx.x;
+    const int b = req_ids ? req_ids[blockIdx.y] : (int)blockIdx.y;
+    const int t = blockIdx.x / nq, h = blockIdx.x % nq;
+    const int q0 = q_start[b];
+    if (t >= q_start[b + 1] - q0) return;
+    const size_t row = (size_t)(q0 + t) * nq + h;
     float M = -INFINITY;
     for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_ml[(row * num_splits + s) * 2]);
     const float Ms = M == -INFINITY ? 0.f : M;
@@ -370,7 +376,7 @@ TFF_API long long tff_attention_bf16_workspace(int rows, int num_splits, int d) 
 //   num_splits  shares of the key range per tile (> 1 needs ``workspace``)
 // Returns TFF_ERR_UNSUPPORTED for head sizes other than 64 and 128.
 static int attention_bf16_impl(
-    const void* q, const int* q_start, const int* pos_start, const int* block_table, int table_width,
+    const void* q, const int* q_start, const int* pos_start, const int* req_ids, const int* block_table, int table_width,
     const void* cache, long long cache_pages, int cache_layers, int layer, int page_size,
     void* out, void* workspace, int num_tokens, int num_requests, int max_q_len, int num_splits,
     int nq, int nkv, int d, float scale, int window, cudaStream_t stream) {
@@ -383,7 +389,7 @@ static int attention_bf16_impl(
     const int G = nq / nkv;
     AttnParams p;
     p.q = (const bf16*)q; p.q_row_stride = nq * d;
-    p.q_start = q_start; p.pos_start = pos_start;
+    p.q_start = q_start; p.pos_start = pos_start; p.req_ids = req_ids;
     p.block_table = block_table; p.table_width = table_width;
     p.cache = (const bf16*)cache; p.L = make_kv_layout(cache_layers, nkv, page_size, d); p.layer = layer;
     p.out = (bf16*)out;
@@ -399,11 +405,11 @@ static int attention_bf16_impl(
     const int q_tiles = (max_q_len * G + block_m - 1) / block_m;
     int st = TFF_ERR_UNSUPPORTED;
     if (keys_mode && cache_pages > 0)      // decode: keys streamed by TMA (attention_decode.cu), when it takes the shape
-        st = tff_attention_decode_launch(q, q_start, pos_start, block_table, table_width, cache, cache_pages,
+        st = tff_attention_decode_launch(q, q_start, pos_start, req_ids, block_table, table_width, cache, cache_pages,
                                          cache_layers, layer, page_size, out, p.part_o, p.part_ml, num_requests,
                                          max_q_len, num_splits, nq, nkv, d, scale, window, stream);
     if (!keys_mode && num_splits == 1 && cache_pages > 0)   // portions: tcgen05 kernel (attention_prefill.cu)
-        st = tff_attention_prefill_launch(q, q_start, pos_start, block_table, table_width, cache, cache_pages,
+        st = tff_attention_prefill_launch(q, q_start, pos_start, req_ids, block_table, table_width, cache, cache_pages,
                                           cache_layers, layer, page_size, out, num_requests, max_q_len, nq, nkv, d,
                                           scale, window, stream);
     if (st == TFF_ERR_UNSUPPORTED) {
@@ -414,10 +420,12 @@ static int attention_bf16_impl(
     }
     if (st != TFF_OK) return st;
     if (num_splits > 1) {
-        if (d == 128) return tff_launch_pdl(attn_combine_kernel<128>, (unsigned)rows, 128, 0, stream,
-                                            (const float*)p.part_o, (const float*)p.part_ml, p.out, num_splits);
-        return tff_launch_pdl(attn_combine_kernel<64>, (unsigned)rows, 64, 0, stream,
-                              (const float*)p.part_o, (const float*)p.part_ml, p.out, num_splits);
+        const dim3 cgrid((unsigned)(nq * max_q_len), (unsigned)num_requests);
+        if (d == 128) return tff_launch_pdl(attn_combine_kernel<128>, cgrid, dim3(128), 0, stream,
+                                            (const float*)p.part_o, (const float*)p.part_ml, p.out, num_splits,
+                                            q_start, req_ids, nq);
+        return tff_launch_pdl(attn_combine_kernel<64>, cgrid, dim3(64), 0, stream,
+                              (const float*)p.part_o, (const float*)p.part_ml, p.out, num_splits, q_start, req_ids, nq);
     }
     return TFF_OK;
 }
@@ -427,19 +435,21 @@ TFF_API int tff_attention_bf16(
     const void* cache, int cache_layers, int layer, int page_size,
     void* out, void* workspace, int num_tokens, int num_requests, int max_q_len, int num_splits,
     int nq, int nkv, int d, float scale, int window, cudaStream_t stream) {
-    return attention_bf16_impl(q, q_start, pos_start, block_table, table_width, cache, 0, cache_layers, layer,
+    return attention_bf16_impl(q, q_start, pos_start, nullptr, block_table, table_width, cache, 0, cache_layers, layer,
                                page_size, out, workspace, num_tokens, num_requests, max_q_len, num_splits, nq, nkv, d,
                                scale, window, stream);
 }
 
 // The same with the number of pages of the cache tensor given, which lets decode-sized calls
 // stream the keys with TMA (a tensor map needs the extent of what it describes).
+// ``req_ids`` (may be null) lists the rows of q_start / pos_start / block_table the launch covers,
+// num_requests of them; null means rows 0 .. num_requests-1.
 TFF_API int tff_attention_bf16_paged(
-    const void* q, const int* q_start, const int* pos_start, const int* block_table, int table_width,
+    const void* q, const int* q_start, const int* pos_start, const int* req_ids, const int* block_table, int table_width,
     const void* cache, long long cache_pages, int cache_layers, int layer, int page_size,
     void* out, void* workspace, int num_tokens, int num_requests, int max_q_len, int num_splits,
     int nq, int nkv, int d, float scale, int window, cudaStream_t stream) {
-    return attention_bf16_impl(q, q_start, pos_start, block_table, table_width, cache, cache_pages, cache_layers,
+    return attention_bf16_impl(q, q_start, pos_start, req_ids, block_table, table_width, cache, cache_pages, cache_layers,
                                layer, page_size, out, workspace, num_tokens, num_requests, max_q_len, num_splits, nq,
                                nkv, d, scale, window, stream);
 }

@@ -84,7 +84,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 struct DecodeParams {
     const bf16* q; int q_row_stride;
-    const int* q_start; const int* pos_start;
+    const int* q_start; const int* pos_start; const int* req_ids;
     const int* block_table; int table_width;
     int cache_layers, layer, page_shift;         // page_size = 1 << page_shift
     bf16* out; float* part_o; float* part_ml; int num_splits;
@@ -120,7 +120,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_cache, const DecodePar
     auto empty_bar = [&](int s) { return bars + 8u * (NSTAGES + s); };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int b = blockIdx.z, kvh = blockIdx.y, split = blockIdx.x;
+    const int kvh = blockIdx.y, split = blockIdx.x;
     const int ps = 1 << p.page_shift;
     const int G = p.nq / p.nkv;
 
@@ -134,6 +134,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_cache, const DecodePar
     pdl_launch_dependents();
     pdl_wait();
 
+    const int b = p.req_ids ? p.req_ids[blockIdx.z] : (int)blockIdx.z;
     const int q0 = p.q_start[b];
     const int q_len = p.q_start[b + 1] - q0;
     const int rows_total = q_len * G;                              // <= 16 by the launcher's choice
@@ -361,7 +362,7 @@ int launch_decode(const CUtensorMap& tm, const DecodeParams& p, int B, cudaStrea
 // Launches the decode kernel (without the merge of the splits).  TFF_ERR_UNSUPPORTED when the
 // shape is not one it takes (head size 64/128, page size 8/16/32/64, at most 16 packed rows).
 int tff_attention_decode_launch(
-    const void* q, const int* q_start, const int* pos_start, const int* block_table, int table_width,
+    const void* q, const int* q_start, const int* pos_start, const int* req_ids, const int* block_table, int table_width,
     const void* cache, long long cache_pages, int cache_layers, int layer, int page_size,
     void* out, float* part_o, float* part_ml, int num_requests, int max_q_len, int num_splits,
     int nq, int nkv, int d, float scale, int window, cudaStream_t stream) {
@@ -375,7 +376,7 @@ int tff_attention_decode_launch(
     if (!tff_tensor_map_2d(cache, rows, d, page_size, 64, 2, &tm)) return TFF_ERR_DRIVER;
     DecodeParams p;
     p.q = (const bf16*)q; p.q_row_stride = nq * d;
-    p.q_start = q_start; p.pos_start = pos_start;
+    p.q_start = q_start; p.pos_start = pos_start; p.req_ids = req_ids;
     p.block_table = block_table; p.table_width = table_width;
     p.cache_layers = cache_layers; p.layer = layer;
     p.page_shift = page_size == 8 ? 3 : page_size == 16 ? 4 : page_size == 32 ? 5 : 6;

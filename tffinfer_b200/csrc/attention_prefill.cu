@@ -126,7 +126,7 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n, int b_mn_major) 
 
 struct PrefillParams {
     const bf16* q; int q_row_stride;
-    const int* q_start; const int* pos_start;
+    const int* q_start; const int* pos_start; const int* req_ids;
     const int* block_table; int table_width;
     int cache_layers, layer, page_shift;
     bf16* out;
@@ -164,7 +164,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const Prefi
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int b = blockIdx.z, kvh = blockIdx.y;
+    const int kvh = blockIdx.y;
     const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;        // later tiles see more keys: issued first
     const int G = p.nq / p.nkv;
     const int ps = 1 << p.page_shift;
@@ -189,6 +189,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const Prefi
     pdl_launch_dependents();
     pdl_wait();
 
+    const int b = p.req_ids ? p.req_ids[blockIdx.z] : (int)blockIdx.z;
     const int q0 = p.q_start[b];
     const int q_len = p.q_start[b + 1] - q0;
     const int rows_total = q_len * G;
@@ -446,7 +447,7 @@ int launch_prefill(const CUtensorMap& tm, const PrefillParams& p, int q_tiles, i
 // Prompt-portion attention on tcgen05.  TFF_ERR_UNSUPPORTED when the shape is not one it takes
 // (head size 64/128, page size 8/16/32/64).
 int tff_attention_prefill_launch(
-    const void* q, const int* q_start, const int* pos_start, const int* block_table, int table_width,
+    const void* q, const int* q_start, const int* pos_start, const int* req_ids, const int* block_table, int table_width,
     const void* cache, long long cache_pages, int cache_layers, int layer, int page_size,
     void* out, int num_requests, int max_q_len, int nq, int nkv, int d, float scale, int window, cudaStream_t stream) {
     if (d != 64 && d != 128) return TFF_ERR_UNSUPPORTED;
@@ -459,7 +460,7 @@ int tff_attention_prefill_launch(
     if (!tff_tensor_map_2d(cache, rows, d, page_size, 64, 2, &tm)) return TFF_ERR_DRIVER;
     PrefillParams p;
     p.q = (const bf16*)q; p.q_row_stride = nq * d;
-    p.q_start = q_start; p.pos_start = pos_start;
+    p.q_start = q_start; p.pos_start = pos_start; p.req_ids = req_ids;
     p.block_table = block_table; p.table_width = table_width;
     p.cache_layers = cache_layers; p.layer = layer;
     p.page_shift = page_size == 8 ? 3 : page_size == 16 ? 4 : page_size == 32 ? 5 : 6;

@@ -30,6 +30,9 @@ class StepEntry:
     want: Sequence[int] = ()
 
 
+NUM_FLAT = 9      # flat integer arrays ahead of the block tables in the packed buffer
+
+
 @dataclass(frozen=True)
 class BatchLayout:
     """Sizes of the packed integer buffer: T tokens, B requests, R logit rows, and the
@@ -40,7 +43,7 @@ class BatchLayout:
     widths: Tuple[int, ...]
 
     def sizes(self) -> List[int]:
-        return [self.T, self.T, self.T, self.B + 1, self.B, self.B, self.B, self.R] + \
+        return [self.T, self.T, self.T, self.B + 1, self.B, self.B, self.B, self.R, self.B] + \
                [self.B * w for w in self.widths]
 
     @property
@@ -70,10 +73,12 @@ class StepBatch:
     kv_len: torch.Tensor          # int32 [B]   tokens of each request in the cache after this step
     slots: torch.Tensor           # int32 [B]   state slot of each request
     logit_rows: torch.Tensor      # int32 [R]   flat rows whose logits are wanted
+    req_order: Optional[torch.Tensor] = None   # int32 [B] request rows ordered by their number of new tokens
     block_tables: List[torch.Tensor] = field(default_factory=list)   # per group int32 [B, width]
     # host copies, for launch decisions
     h_q_lens: Optional[np.ndarray] = None
     h_pos_start: Optional[np.ndarray] = None
+    h_sorted_q_lens: Optional[np.ndarray] = None     # q_lens in the order of req_order
     all_decode: bool = False      # every request brings exactly one token
     real_requests: int = 0        # requests that are not padding
     real_logit_rows: int = 0
@@ -83,8 +88,8 @@ class StepBatch:
 def batch_views(dev: torch.Tensor, layout: BatchLayout):
     """Slices of the packed device buffer, in the order of BatchLayout.sizes()."""
     offs, sizes = layout.offsets(), layout.sizes()
-    v = [dev[o:o + n] for o, n in zip(offs[:8], sizes[:8])]
-    bts = [dev[o:o + n].view(layout.B, w) for o, n, w in zip(offs[8:], sizes[8:], layout.widths)]
+    v = [dev[o:o + n] for o, n in zip(offs[:NUM_FLAT], sizes[:NUM_FLAT])]
+    bts = [dev[o:o + n].view(layout.B, w) for o, n, w in zip(offs[NUM_FLAT:], sizes[NUM_FLAT:], layout.widths)]
     return v, bts
 
 
@@ -137,12 +142,15 @@ def pack_step(entries: Sequence[StepEntry], starts: Sequence[int], slots: Sequen
     offs = layout.offsets()
     slot_arr = np.full(B, dummy_slot, dtype=np.int32)
     slot_arr[:nreal] = np.asarray(slots, dtype=np.int32)
-    for o, arr in zip(offs[:8], (token_ids, positions, tok_req, q_start, pos_start, kv_len, slot_arr,
-                                 np.asarray(rows, dtype=np.int32))):
+    # requests ordered by the number of tokens they bring (shortest first): kernels that treat
+    # single decoded tokens and long portions differently take a prefix or a suffix of this order
+    req_order = np.argsort(q_lens, kind="stable").astype(np.int32)
+    for o, arr in zip(offs[:NUM_FLAT], (token_ids, positions, tok_req, q_start, pos_start, kv_len, slot_arr,
+                                        np.asarray(rows, dtype=np.int32), req_order)):
         out[o:o + arr.shape[0]] = arr
     for g in range(G):
         w = layout.widths[g]
-        bt = out[offs[8 + g]:offs[8 + g] + B * w].reshape(B, w)
+        bt = out[offs[NUM_FLAT + g]:offs[NUM_FLAT + g] + B * w].reshape(B, w)
         bt[:nreal] = -1
         bt[nreal:] = dummy_pages[g] if dummy_pages is not None else -1
         for i, t in enumerate(tables[g]):
@@ -152,6 +160,7 @@ def pack_step(entries: Sequence[StepEntry], starts: Sequence[int], slots: Sequen
             if n:
                 bt[i, :n] = t
     info = dict(max_q_len=int(q_lens.max()), max_kv_len=int(kv_len.max()), q_lens=q_lens, pos_start=pos_start,
+                sorted_q_lens=q_lens[req_order],
                 all_decode=bool((q_lens == 1).all()), real_requests=nreal, real_logit_rows=real_rows)
     return out, layout, info
 
@@ -162,8 +171,9 @@ def batch_from_device(dev: torch.Tensor, layout: BatchLayout, info) -> StepBatch
         num_tokens=layout.T, num_requests=layout.B, num_logit_rows=layout.R,
         max_q_len=info["max_q_len"], max_kv_len=info["max_kv_len"],
         token_ids=v[0], positions=v[1], tok_req=v[2], q_start=v[3], pos_start=v[4], kv_len=v[5],
-        slots=v[6], logit_rows=v[7], block_tables=bts,
-        h_q_lens=info["q_lens"], h_pos_start=info["pos_start"], all_decode=info["all_decode"],
+        slots=v[6], logit_rows=v[7], req_order=v[8], block_tables=bts,
+        h_q_lens=info["q_lens"], h_pos_start=info["pos_start"], h_sorted_q_lens=info["sorted_q_lens"],
+        all_decode=info["all_decode"],
         real_requests=info["real_requests"], real_logit_rows=info["real_logit_rows"])
 
 

@@ -265,18 +265,35 @@ class CudaKernels:
 
     def attention_bf16(self, q, batch, block_table, kv_cache, kv_layer, page_size, out,
                        nq, nkv, d, scale, window, num_splits=None) -> None:
-        """Flash attention over the paged cache on mma.sync (head sizes 64 and 128)."""
+        """Flash attention over the paged cache (head sizes 64 and 128).  Requests that bring so few
+        tokens that they fit a 16-row tile (decoded tokens) and requests that bring long portions are
+        launched apart when a step holds both, each with the kernel made for it."""
+        G = nq // nkv
+        sq = batch.h_sorted_q_lens
+        B = batch.num_requests
+        n_short = int(np.searchsorted(sq, 16 // G, side="right")) if (sq is not None and num_splits is None) else 0
+        if 0 < n_short < B and batch.req_order is not None:
+            self._attention_bf16_launch(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, scale,
+                                        window, None, batch.req_order[:n_short], n_short, int(sq[n_short - 1]))
+            self._attention_bf16_launch(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, scale,
+                                        window, None, batch.req_order[n_short:], B - n_short, int(sq[-1]))
+        else:
+            self._attention_bf16_launch(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, scale,
+                                        window, num_splits, None, B, batch.max_q_len)
+
+    def _attention_bf16_launch(self, q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, scale,
+                               window, num_splits, req_ids, num_requests, max_q_len) -> None:
         T = q.shape[0]
-        splits = num_splits if num_splits is not None else self.attention_splits(
-            batch.num_requests, batch.max_q_len, nq, nkv)
+        splits = num_splits if num_splits is not None else self.attention_splits(num_requests, max_q_len, nq, nkv)
         ws = None
         if splits > 1:
             ws = torch.empty(T * nq * splits * (d + 2), dtype=torch.float32, device=q.device)
         self._check(self.lib.tff_attention_bf16_paged(
-            _ptr(q), _ptr(batch.q_start), _ptr(batch.pos_start), _ptr(block_table), _c_int(block_table.shape[1]),
+            _ptr(q), _ptr(batch.q_start), _ptr(batch.pos_start), _ptr(req_ids), _ptr(block_table),
+            _c_int(block_table.shape[1]),
             _ptr(kv_cache), ctypes.c_longlong(kv_cache.shape[0]), _c_int(kv_cache.shape[1]), _c_int(kv_layer),
             _c_int(page_size),
-            _ptr(out), _ptr(ws), _c_int(T), _c_int(batch.num_requests), _c_int(batch.max_q_len), _c_int(splits),
+            _ptr(out), _ptr(ws), _c_int(T), _c_int(num_requests), _c_int(max_q_len), _c_int(splits),
             _c_int(nq), _c_int(nkv), _c_int(d), _c_float(scale), _c_int(window), self._stream()), "attention_bf16")
         self.launches += 2 if splits > 1 else 1
 
