@@ -144,13 +144,14 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
          | ((uint32_t)(m >> 4) << 24);                // m_dim
 }
 
-template <int BN, bool TMA_OUT> struct TileCfg {
+template <int BN, bool TMA_OUT, bool SWAP = false> struct TileCfg {
     static constexpr int kStageBytes = BM * BK * 2 + BN * BK * 2;
-    static constexpr int kStages = BN >= 256 ? 4 : BN >= 128 ? 5 : (BN >= 64 ? 4 : 5);
-    static constexpr int kCtasPerSm = BN >= 128 ? 1 : 2;
+    static constexpr int kStages = BN >= 256 ? 4 : BN >= 128 ? 5 : (BN >= 64 ? 8 : (BN >= 32 ? 5 : 4));
+    static constexpr int kCtasPerSm = BN >= 64 ? 1 : (BN >= 32 ? 2 : 3);
     static constexpr int kAccCols = BN < 32 ? 32 : BN;              // columns of one accumulator buffer
     static constexpr int kTmemCols = 2 * kAccCols;                  // 64 .. 512, a power of two
-    static constexpr int kStagingBytes = TMA_OUT ? 4 * 2 * 4096 : 0;   // 4 warps x 2 buffers x (32 rows x 128 B)
+    // epilogue staging: 4 warps x (32 rows x 128 B); two buffers a warp in the normal orientation, one when swapped
+    static constexpr int kStagingBytes = TMA_OUT ? (SWAP ? 4 * 4096 : 4 * 2 * 4096) : 0;
     static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
@@ -188,14 +189,14 @@ struct SegIter {
 };
 
 // out element (m, n): normal -> lane operand row = m, column operand row = n; swapped -> the reverse.
-// TMA_OUT (normal orientation only): the epilogue goes through shared memory and TMA.
+// TMA_OUT: the epilogue goes through shared memory and TMA (stores, or float32 add-reductions).
 template <int BN, bool SWAP, int EPI, typename TC, bool TMA_OUT>
-__global__ void __launch_bounds__(NUM_THREADS, TileCfg<BN, TMA_OUT>::kCtasPerSm)
+__global__ void __launch_bounds__(NUM_THREADS, TileCfg<BN, TMA_OUT, SWAP>::kCtasPerSm)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_lane,   // operand whose rows land on TMEM lanes (box 64 x 128)
                const __grid_constant__ CUtensorMap tm_col,    // operand whose rows land on TMEM columns (box 64 x BN)
                const __grid_constant__ CUtensorMap tm_out,    // output, boxes of 128 bytes x 32 rows (TMA_OUT only)
                TC* __restrict__ out, int rows_lane, int rows_col, int K, int ldo, int stream_k, int* error_flag) {
-    using Cfg = TileCfg<BN, TMA_OUT>;
+    using Cfg = TileCfg<BN, TMA_OUT, SWAP>;
     constexpr int STAGES = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -325,7 +326,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_lane,   // operand whose r
             const int lane_row0 = (it.tile % n_lane_tiles) * BM, col_row0 = (it.tile / n_lane_tiles) * BN;
             const uint32_t t_addr = tmem_base + acc * Cfg::kAccCols + ((uint32_t)(q * 32) << 16);
             const bool partial = stream_k && (it.kb1 - it.kb0) < kbt;   // a share of the tile's K range: add
-            if constexpr (TMA_OUT) {
+            if constexpr (TMA_OUT && SWAP) {
+                // Swapped orientation, float32 out: the thread holds feature n = its TMEM lane for 16 tokens at a
+                // time.  A warp stages a box of 32 tokens x 32 features (one 128-byte row per token, written by the
+                // 32 lanes side by side, 16-byte chunks XOR-swizzled by token % 8) and one lane hands it to TMA:
+                // a store, or an add-reduction done in L2 when the product is added to ``out``.
+                const uint32_t buf = staging + (uint32_t)(warp - 2) * 4096u;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    if (lane == 0) bulk_wait_read<0>();        // the box staged before this one has been read
+                    __syncwarp();
+#pragma unroll
+                    for (int h = 0; h < (BN >= 32 ? 2 : 1); ++h) {
+                        uint32_t v[16];
+                        tmem_ld16(t_addr + (uint32_t)(c0 + h * 16), v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int m = h * 16 + j;              // token row of the box
+                            const uint32_t dst = buf + (uint32_t)m * 128u + (uint32_t)((((lane >> 2) ^ (m & 7)) << 4) + ((lane & 3) << 2));
+                            asm volatile("st.shared.b32 [%0], %1;" ::"r"(dst), "r"(v[j]) : "memory");
+                        }
+                    }
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        // rows of the box beyond M are clipped by TMA (with BN = 16 the box's upper half is never written)
+                        if (EPI == EPI_ADD || partial) tma_reduce_add_2d(&tm_out, buf, lane_row0 + q * 32, col_row0 + c0);
+                        else tma_store_2d(&tm_out, buf, lane_row0 + q * 32, col_row0 + c0);
+                        bulk_commit();
+                    }
+                }
+            } else if constexpr (TMA_OUT) {
                 // 128-byte-wide column chunks: 32 float32 or 64 bfloat16 per row
                 constexpr int CW = 128 / (int)sizeof(TC);      // output columns per chunk
                 constexpr int AW = EPI == EPI_SWIGLU ? 128 : CW;   // accumulator columns per chunk
@@ -442,7 +474,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_lane,   // operand whose r
 template <int BN, bool SWAP, int EPI, typename TC, bool TMA_OUT>
 int launch_tc(const CUtensorMap& tl, const CUtensorMap& tc, const CUtensorMap& to, void* out,
               int rows_lane, int rows_col, int K, int ldo, int stream_k, cudaStream_t stream) {
-    using Cfg = TileCfg<BN, TMA_OUT>;
+    using Cfg = TileCfg<BN, TMA_OUT, SWAP>;
     auto kern = gemm_tc_kernel<BN, SWAP, EPI, TC, TMA_OUT>;
     static bool configured = false;
     if (!configured) {
@@ -492,13 +524,16 @@ TFF_API int tff_gemm_tc(const void* A, const void* W, void* out, int out_is_bf16
     CUtensorMap tl, tc, to;
     if (!tff_tensor_map_2d(lane_ptr, rows_lane, K, BM, BK, 2, &tl)) return TFF_ERR_DRIVER;
     if (!tff_tensor_map_2d(col_ptr, rows_col, K, bn, BK, 2, &tc)) return TFF_ERR_DRIVER;
-    // TMA output: normal orientation, row pitch a multiple of 16 bytes, 16-byte aligned base
+    // TMA output: row pitch a multiple of 16 bytes, 16-byte aligned base
     const int elt = out_is_bf16 ? 2 : 4;
-    const bool tma_out = !swap && ((long long)N * elt) % 16 == 0 && ((uintptr_t)out & 15) == 0 && bn >= 128 / elt;
+    // (swapped: float32 only, boxes of 32 tokens x 32 features)
+    const bool tma_out = ((long long)N * elt) % 16 == 0 && ((uintptr_t)out & 15) == 0 &&
+                         (swap ? (!out_is_bf16 && bn >= 32) : bn >= 128 / elt);
     to = tl;
     if (tma_out && !tff_tensor_map_2d(out, M, N, 32, 128 / elt, elt, &to)) return TFF_ERR_DRIVER;
 #define TFF_CASE(BN_)                                                                                              \
     case BN_:                                                                                                      \
+        if (swap && tma_out) return dispatch_epi<BN_, true, true>(tl, tc, to, out, out_is_bf16, add, rows_lane, rows_col, K, N, stream_k, stream); \
         if (swap) return dispatch_epi<BN_, true, false>(tl, tc, to, out, out_is_bf16, add, rows_lane, rows_col, K, N, stream_k, stream); \
         if (tma_out) return dispatch_epi<BN_, false, true>(tl, tc, to, out, out_is_bf16, add, rows_lane, rows_col, K, N, stream_k, stream); \
         return dispatch_epi<BN_, false, false>(tl, tc, to, out, out_is_bf16, add, rows_lane, rows_col, K, N, stream_k, stream);
