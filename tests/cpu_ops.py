@@ -19,6 +19,9 @@ class CpuOps:
     def __init__(self):
         self.launches = 0
 
+    def projection_buffer(self, rows, width, device, act_dtype):
+        return torch.empty((rows, width), dtype=torch.float32, device=device)
+
     def embed(self, token_ids, table, out):
         out.copy_(table[token_ids.long()].to(torch.float32))
 

@@ -319,6 +319,50 @@ def test_prompt_attention_when_the_running_maximum_jumps_late(ops, nq, nkv, d, p
     ops.check_errors()
 
 
+def test_accumulator_buffers_are_left_at_zero_by_their_readers(ops):
+    """Decode-sized bfloat16 projections add their split shares into a persistent float32 buffer; the kernel
+    that reads the buffer clears it, so that no clearing kernel runs.  Two rounds through the same buffers."""
+    nq, nkv, d, page, H, I = 8, 2, 64, 16, 256, 320
+    W = (nq + 2 * nkv) * d
+    cpu = CpuOps()
+    table = torch.empty(128, d // 2, 2); cpu.rope_table(table, 1e4, d)
+    for rnd in range(2):
+        T = 5
+        h = g((T, H), torch.bfloat16, 80 + rnd)
+        w_qkv = g((W, H), torch.bfloat16, 82 + rnd, 0.05)
+        qkv = ops.projection_buffer(T, W, DEV, torch.bfloat16)
+        assert float(qkv.abs().max()) == 0.0
+        launches = ops.launches
+        ops.gemm(h.to(DEV), w_qkv.to(DEV), qkv)
+        assert ops.launches == launches + 1                       # no clearing kernel
+        ref = (h.double() @ w_qkv.double().t())
+        assert rel_err(qkv, ref) < 1e-5
+        entries = [StepEntry(0, [0] * T, [])]
+        tables = [[[3, 1]]]
+        bg = build_step_batch(entries, [7], [0], tables, DEV)
+        bc = build_step_batch(entries, [7], [0], tables, "cpu")
+        cache_g = torch.zeros((4, 1, 2, nkv, page, d), dtype=torch.bfloat16, device=DEV)
+        cache_c = torch.zeros((4, 1, 2, nkv, page, d), dtype=torch.bfloat16)
+        q_g = torch.empty(T, nq * d, dtype=torch.bfloat16, device=DEV)
+        q_c = torch.empty(T, nq * d, dtype=torch.bfloat16)
+        qkv_host = qkv.cpu().clone()
+        ops.qk_norm_rope_kv_write(qkv, q_g, None, None, 1e-6, table.to(DEV), d, bg, bg.block_tables[0], cache_g, 0, page,
+                                  nq, nkv, d, True)
+        cpu.qk_norm_rope_kv_write(qkv_host, q_c, None, None, 1e-6, table, d, bc, bc.block_tables[0], cache_c, 0, page,
+                                  nq, nkv, d, True)
+        assert rel_err(q_g, q_c) < 1e-2 and rel_err(cache_g, cache_c) < 1e-2
+        assert float(qkv.abs().max()) == 0.0                      # cleared by its reader
+        # gate/up accumulators, cleared by the SwiGLU kernel
+        a = g((T, H), torch.bfloat16, 84 + rnd)
+        wg, wu = g((I, H), torch.bfloat16, 86 + rnd, 0.05), g((I, H), torch.bfloat16, 88 + rnd, 0.05)
+        out = torch.empty(T, I, dtype=torch.bfloat16, device=DEV)
+        ops.gemm_swiglu(a.to(DEV), ops.merge_gate_up(wg.to(DEV), wu.to(DEV)), out)
+        gate, up = a.double() @ wg.double().t(), a.double() @ wu.double().t()
+        assert rel_err(out, (gate / (1 + torch.exp(-gate))) * up) < 1.2e-2
+        assert float(ops.projection_buffer(T, 2 * I, DEV, torch.bfloat16).abs().max()) == 0.0
+    ops.check_errors()
+
+
 def test_attention_finds_one_far_key_among_hundreds(ops):
     """One key far back is made to dominate: a kernel that skips a page, or reads the wrong
     one, returns something else than that key's value."""

@@ -69,8 +69,10 @@ TFF_API int tff_rmsnorm(const float* x, const float* w, const int* row_index, vo
 // (src/kernel/cuda/unary.cu:10-27: x1 = gate, x2 = up).
 // ``block`` = 0: gu[t] = [gate (I) | up (I)]; ``block`` = b > 0: gate and up alternate in blocks of b
 // columns, gate feature i at column (i / b) * 2b + i % b and its up feature b columns further.
+// ``clear`` != 0: the input is set to zero once it has been read (it is an accumulator buffer the
+// next split product adds into).
 template <typename TIN, typename T>
-__global__ void swiglu_kernel(const TIN* __restrict__ gu, T* __restrict__ out, long long total, int inter, int block) {
+__global__ void swiglu_kernel(TIN* __restrict__ gu, T* __restrict__ out, long long total, int inter, int block, int clear) {
     pdl_launch_dependents();          // the next kernel may become resident (it waits before it reads or writes)
     pdl_wait();
     for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -82,20 +84,21 @@ __global__ void swiglu_kernel(const TIN* __restrict__ gu, T* __restrict__ out, l
         const float g = to_f32<TIN>(gu[t * 2 * inter + gc]);
         const float u = to_f32<TIN>(gu[t * 2 * inter + uc]);
         out[idx] = from_f32<T>((g / (1.0f + expf(-g))) * u);
+        if (clear) { gu[t * 2 * inter + gc] = from_f32<TIN>(0.f); gu[t * 2 * inter + uc] = from_f32<TIN>(0.f); }
     }
 }
 
 // dtype codes: 0 = float32, 1 = bfloat16; the input may be float32 with a bfloat16 output.
-TFF_API int tff_swiglu(const void* gu, int in_dt, void* out, int out_dt, int rows, int inter, int block,
+TFF_API int tff_swiglu(void* gu, int in_dt, void* out, int out_dt, int rows, int inter, int block, int clear,
                        cudaStream_t stream) {
     if (rows <= 0) return TFF_OK;
     if (inter <= 0 || block < 0 || (block > 0 && inter % block != 0)) return TFF_ERR_BAD_ARGUMENT;
     const long long total = (long long)rows * inter;
     const int nt = 256;
     const int blocks = (int)((total + nt - 1) / nt < 148 * 16 ? (total + nt - 1) / nt : 148 * 16);
-    if (in_dt == 1 && out_dt == 1) return tff_launch_pdl(swiglu_kernel<bf16, bf16>, blocks, nt, 0, stream, (const bf16*)gu, (bf16*)out, total, inter, block);
-    if (in_dt == 0 && out_dt == 1) return tff_launch_pdl(swiglu_kernel<float, bf16>, blocks, nt, 0, stream, (const float*)gu, (bf16*)out, total, inter, block);
-    if (in_dt == 0 && out_dt == 0) return tff_launch_pdl(swiglu_kernel<float, float>, blocks, nt, 0, stream, (const float*)gu, (float*)out, total, inter, block);
+    if (in_dt == 1 && out_dt == 1) return tff_launch_pdl(swiglu_kernel<bf16, bf16>, blocks, nt, 0, stream, (bf16*)gu, (bf16*)out, total, inter, block, clear);
+    if (in_dt == 0 && out_dt == 1) return tff_launch_pdl(swiglu_kernel<float, bf16>, blocks, nt, 0, stream, (float*)gu, (bf16*)out, total, inter, block, clear);
+    if (in_dt == 0 && out_dt == 0) return tff_launch_pdl(swiglu_kernel<float, float>, blocks, nt, 0, stream, (float*)gu, (float*)out, total, inter, block, clear);
     return TFF_ERR_BAD_ARGUMENT;
 }
 
@@ -134,7 +137,7 @@ TFF_API int tff_rope_table(float* table, const float* inv_freq, int max_pos, int
 // src/kernel/cuda/set_row.cu:72-123.  Unlike the reference, keys are stored rotated.
 template <typename TIN, typename T>
 __global__ void qk_norm_rope_kv_write_kernel(
-    const TIN* __restrict__ qkv, T* __restrict__ q_out,
+    TIN* __restrict__ qkv, int clear_input, T* __restrict__ q_out,
     const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
     const float2* __restrict__ table, int rot_dim,
     const int* __restrict__ positions, const int* __restrict__ tok_req,
@@ -149,8 +152,11 @@ __global__ void qk_norm_rope_kv_write_kernel(
     const int heads = nq + 2 * nkv;
     if (head >= heads) return;
     const bool is_q = head < nq, is_k = !is_q && head < nq + nkv;
-    if (!is_q && !write_cache) return;
-    const TIN* src = qkv + (size_t)t * heads * d + (size_t)head * d;
+    TIN* src = qkv + (size_t)t * heads * d + (size_t)head * d;
+    if (!is_q && !write_cache) {
+        if (clear_input) for (int i = lane; i < d; i += 32) src[i] = from_f32<TIN>(0.f);
+        return;
+    }
     const int pos = positions[t];
 
     T* dst;
@@ -160,12 +166,18 @@ __global__ void qk_norm_rope_kv_write_kernel(
         const int kvh = is_k ? head - nq : head - nq - nkv;
         const int b = tok_req[t];
         const int page = block_table[(size_t)b * table_width + pos / L.page_size];
-        if (page < 0) return;                 // no page: the host never schedules this; write nothing
+        if (page < 0) {                       // no page: the host never schedules this; write nothing
+            if (clear_input) for (int i = lane; i < d; i += 32) src[i] = from_f32<TIN>(0.f);
+            return;
+        }
         dst = cache + (size_t)page * L.page_stride + (size_t)layer * L.layer_stride +
               (is_k ? 0 : L.kv_stride) + (size_t)kvh * L.head_stride + (size_t)(pos % L.page_size) * d;
     }
     if (!is_q && !is_k) {                     // V: plain copy
-        for (int i = lane; i < d; i += 32) dst[i] = from_f32<T>(to_f32<TIN>(src[i]));
+        for (int i = lane; i < d; i += 32) {
+            dst[i] = from_f32<T>(to_f32<TIN>(src[i]));
+            if (clear_input) src[i] = from_f32<TIN>(0.f);
+        }
         return;
     }
     const float* w = is_q ? q_w : k_w;
@@ -196,11 +208,19 @@ __global__ void qk_norm_rope_kv_write_kernel(
         if (w) a = (a * rs) * w[i];
         dst[i] = from_f32<T>(a);
     }
+    if (clear_input) {
+        // every lane has read what it needs of the row (the stores above follow the loads in program
+        // order, and a lane only ever reads the elements it clears or their rotation partners, which it
+        // has already consumed): the accumulator row goes back to zero for the next split product
+        __syncwarp();
+        for (int i = lane; i < d; i += 32) src[i] = from_f32<TIN>(0.f);
+    }
 }
 
 // in_is_f32: the projection row is float32 (else it has the activation type given by is_bf16).
+// clear_input != 0: the projection row is set to zero once it has been read.
 TFF_API int tff_qk_norm_rope_kv_write(
-    const void* qkv, int in_is_f32, void* q_out, int is_bf16, const float* q_w, const float* k_w, float eps,
+    void* qkv, int in_is_f32, int clear_input, void* q_out, int is_bf16, const float* q_w, const float* k_w, float eps,
     const float* table, int rot_dim, int max_pos,
     const int* positions, const int* tok_req, const int* block_table, int table_width,
     void* cache, int cache_layers, int layer, int page_size, int write_cache,
@@ -214,7 +234,7 @@ TFF_API int tff_qk_norm_rope_kv_write(
     dim3 grid((heads + warps - 1) / warps, num_tokens);
 #define TFF_QK_LAUNCH(TIN, T)                                                                                  \
     tff_launch_pdl(qk_norm_rope_kv_write_kernel<TIN, T>, grid, warps * 32, 0, stream,                          \
-        (const TIN*)qkv, (T*)q_out, q_w, k_w, eps, (const float2*)table, rot_dim, positions, tok_req,          \
+        (TIN*)qkv, clear_input, (T*)q_out, q_w, k_w, eps, (const float2*)table, rot_dim, positions, tok_req,          \
         block_table, table_width, (T*)cache, L, layer, write_cache, nq, nkv, d, max_pos)
     if (is_bf16) {
         if (in_is_f32) return TFF_QK_LAUNCH(float, bf16);

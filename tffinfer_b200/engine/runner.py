@@ -250,8 +250,14 @@ class ModelRunner:
         return st["logits"][:batch.real_logit_rows]
 
     def _forward(self, batch: StepBatch) -> torch.Tensor:
-        return self.model.forward(batch, self.ops, self.act_dtype, self.bindings, self.kv_caches,
-                                  batch.block_tables, self.ecfg.page_size, self.states)
+        try:
+            return self.model.forward(batch, self.ops, self.act_dtype, self.bindings, self.kv_caches,
+                                      batch.block_tables, self.ecfg.page_size, self.states)
+        except Exception:
+            reset = getattr(self.ops, "reset_accumulators", None)
+            if reset is not None:
+                reset()            # a step cut short may leave accumulator buffers half used
+            raise
 
     def run_batch(self, batch: StepBatch) -> torch.Tensor:
         if getattr(batch, "graph_bucket", None) is not None:

@@ -62,6 +62,8 @@ class CudaKernels:
             raise KernelError(f"cannot load the kernel library {path}: {e}") from None
         self.path = path
         self.launches = 0          # number of kernel launches issued through this object
+        self._accumulators = {}    # (shape, device) -> float32 buffer kept at zero between uses
+        self._acc_zero = {}        # data_ptr -> True while the buffer is known to hold zeros
         self._inv_freq_cache = {}
 
     # ------------------------------------------------------------- plumbing
@@ -157,7 +159,10 @@ class CudaKernels:
             add = 1
         elif stream_k:
             assert out.dtype == torch.float32
-            self.zero_f32(out)                # shares of a split tile are added to it
+            if not self._acc_zero.get(out.data_ptr(), False):
+                self.zero_f32(out)            # shares of a split tile are added to it
+        if out.data_ptr() in self._acc_zero:
+            self._acc_zero[out.data_ptr()] = False
         self._check(self.lib.tff_gemm_tc(_ptr(a), _ptr(w), _ptr(out), _c_int(_dt(out)), _c_int(add),
                                          _c_int(M), _c_int(N), _c_int(K), _c_int(swap), _c_int(bn), _c_int(stream_k),
                                          self._stream()), "gemm_tc")
@@ -188,14 +193,39 @@ class CudaKernels:
             return torch.cat([gate_w, up_w], dim=0).contiguous()
         return torch.stack([gate_w.view(I // b, b, K), up_w.view(I // b, b, K)], dim=1).reshape(2 * I, K).contiguous()
 
+    # ------------------------------------------------------- accumulator buffers
+    def projection_buffer(self, rows: int, width: int, device, act_dtype) -> torch.Tensor:
+        """A float32 [rows, width] buffer for a projection's accumulators.  For decode-sized bfloat16
+        batches it is a persistent buffer that is zero now and that its reader sets back to zero
+        (``release_input`` of qk_norm_rope_kv_write, ``clear`` of swiglu), so that the split product
+        can add into it without a clearing kernel; otherwise it is plain scratch."""
+        if act_dtype != torch.bfloat16 or rows > self.SWAP_MAX_M:
+            return torch.empty((rows, width), dtype=torch.float32, device=device)
+        key = (rows, width, str(device))
+        buf = self._accumulators.get(key)
+        if buf is None:
+            buf = torch.zeros((rows, width), dtype=torch.float32, device=device)
+            self._accumulators[key] = buf
+            self._acc_zero[buf.data_ptr()] = True
+        return buf
+
+    def reset_accumulators(self) -> None:
+        """After a step that was cut short: every accumulator buffer back to zero."""
+        for buf in self._accumulators.values():
+            buf.zero_()
+            self._acc_zero[buf.data_ptr()] = True
+
     def swiglu(self, gate_up, out, block: int = 0) -> None:
         """out[t, i] = silu(gate[t, i]) * up[t, i]; gate_up float32 or of out's type, [gate | up] (block = 0) or
         alternating in blocks of ``block`` columns."""
         self._need_cuda(gate_up, out)
         T, I = out.shape
         assert gate_up.shape == (T, 2 * I) and gate_up.dtype in (torch.float32, out.dtype)
+        clear = 1 if gate_up.data_ptr() in self._acc_zero else 0
         self._check(self.lib.tff_swiglu(_ptr(gate_up), _c_int(_dt(gate_up)), _ptr(out), _c_int(_dt(out)),
-                                        _c_int(T), _c_int(I), _c_int(block), self._stream()), "swiglu")
+                                        _c_int(T), _c_int(I), _c_int(block), _c_int(clear), self._stream()), "swiglu")
+        if clear:
+            self._acc_zero[gate_up.data_ptr()] = True
         self.launches += 1
 
     def rope_table(self, table, theta: float, rot_dim: int) -> None:
@@ -225,14 +255,17 @@ class CudaKernels:
             assert kv_cache is not None and kv_cache.dtype == q_out.dtype, "cache dtype must match activations"
             assert tuple(kv_cache.shape[2:]) == (2, nkv, page_size, d)
         layers = kv_cache.shape[1] if kv_cache is not None else 1
+        clear = 1 if qkv.data_ptr() in self._acc_zero else 0
         self._check(self.lib.tff_qk_norm_rope_kv_write(
-            _ptr(qkv), _c_int(1 if qkv.dtype == torch.float32 else 0), _ptr(q_out), _c_int(_dt(q_out)),
+            _ptr(qkv), _c_int(1 if qkv.dtype == torch.float32 else 0), _c_int(clear), _ptr(q_out), _c_int(_dt(q_out)),
             _ptr(q_w), _ptr(k_w), _c_float(eps),
             _ptr(table), _c_int(rot_dim), _c_int(table.shape[0] if table is not None else 0),
             _ptr(batch.positions), _ptr(batch.tok_req), _ptr(block_table),
             _c_int(block_table.shape[1] if block_table is not None else 0),
             _ptr(kv_cache), _c_int(layers), _c_int(kv_layer), _c_int(page_size), _c_int(1 if write_cache else 0),
             _c_int(T), _c_int(nq), _c_int(nkv), _c_int(d), self._stream()), "qk_norm_rope_kv_write")
+        if clear:
+            self._acc_zero[qkv.data_ptr()] = True
         self.launches += 1
 
     def attention(self, q, batch, block_table, kv_cache, kv_layer, page_size, out,
@@ -323,7 +356,10 @@ class CudaKernels:
             self.launches += 1
             return
         small = tc and T <= self.SWAP_MAX_M
-        gu = torch.empty((T, 2 * I), dtype=torch.float32 if small else out.dtype, device=out.device)
+        if small:
+            gu = self.projection_buffer(T, 2 * I, out.device, out.dtype)
+        else:
+            gu = torch.empty((T, 2 * I), dtype=out.dtype, device=out.device)
         self.gemm(a, w_gate_up, gu)
         self.swiglu(gu, out, block)
     def argmax(self, logits, out) -> None:

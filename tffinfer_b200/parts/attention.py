@@ -73,7 +73,7 @@ class GQAttention(Mixer):
         ops, batch = ctx.ops, ctx.batch
         T = h.shape[0]
         # the projection's accumulators stay in float32 until q and k have been normalised
-        qkv = torch.empty((T, self.q_width + 2 * self.kv_width), dtype=torch.float32, device=h.device)
+        qkv = ops.projection_buffer(T, self.q_width + 2 * self.kv_width, h.device, h.dtype)
         ops.gemm(h, self.w_qkv, qkv)
         q = torch.empty((T, self.q_width), dtype=h.dtype, device=h.device)
         rot = ctx.position.rotary() if ctx.position is not None else None
