@@ -218,6 +218,79 @@ __global__ void qk_norm_rope_kv_write_kernel(
 }
 
 // in_is_f32: the projection row is float32 (else it has the activation type given by is_bf16).
+// The same for head size 128 with the whole head rotated (the common case): a lane owns four
+// consecutive elements (one 16-byte load of float32 accumulators), its rotation partner is lane ^ 16.
+template <typename T> __device__ __forceinline__ void store4(T* p, float a, float b, float c, float d);
+template <> __device__ __forceinline__ void store4<float>(float* p, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+template <> __device__ __forceinline__ void store4<bf16>(bf16* p, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 v;
+    v.x = *reinterpret_cast<uint32_t*>(&lo);
+    v.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = v;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+qk_norm_rope_kv_write_d128_kernel(
+    float* __restrict__ qkv, int clear_input, T* __restrict__ q_out,
+    const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+    const float2* __restrict__ table,
+    const int* __restrict__ positions, const int* __restrict__ tok_req,
+    const int* __restrict__ block_table, int table_width,
+    T* __restrict__ cache, KvLayout L, int layer, int write_cache, int nq, int nkv, int max_pos) {
+    pdl_launch_dependents();
+    pdl_wait();
+    constexpr int d = 128;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.y;
+    const int head = blockIdx.x * 8 + warp;
+    const int heads = nq + 2 * nkv;
+    if (head >= heads) return;
+    const bool is_q = head < nq, is_k = !is_q && head < nq + nkv;
+    float* src = qkv + (size_t)t * heads * d + (size_t)head * d + lane * 4;
+    const float4 x = *reinterpret_cast<const float4*>(src);
+    if (clear_input) *reinterpret_cast<float4*>(src) = make_float4(0.f, 0.f, 0.f, 0.f);   // this lane alone reads these four
+    if (!is_q && !write_cache) return;
+    const int pos = positions[t];
+    T* dst;
+    if (is_q) {
+        dst = q_out + (size_t)t * nq * d + (size_t)head * d + lane * 4;
+    } else {
+        const int kvh = is_k ? head - nq : head - nq - nkv;
+        const int page = block_table[(size_t)tok_req[t] * table_width + pos / L.page_size];
+        if (page < 0) return;
+        dst = cache + (size_t)page * L.page_stride + (size_t)layer * L.layer_stride +
+              (is_k ? 0 : L.kv_stride) + (size_t)kvh * L.head_stride + (size_t)(pos % L.page_size) * d + lane * 4;
+    }
+    if (!is_q && !is_k) { store4<T>(dst, x.x, x.y, x.z, x.w); return; }
+    const float* w = is_q ? q_w : k_w;
+    float n0 = x.x, n1 = x.y, n2 = x.z, n3 = x.w;
+    if (w) {
+        float ss = fmaf(x.x, x.x, fmaf(x.y, x.y, fmaf(x.z, x.z, x.w * x.w)));
+        ss = warp_sum(ss);
+        const float rs = rsqrtf(ss / (float)d + eps);
+        const float4 wv = *reinterpret_cast<const float4*>(w + lane * 4);
+        n0 = (x.x * rs) * wv.x; n1 = (x.y * rs) * wv.y; n2 = (x.z * rs) * wv.z; n3 = (x.w * rs) * wv.w;
+    }
+    if (table != nullptr && pos >= 0 && pos < max_pos) {
+        const float p0 = __shfl_xor_sync(0xffffffffu, n0, 16), p1 = __shfl_xor_sync(0xffffffffu, n1, 16);
+        const float p2 = __shfl_xor_sync(0xffffffffu, n2, 16), p3 = __shfl_xor_sync(0xffffffffu, n3, 16);
+        const float4* cs = reinterpret_cast<const float4*>(table + (size_t)pos * 64 + (lane & 15) * 4);
+        const float4 c01 = cs[0], c23 = cs[1];                 // (cos0, sin0, cos1, sin1), (cos2, sin2, cos3, sin3)
+        if (lane < 16) {                                        // first half: a cos - b sin, b = partner
+            n0 = n0 * c01.x - p0 * c01.y; n1 = n1 * c01.z - p1 * c01.w;
+            n2 = n2 * c23.x - p2 * c23.y; n3 = n3 * c23.z - p3 * c23.w;
+        } else {                                                // second half: a sin + b cos, a = partner
+            n0 = p0 * c01.y + n0 * c01.x; n1 = p1 * c01.w + n1 * c01.z;
+            n2 = p2 * c23.y + n2 * c23.x; n3 = p3 * c23.w + n3 * c23.z;
+        }
+    }
+    store4<T>(dst, n0, n1, n2, n3);
+}
+
 // clear_input != 0: the projection row is set to zero once it has been read.
 TFF_API int tff_qk_norm_rope_kv_write(
     void* qkv, int in_is_f32, int clear_input, void* q_out, int is_bf16, const float* q_w, const float* k_w, float eps,
@@ -230,6 +303,17 @@ TFF_API int tff_qk_norm_rope_kv_write(
     if (write_cache && (cache == nullptr || block_table == nullptr || page_size <= 0)) return TFF_ERR_BAD_ARGUMENT;
     const KvLayout L = make_kv_layout(cache_layers, nkv, page_size > 0 ? page_size : 1, d);
     const int heads = nq + 2 * nkv;
+    if (d == 128 && in_is_f32 && (table == nullptr || rot_dim == 128) && ((uintptr_t)qkv & 15) == 0 &&
+        ((uintptr_t)q_out & 15) == 0 && ((uintptr_t)cache & 15) == 0) {
+        dim3 grid8((heads + 7) / 8, num_tokens);
+        if (is_bf16)
+            return tff_launch_pdl(qk_norm_rope_kv_write_d128_kernel<bf16>, grid8, dim3(256), 0, stream, (float*)qkv,
+                                  clear_input, (bf16*)q_out, q_w, k_w, eps, (const float2*)table, positions, tok_req,
+                                  block_table, table_width, (bf16*)cache, L, layer, write_cache, nq, nkv, max_pos);
+        return tff_launch_pdl(qk_norm_rope_kv_write_d128_kernel<float>, grid8, dim3(256), 0, stream, (float*)qkv,
+                              clear_input, (float*)q_out, q_w, k_w, eps, (const float2*)table, positions, tok_req,
+                              block_table, table_width, (float*)cache, L, layer, write_cache, nq, nkv, max_pos);
+    }
     const int warps = 4;
     dim3 grid((heads + warps - 1) / warps, num_tokens);
 #define TFF_QK_LAUNCH(TIN, T)                                                                                  \

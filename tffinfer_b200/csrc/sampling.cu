@@ -168,9 +168,74 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
 
 }  // namespace
 
-TFF_API int tff_argmax(const float* logits, int* out, int rows, int vocab, cudaStream_t stream) {
+// Greedy choice with the vocabulary cut into shares, one CTA a share, for few rows of a large
+// vocabulary (one CTA a row would leave the GPU idle).  The shares write (value, index) candidates
+// into ``scratch`` (rows * shares pairs); the last share of a row to finish -- a ticket counter per
+// row, reset for the next call -- picks the first maximum among them.
+constexpr int ARGMAX_SHARES = 16;
+__global__ void __launch_bounds__(256)
+argmax_split_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab,
+                    float* __restrict__ cand_val, int* __restrict__ cand_idx, unsigned* __restrict__ tickets) {
+    __shared__ float sval[8];
+    __shared__ int sidx[8];
+    __shared__ bool last;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.y, share = blockIdx.x;
+    const int per = (vocab + ARGMAX_SHARES - 1) / ARGMAX_SHARES;
+    const int lo = share * per, hi = min(vocab, lo + per);
+    const float* row = logits + (size_t)r * vocab;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = lo + threadIdx.x; i < hi; i += 256) {
+        const float v = row[i];
+        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { sval[warp] = best; sidx[warp] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w)
+            if (sval[w] > best || (sval[w] == best && sidx[w] < bi)) { best = sval[w]; bi = sidx[w]; }
+        cand_val[r * ARGMAX_SHARES + share] = best;
+        cand_idx[r * ARGMAX_SHARES + share] = bi;
+        __threadfence();
+        last = atomicAdd(&tickets[r], 1u) == ARGMAX_SHARES - 1;
+    }
+    __syncthreads();
+    if (last && threadIdx.x == 0) {
+        __threadfence();
+        float b = -INFINITY;
+        int id = 0x7fffffff;
+        for (int s2 = 0; s2 < ARGMAX_SHARES; ++s2) {
+            const float v = cand_val[r * ARGMAX_SHARES + s2];
+            const int i = cand_idx[r * ARGMAX_SHARES + s2];
+            if (v > b || (v == b && i < id)) { b = v; id = i; }
+        }
+        out[r] = id == 0x7fffffff ? 0 : id;
+        tickets[r] = 0;
+    }
+}
+
+// ``scratch`` (may be null): (64 + 2 * 64 * 16) 32-bit words, the first 64 of them zero before the
+// first call (the kernel leaves them zero); with it, up to 64 rows of a large vocabulary are searched
+// by 16 CTAs each.
+TFF_API int tff_argmax(const float* logits, int* out, int rows, int vocab, void* scratch, cudaStream_t stream) {
     if (rows <= 0) return TFF_OK;
     if (vocab <= 0) return TFF_ERR_BAD_ARGUMENT;
+    if (scratch != nullptr && vocab >= 16384 && rows <= 64) {
+        unsigned* tickets = (unsigned*)scratch;                       // 64 counters, zero between calls
+        float* cand_val = (float*)(tickets + 64);                     // 64 x 16 values
+        int* cand_idx = (int*)(cand_val + 64 * ARGMAX_SHARES);        // 64 x 16 indices
+        return tff_launch_pdl(argmax_split_kernel, dim3(ARGMAX_SHARES, rows), dim3(256), 0, stream, logits, out, vocab,
+                              cand_val, cand_idx, tickets);
+    }
     return tff_launch_pdl(argmax_kernel, rows, NT, 0, stream, logits, out, vocab);
 }
 

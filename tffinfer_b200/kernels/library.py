@@ -366,7 +366,13 @@ class CudaKernels:
         self._need_cuda(logits, out)
         R, V = logits.shape
         assert logits.dtype == torch.float32 and out.dtype == torch.int32 and out.numel() == R
-        self._check(self.lib.tff_argmax(_ptr(logits), _ptr(out), _c_int(R), _c_int(V), self._stream()), "argmax")
+        scratch = getattr(self, "_argmax_scratch", None)
+        if scratch is None or scratch.device != logits.device:
+            # 64 ticket counters (kept at zero by the kernel), then the candidates of 16 shares for up to 64 rows
+            scratch = torch.zeros(64 + 2 * 64 * 16, dtype=torch.int32, device=logits.device)
+            self._argmax_scratch = scratch
+        use = scratch
+        self._check(self.lib.tff_argmax(_ptr(logits), _ptr(out), _c_int(R), _c_int(V), _ptr(use), self._stream()), "argmax")
         self.launches += 1
 
     def sample(self, logits, temperature, uniform, out, top_k=None, top_p=None, min_p=None) -> None:
