@@ -71,6 +71,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm,
         ::"r"(dst), "l"(tm), "r"(bar), "r"(x), "r"(y) : "memory");
 }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// 2^x on the special-function unit (float32 in and out; 2^-inf = 0)
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -331,14 +337,23 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const Prefi
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(s_empty(sb));               // the S buffer may be overwritten
-            float m_blk = -INFINITY;
+            // Scores stay unscaled in registers; the scale (> 0) is folded into the exponent below.  Key
+            // blocks that every row of the warp sees whole need no mask.
+            float m_raw = -INFINITY;
+            const int n_first = blk * BLOCK_N;
+            if (__all_sync(0xffffffffu, rv && n_first + BLOCK_N - 1 <= pr && n_first >= lo_r)) {
 #pragma unroll
-            for (int i = 0; i < BLOCK_N; ++i) {
-                const int n = blk * BLOCK_N + i;
-                const bool vis = rv && n <= pr && n >= lo_r;
-                s[i] = vis ? s[i] * p.scale_log2 : -INFINITY;
-                m_blk = fmaxf(m_blk, s[i]);
+                for (int i = 0; i < BLOCK_N; ++i) m_raw = fmaxf(m_raw, s[i]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < BLOCK_N; ++i) {
+                    const int n = n_first + i;
+                    const bool vis = rv && n <= pr && n >= lo_r;
+                    s[i] = vis ? s[i] : -INFINITY;
+                    m_raw = fmaxf(m_raw, s[i]);
+                }
             }
+            const float m_blk = m_raw * p.scale_log2;
             // lazy rescale: only when the maximum has grown by more than the threshold (warp-uniform decision)
             const bool grow = m_blk > m_used + RESCALE_THRESHOLD || (m_used == -INFINITY && m_blk > -INFINITY);
             if (__any_sync(0xffffffffu, grow)) {
@@ -376,10 +391,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const Prefi
                 uint32_t w[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const float e0 = exp2f(s[c * 8 + 2 * i] - ms), e1 = exp2f(s[c * 8 + 2 * i + 1] - ms);
+                    const float e0 = ex2_approx(fmaf(s[c * 8 + 2 * i], p.scale_log2, -ms));
+                    const float e1 = ex2_approx(fmaf(s[c * 8 + 2 * i + 1], p.scale_log2, -ms));
                     __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
-                    // the sum uses the rounded values, which are what the PV product multiplies
-                    lsum += __bfloat162float(b2.x) + __bfloat162float(b2.y);
+                    lsum += e0 + e1;
                     w[i] = *reinterpret_cast<uint32_t*>(&b2);
                 }
                 *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -452,7 +467,7 @@ int tff_attention_prefill_launch(
     void* out, int num_requests, int max_q_len, int nq, int nkv, int d, float scale, int window, cudaStream_t stream) {
     if (d != 64 && d != 128) return TFF_ERR_UNSUPPORTED;
     if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64) return TFF_ERR_UNSUPPORTED;
-    if (cache_pages <= 0) return TFF_ERR_UNSUPPORTED;
+    if (cache_pages <= 0 || !(scale > 0.f)) return TFF_ERR_UNSUPPORTED;     // the kernel folds a positive scale into the exponent
     if (((uintptr_t)cache & 15) || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) || (nq * d) % 8) return TFF_ERR_UNSUPPORTED;
     const long long rows = cache_pages * cache_layers * 2 * nkv * page_size;
     if (rows >= (1ll << 31) || num_requests > 65535 || nkv > 65535) return TFF_ERR_UNSUPPORTED;
