@@ -57,3 +57,21 @@ def test_cut_modes_match_plain(plain_logits, name, mode, dtype):
                              f"(rel err {bad[1]:.3e}) of {len(reqs[r])}")
         assert torch.isfinite(got[r]).all()
     assert all(p.num_free == p.num_pages for p in runner.cache.pools)
+
+
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_weights_stored_in_32_bits_stay_so_when_serving_in_bfloat16(tmp_path, name):
+    """A model folder whose tensors are float32: in the bfloat16 mode they are not narrowed (the products
+    with them run on the FFMA kernel), activations and cache are bfloat16, and the logits still follow the
+    plain implementation."""
+    d = make_model_dir(tmp_path, name, store_dtype="float32")
+    reqs = make_requests(name)
+    pm = PlainModel(d)
+    pool, steps = _steps(name, "portions", reqs)
+    runner = ModelRunner(d, EngineConfig(dtype="bfloat16", page_size=PAGE_SIZE[name], max_cache_tokens=pool,
+                                         max_live_requests=4, use_cuda_graphs=False))
+    assert runner.model.lm_head.dtype == torch.float32 and runner.kv_caches[0].dtype == torch.bfloat16
+    got = run_trace(runner, reqs, steps)
+    for r, t in reqs.items():
+        bad = first_bad(got[r], pm.logits(t), TOL["bfloat16"])
+        assert bad is None, (name, r, bad)
