@@ -64,7 +64,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
             return
@@ -166,9 +166,7 @@ def decode_run(engine, batch: int, steps: int, warmup: int, seed: int, sampler=N
     ops.check_errors()
     h2d = engine.runner.last_h2d_bytes
     for i in ids:                                   # stop the requests and give their pages back
-        r = engine.requests.pop(i)
-        if r.status == "running":
-            engine.scheduler._finish(r, "abort", release=True)
+        engine.abort(i)
     return {"tok_s": batch * steps / (dev_ms / 1e3), "ms_per_step": dev_ms / steps,
             "e2e_tok_s": batch * steps / wall, "launches": launches, "mean_context": (ctx0 + ctx1) / 2,
             "h2d_bytes": h2d, "d2h_bytes": 4 * batch}

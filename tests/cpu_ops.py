@@ -22,6 +22,10 @@ class CpuOps:
     def projection_buffer(self, rows, width, device, act_dtype):
         return torch.empty((rows, width), dtype=torch.float32, device=device)
 
+    def gather_tokens(self, token_ids, drawn, src):
+        m = src >= 0
+        token_ids[m] = drawn[src[m].long()]
+
     def embed(self, token_ids, table, out):
         out.copy_(table[token_ids.long()].to(torch.float32))
 

@@ -349,3 +349,21 @@ TFF_API int tff_zero_f32(float* p, long long n, cudaStream_t stream) {
     if (blocks > 148 * 8) blocks = 148 * 8;
     return tff_launch_pdl(zero_f32_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, (float4*)p, p + n4 * 4, n4, ntail);
 }
+
+// ------------------------------------------------------------ token hand-over
+// token_ids[i] = drawn[src[i]] where src[i] >= 0: the tokens a step drew go into the next step's
+// batch on the device, without a round trip through the host.
+__global__ void gather_tokens_kernel(int* __restrict__ token_ids, const int* __restrict__ drawn,
+                                     const int* __restrict__ src, int n, int num_drawn) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int s = src[i];
+    if (s >= 0 && s < num_drawn) token_ids[i] = drawn[s];
+}
+
+TFF_API int tff_gather_tokens(int* token_ids, const int* drawn, const int* src, int n, int num_drawn, cudaStream_t stream) {
+    if (n <= 0) return TFF_OK;
+    return tff_launch_pdl(gather_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, token_ids, drawn, src, n, num_drawn);
+}

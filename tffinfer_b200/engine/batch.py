@@ -28,9 +28,11 @@ class StepEntry:
     req: object
     tokens: Sequence[int]
     want: Sequence[int] = ()
+    token_src: Optional[Sequence[int]] = None    # per token: row of the previous step's drawn tokens to take the
+                                                 # id from on the device, or -1 for the id given in ``tokens``
 
 
-NUM_FLAT = 9      # flat integer arrays ahead of the block tables in the packed buffer
+NUM_FLAT = 10     # flat integer arrays ahead of the block tables in the packed buffer
 
 
 @dataclass(frozen=True)
@@ -43,7 +45,7 @@ class BatchLayout:
     widths: Tuple[int, ...]
 
     def sizes(self) -> List[int]:
-        return [self.T, self.T, self.T, self.B + 1, self.B, self.B, self.B, self.R, self.B] + \
+        return [self.T, self.T, self.T, self.B + 1, self.B, self.B, self.B, self.R, self.B, self.T] + \
                [self.B * w for w in self.widths]
 
     @property
@@ -74,6 +76,7 @@ class StepBatch:
     slots: torch.Tensor           # int32 [B]   state slot of each request
     logit_rows: torch.Tensor      # int32 [R]   flat rows whose logits are wanted
     req_order: Optional[torch.Tensor] = None   # int32 [B] request rows ordered by their number of new tokens
+    tok_src: Optional[torch.Tensor] = None     # int32 [T] rows of the previous step's drawn tokens (-1: none), or None
     block_tables: List[torch.Tensor] = field(default_factory=list)   # per group int32 [B, width]
     # host copies, for launch decisions
     h_q_lens: Optional[np.ndarray] = None
@@ -145,8 +148,16 @@ def pack_step(entries: Sequence[StepEntry], starts: Sequence[int], slots: Sequen
     # requests ordered by the number of tokens they bring (shortest first): kernels that treat
     # single decoded tokens and long portions differently take a prefix or a suffix of this order
     req_order = np.argsort(q_lens, kind="stable").astype(np.int32)
+    tok_src = np.full(T, -1, dtype=np.int32)
+    has_src = False
+    for i, e in enumerate(entries):
+        if e.token_src is not None:
+            tok_src[q_start[i]:q_start[i] + len(e.tokens)] = np.asarray(e.token_src, dtype=np.int32)
+            has_src = True
+    if has_src:
+        token_ids[tok_src >= 0] = 0
     for o, arr in zip(offs[:NUM_FLAT], (token_ids, positions, tok_req, q_start, pos_start, kv_len, slot_arr,
-                                        np.asarray(rows, dtype=np.int32), req_order)):
+                                        np.asarray(rows, dtype=np.int32), req_order, tok_src)):
         out[o:o + arr.shape[0]] = arr
     for g in range(G):
         w = layout.widths[g]
@@ -160,7 +171,7 @@ def pack_step(entries: Sequence[StepEntry], starts: Sequence[int], slots: Sequen
             if n:
                 bt[i, :n] = t
     info = dict(max_q_len=int(q_lens.max()), max_kv_len=int(kv_len.max()), q_lens=q_lens, pos_start=pos_start,
-                sorted_q_lens=q_lens[req_order],
+                sorted_q_lens=q_lens[req_order], has_token_src=has_src,
                 all_decode=bool((q_lens == 1).all()), real_requests=nreal, real_logit_rows=real_rows)
     return out, layout, info
 
@@ -171,7 +182,7 @@ def batch_from_device(dev: torch.Tensor, layout: BatchLayout, info) -> StepBatch
         num_tokens=layout.T, num_requests=layout.B, num_logit_rows=layout.R,
         max_q_len=info["max_q_len"], max_kv_len=info["max_kv_len"],
         token_ids=v[0], positions=v[1], tok_req=v[2], q_start=v[3], pos_start=v[4], kv_len=v[5],
-        slots=v[6], logit_rows=v[7], req_order=v[8], block_tables=bts,
+        slots=v[6], logit_rows=v[7], req_order=v[8], tok_src=v[9] if info["has_token_src"] else None, block_tables=bts,
         h_q_lens=info["q_lens"], h_pos_start=info["pos_start"], h_sorted_q_lens=info["sorted_q_lens"],
         all_decode=info["all_decode"],
         real_requests=info["real_requests"], real_logit_rows=info["real_logit_rows"])

@@ -18,7 +18,7 @@ from ..config import EngineConfig
 from ..sampling import Sampler, SamplingParams
 from .batch import StepEntry
 from .runner import ModelRunner
-from .scheduler import Scheduler, Request, StepOutput
+from .scheduler import Scheduler, Request, StepOutput, PENDING
 
 
 class Engine:
@@ -36,6 +36,9 @@ class Engine:
         self.requests: Dict[Hashable, Request] = {}
         self._ids = itertools.count()
         self.step_events = None      # optional (start, end) CUDA events recorded around the step's device work
+        self._inflight = None        # the step that has been launched and whose drawn tokens have not been read
+        self._host_tokens = [None, None]   # pinned buffers the drawn tokens are copied to, used in turn
+        self._host_flip = 0
 
     # --------------------------------------------------------------- requests
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
@@ -54,35 +57,103 @@ class Engine:
         return rid
 
     def has_unfinished(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._inflight is not None
 
     # ------------------------------------------------------------------- step
     def step(self) -> List[StepOutput]:
-        """One scheduler step: plan, run the batch, draw tokens, commit."""
-        plan = self.scheduler.schedule()
+        """One scheduler step: plan, run the batch, draw tokens.
+
+        With ``async_steps`` the drawn tokens stay on the device: the next step is planned and launched
+        with them (count-based endings are known without their values) and only then are the tokens of
+        the step before read, so the host works while the device does.  Outputs therefore come one call
+        late; ``has_unfinished`` stays true until the last ones have been handed out.  Whenever the host
+        needs token values first -- a preempted request to recompute, pages about to run out, a
+        repetition penalty -- the step in flight is read before planning."""
+        outs: List[StepOutput] = []
+        sched = self.scheduler
+        if self._inflight is not None and (not self.ecfg.async_steps or sched.has_pending_outside_running()
+                                           or sched.may_run_out_of_pages() or self._needs_token_values()):
+            outs += self._resolve_inflight()
+        plan = sched.schedule()
+        if not plan.entries:
+            sched.commit_launch(plan)
+            outs += sched.resolve(plan, {})
+            outs += self._resolve_inflight()
+            return outs
+        prev = self._inflight
+        prev_rows = {r.id: i for i, r in enumerate(prev["samplers"])} if prev else {}
+        entries = []
+        for e in plan.entries:
+            src = None
+            if PENDING in e.tokens:
+                src = [prev_rows[e.request.id] if t == PENDING else -1 for t in e.tokens]
+            entries.append(StepEntry(e.request.id, e.tokens, [len(e.tokens) - 1] if e.samples else [], token_src=src))
+        batch = self.runner.make_batch(entries, prev["tokens"] if prev else None)
+        ev = self.step_events
+        if ev is not None:
+            ev[0].record()
+        logits = self.runner.run_batch(batch)
+        record = {"plan": plan, "samplers": [e.request for e in plan.entries if e.samples], "tokens": None,
+                  "host": None, "event": None}
+        samplers = record["samplers"]
+        if samplers:
+            need_seen = any(r.params.repetition_penalty != 1.0 for r in samplers)
+            toks = self.sampler.sample(
+                logits, [r.params for r in samplers], [r.key for r in samplers],
+                [len(r.generated) for r in samplers],
+                [r.tokens for r in samplers] if need_seen else None)
+            record["tokens"] = toks
+            if toks.is_cuda:
+                i = self._host_flip                    # two pinned buffers in turn: the one of the step
+                self._host_flip ^= 1                   # before may not have been read yet
+                host = self._host_tokens[i]
+                if host is None or host.numel() < toks.numel():
+                    host = torch.empty(max(256, toks.numel()), dtype=torch.int32, pin_memory=True)
+                    self._host_tokens[i] = host
+                host[:toks.numel()].copy_(toks, non_blocking=True)
+                record["host"] = host
+                record["event"] = torch.cuda.Event()
+                record["event"].record()
+        if ev is not None:
+            ev[1].record()
+        sched.commit_launch(plan)
+        self._inflight = record
+        if prev is not None:
+            outs += self._resolve(prev)
+        if not self.ecfg.async_steps:
+            outs += self._resolve_inflight()
+        return outs
+
+    def _needs_token_values(self) -> bool:
+        return any(r.params.repetition_penalty != 1.0 for r in self.scheduler.running) or \
+            any(r.params.repetition_penalty != 1.0 for r in self.scheduler.waiting)
+
+    def _resolve(self, record) -> List[StepOutput]:
         drawn: Dict[Hashable, int] = {}
-        if plan.entries:
-            entries = [StepEntry(e.request.id, e.tokens, [len(e.tokens) - 1] if e.samples else [])
-                       for e in plan.entries]
-            batch = self.runner.make_batch(entries)
-            ev = self.step_events
-            if ev is not None:
-                ev[0].record()
-            logits = self.runner.run_batch(batch)
-            samplers = [e.request for e in plan.entries if e.samples]
-            if samplers:
-                need_seen = any(r.params.repetition_penalty != 1.0 for r in samplers)
-                toks = self.sampler.sample(
-                    logits, [r.params for r in samplers], [r.key for r in samplers],
-                    [len(r.generated) for r in samplers],
-                    [r.tokens for r in samplers] if need_seen else None)
-                if ev is not None:
-                    ev[1].record()
-                host = toks.cpu().tolist()
-                drawn = {r.id: t for r, t in zip(samplers, host)}
-            elif ev is not None:
-                ev[1].record()
-        return self.scheduler.update(plan, drawn)
+        if record["samplers"]:
+            if record["event"] is not None:
+                record["event"].synchronize()
+                host = record["host"][:len(record["samplers"])].tolist()
+            else:
+                host = record["tokens"].tolist()
+            drawn = {r.id: t for r, t in zip(record["samplers"], host)}
+        return self.scheduler.resolve(record["plan"], drawn)
+
+    def _resolve_inflight(self) -> List[StepOutput]:
+        if self._inflight is None:
+            return []
+        record, self._inflight = self._inflight, None
+        return self._resolve(record)
+
+    def abort(self, request_id: Hashable) -> None:
+        """Ends a request now (reason "abort") and gives back what it holds."""
+        self._resolve_inflight()
+        r = self.requests.pop(request_id, None)
+        if r is None or r.status == "finished":
+            return
+        if r in self.scheduler.waiting:
+            self.scheduler.waiting.remove(r)
+        self.scheduler._finish(r, "abort", release=r.status == "running")
 
     # --------------------------------------------------------------- generate
     def generate(self, prompts: Sequence[Sequence[int]],

@@ -159,9 +159,10 @@ class ModelRunner:
         return self.cache.num_tokens(req)
 
     # ------------------------------------------------------------------- step
-    def make_batch(self, entries: Sequence[StepEntry]) -> StepBatch:
+    def make_batch(self, entries: Sequence[StepEntry], prev_tokens: Optional[torch.Tensor] = None) -> StepBatch:
         """Checks the entries, takes the pages they need (all or nothing) and builds
-        the device-side batch.  Raises OutOfPages without side effects."""
+        the device-side batch.  Raises OutOfPages without side effects.  Entries with
+        ``token_src`` take token ids from ``prev_tokens`` (int32, on the device)."""
         seen = set()
         for e in entries:
             if not self.cache.is_live(e.req):
@@ -174,9 +175,11 @@ class ModelRunner:
                 raise RequestError(f"request {e.req!r} brings no tokens")
             if self.cache.num_tokens(e.req) + n > self.max_model_len:
                 raise RequestError(f"request {e.req!r} would exceed the maximum length {self.max_model_len}")
-            lo, hi = min(e.tokens), max(e.tokens)
-            if lo < 0 or hi >= self.desc.vocab_size:
+            toks = e.tokens if e.token_src is None else [t for t, s in zip(e.tokens, e.token_src) if s < 0]
+            if toks and (min(toks) < 0 or max(toks) >= self.desc.vocab_size):
                 raise RequestError(f"request {e.req!r}: token id outside [0, {self.desc.vocab_size})")
+            if e.token_src is not None and prev_tokens is None:
+                raise RequestError(f"request {e.req!r} takes tokens from a previous step, but none was given")
         # all-or-nothing over the whole step: check first, then take
         need = [0] * len(self.groups)
         for e in entries:
@@ -192,8 +195,13 @@ class ModelRunner:
         slots = [self.cache.slot_of(e.req) for e in entries]
         tables = [[self.cache.block_table(e.req, g) for e in entries] for g in range(len(self.groups))]
         if self._graph_eligible(entries):
-            return self._make_static_batch(entries, starts, slots, tables)
+            batch = self._make_static_batch(entries, starts, slots, tables)
+            if batch.tok_src is not None:
+                self.ops.gather_tokens(batch.token_ids, prev_tokens, batch.tok_src)
+            return batch
         batch = build_step_batch(entries, starts, slots, tables, self.device, pinned=self.device.type == "cuda")
+        if batch.tok_src is not None:
+            self.ops.gather_tokens(batch.token_ids, prev_tokens, batch.tok_src)
         self.last_h2d_bytes = batch.token_ids.numel() * 0 + 4 * (
             3 * batch.num_tokens + 4 * batch.num_requests + 1 + batch.num_logit_rows
             + sum(t.numel() for t in batch.block_tables))

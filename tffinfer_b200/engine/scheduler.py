@@ -35,6 +35,7 @@ from ..cache import CacheManager
 from ..sampling.params import SamplingParams
 
 WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+PENDING = -1      # stands in ``generated`` for a token that a launched step has drawn but the host has not read yet
 
 
 @dataclass
@@ -63,6 +64,8 @@ class PlanEntry:
     start: int                 # position of the first token of this portion
     tokens: List[int]
     samples: bool              # the portion ends at the request's last known token: a token is drawn
+    gen_index: Optional[int] = None    # where in ``generated`` the drawn token goes (set when the step is launched)
+    reason: Optional[str] = None       # why the request ends with this step, if it does and that is known at launch
 
 
 @dataclass
@@ -203,13 +206,11 @@ class Scheduler:
         return StepPlan(entries, preempted, finished)
 
     # ---------------------------------------------------------------- update
-    def update(self, plan: StepPlan, drawn: Dict[Hashable, int]) -> List[StepOutput]:
-        """Commits the step: tokens written, drawn tokens appended, finished requests freed.
-        ``drawn[request id]`` is the token drawn for each entry with ``samples``."""
-        outs: List[StepOutput] = []
+    def commit_launch(self, plan: StepPlan) -> None:
+        """The step has been handed to the device.  Its tokens count as written; every request that
+        draws a token gets a PENDING one (the value arrives with :meth:`resolve`); requests that end by
+        count end now and give their pages back -- whoever takes those pages runs later on the device."""
         self.counters["steps"] += 1
-        for r in plan.finished:
-            outs.append(StepOutput(r.id, None, True, r.finish_reason))
         for e in plan.entries:
             r = e.request
             self.cache.commit(r.id, len(e.tokens))
@@ -219,20 +220,55 @@ class Scheduler:
                 self.counters["prefill_tokens"] += len(e.tokens)
             if not e.samples:
                 continue
-            reason = None
-            tok = None
             if len(r.generated) >= r.params.max_new_tokens:
-                reason = "length"
+                e.reason = "length"                    # nothing is drawn
             else:
-                tok = int(drawn[r.id])
-                r.generated.append(tok)
-                if tok in r.params.eos_token_ids:
-                    reason = "stop"
-                elif len(r.generated) >= r.params.max_new_tokens:
-                    reason = "length"
+                r.generated.append(PENDING)
+                e.gen_index = len(r.generated) - 1
+                if len(r.generated) >= r.params.max_new_tokens:
+                    e.reason = "length"
                 elif len(r) >= self.max_model_len:
-                    reason = "max_position"
-            if reason is not None:
-                self._finish(r, reason, release=True)
+                    e.reason = "max_position"
+            if e.reason is not None:
+                self._finish(r, e.reason, release=True)
+
+    def resolve(self, plan: StepPlan, drawn: Dict[Hashable, int]) -> List[StepOutput]:
+        """The drawn tokens of a launched step have reached the host: they replace the PENDING entries,
+        stop tokens end their requests (tokens drawn after a stop token by a step that was already
+        launched are dropped)."""
+        outs: List[StepOutput] = []
+        for r in plan.finished:
+            outs.append(StepOutput(r.id, None, True, r.finish_reason))
+        for e in plan.entries:
+            if not e.samples:
+                continue
+            r = e.request
+            if e.gen_index is None:
+                outs.append(StepOutput(r.id, None, True, e.reason))
+                continue
+            if e.gen_index >= len(r.generated):
+                continue                               # drawn after the request's stop token: void
+            tok = int(drawn[r.id])
+            r.generated[e.gen_index] = tok
+            reason = e.reason
+            if tok in r.params.eos_token_ids:
+                del r.generated[e.gen_index + 1:]
+                if r.status != FINISHED:
+                    self._finish(r, "stop", release=True)
+                r.finish_reason = reason = "stop"
             outs.append(StepOutput(r.id, tok, reason is not None, reason))
         return outs
+
+    def update(self, plan: StepPlan, drawn: Dict[Hashable, int]) -> List[StepOutput]:
+        """Launch and result in one: for callers that read the drawn tokens before the next step."""
+        self.commit_launch(plan)
+        return self.resolve(plan, drawn)
+
+    # ------------------------------------------------------- for pipelined steps
+    def has_pending_outside_running(self) -> bool:
+        """A waiting request (preempted) still holds a PENDING token: its tokens cannot be sent yet."""
+        return any(PENDING in r.generated for r in self.waiting)
+
+    def may_run_out_of_pages(self) -> bool:
+        """Every running request may ask for one more page in the next step."""
+        return any(p.num_free < len(self.running) for p in self.cache.pools)

@@ -173,6 +173,14 @@ class CudaKernels:
         self._check(self.lib.tff_zero_f32(_ptr(t), ctypes.c_longlong(t.numel()), self._stream()), "zero_f32")
         self.launches += 1
 
+    def gather_tokens(self, token_ids, drawn, src) -> None:
+        """token_ids[i] = drawn[src[i]] wherever src[i] >= 0 (all int32, on the device)."""
+        self._need_cuda(token_ids, drawn, src)
+        assert token_ids.dtype == drawn.dtype == src.dtype == torch.int32 and src.numel() == token_ids.numel()
+        self._check(self.lib.tff_gather_tokens(_ptr(token_ids), _ptr(drawn), _ptr(src), _c_int(token_ids.numel()),
+                                               _c_int(drawn.numel()), self._stream()), "gather_tokens")
+        self.launches += 1
+
     def check_errors(self) -> None:
         """Synchronises and raises if a bounded wait inside a kernel ran out since the last check."""
         v = self.lib.tff_kernel_error()
