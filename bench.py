@@ -199,8 +199,71 @@ def prefill_run(engine, iters: int, warmup: int, seed: int):
     return statistics.median(times)
 
 
+# BASELINE.json configs[3] and configs[4]: whole-workload runs through the scheduler
+WORKLOADS = {
+    "mixed14b": dict(shape=dict(num_layers=40, hidden_size=5120, num_heads=40, num_kv_heads=8, head_dim=128,
+                                intermediate_size=17408, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6,
+                                max_position=40960),
+                     requests=32, prompt_lens=(128, 4096), new_tokens=128, chunk=512, context=4352),
+    "long32b": dict(shape=dict(num_layers=64, hidden_size=5120, num_heads=64, num_kv_heads=8, head_dim=128,
+                               intermediate_size=25600, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6,
+                               max_position=40960),
+                    requests=16, prompt_lens=(8192, 8192), new_tokens=256, chunk=2048, context=8448),
+}
+
+
+def run_workload(name: str, layers: int = 0) -> int:
+    """Runs a whole workload (prompts prefilled in portions while others decode) and prints its totals."""
+    import torch
+    import tffinfer_b200 as tff
+    from tffinfer_b200.config import Qwen3Config
+    from tffinfer_b200.weights import random_tensors_on_device
+    w = WORKLOADS[name]
+    shape = dict(w["shape"])
+    if layers:
+        shape["num_layers"] = layers
+    cfg = Qwen3Config(architecture="Qwen3ForCausalLM", tie_word_embeddings=False,
+                      layer_types=("full_attention",) * shape["num_layers"], **shape).validate()
+    rng = random.Random(0)
+    lens = [rng.randint(*w["prompt_lens"]) for _ in range(w["requests"])]
+    cache_tokens = sum(-(-(n + w["new_tokens"] + 1) // PAGE_SIZE) * PAGE_SIZE for n in lens)
+    ecfg = tff.EngineConfig(dtype="bfloat16", page_size=PAGE_SIZE, max_cache_tokens=cache_tokens,
+                            max_live_requests=w["requests"], max_tokens_per_step=w["chunk"], max_model_len=w["context"])
+    tensors = random_tensors_on_device(cfg, 0, "cuda", "bfloat16")
+    engine = tff.Engine(runner=tff.ModelRunner(config=cfg, tensors=tensors, engine_config=ecfg))
+    del tensors
+    torch.cuda.empty_cache()
+    sp = tff.SamplingParams(max_new_tokens=w["new_tokens"])
+    warm = engine.generate([[1, 2, 3, 4]], tff.SamplingParams(max_new_tokens=4))       # builds kernels, first graphs
+    prompts = [[rng.randrange(cfg.vocab_size) for _ in range(n)] for n in lens]
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    ids = [engine.add_request(p, sp, key=i) for i, p in enumerate(prompts)]
+    steps = 0
+    first_token_at = {}
+    while engine.has_unfinished():
+        for o in engine.step():
+            if o.token is not None and o.request_id not in first_token_at:
+                first_token_at[o.request_id] = time.perf_counter() - t0
+        steps += 1
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    engine.runner.ops.check_errors()
+    gen = sum(len(engine.requests[i].generated) for i in ids)
+    st = engine.stats()
+    print(json.dumps({"workload": name, "layers": cfg.num_layers, "requests": len(ids), "prompt_tokens": sum(lens),
+                      "generated_tokens": gen, "seconds": round(dt, 3), "steps": steps,
+                      "total_tok_s": round((sum(lens) + gen) / dt, 1), "generated_tok_s": round(gen / dt, 1),
+                      "mean_time_to_first_token_s": round(sum(first_token_at.values()) / max(1, len(first_token_at)), 3),
+                      "pages_high_water": st["pages_high_water"], "pages_total": st["pages_total"],
+                      "preemptions": st["preemptions"], "dtype": "bf16", "data": "synthetic"}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="headline", choices=["headline"] + sorted(WORKLOADS),
+                    help="headline: the decode/prefill benchmark; else a whole workload through the scheduler")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=4)
@@ -222,6 +285,8 @@ def main() -> int:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     warmup = max(3, args.warmup)
+    if args.workload != "headline":
+        return run_workload(args.workload, 0 if args.layers == SHAPE["num_layers"] else args.layers)
 
     import torch
     if not torch.cuda.is_available():
