@@ -38,13 +38,13 @@ def tiny_config(name: str) -> Qwen3Config:
     if name == "D":   # head size 64, multiples of 8 everywhere: takes the tensor-core kernels in bfloat16
         return Qwen3Config(architecture="Qwen3ForCausalLM", hidden_size=128, num_layers=2, num_heads=4,
                            num_kv_heads=2, head_dim=64, intermediate_size=192, vocab_size=264,
-                           rms_norm_eps=1e-6, rope_theta=1e5, max_position=512, tie_word_embeddings=False,
+                           rms_norm_eps=1e-6, rope_theta=1e5, max_position=1024, tie_word_embeddings=False,
                            sliding_window=40, layer_types=(FULL, SLIDE)).validate()
     raise KeyError(name)
 
 
 PAGE_SIZE = {"A": 4, "B": 8, "C": 16, "D": 16}
-PROMPT_LENS = {"A": [1, 7, 33], "B": [2, 13, 40, 64], "C": [3, 29, 70, 101], "D": [5, 90, 37, 260]}
+PROMPT_LENS = {"A": [1, 7, 33], "B": [2, 13, 40, 64], "C": [3, 29, 70, 101], "D": [5, 90, 37, 600]}
 DECODE_LENS = {"A": 16, "B": 24, "C": 40, "D": 36}
 
 

@@ -31,6 +31,19 @@ TFF_API int tff_embed(const int* tokens, const void* table, int table_is_bf16, f
     return tff_launch_pdl(embed_kernel<float>, num_tokens, nt, 0, stream, tokens, (const float*)table, out, hidden, vocab);
 }
 
+// four consecutive outputs in one store
+template <typename T> __device__ __forceinline__ void store4(T* p, float a, float b, float c, float d);
+template <> __device__ __forceinline__ void store4<float>(float* p, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+template <> __device__ __forceinline__ void store4<bf16>(bf16* p, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 v;
+    v.x = *reinterpret_cast<uint32_t*>(&lo);
+    v.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = v;
+}
+
 // ------------------------------------------------------------------ RMSNorm
 // out[r, :] = (x[row, :] * rsqrt(mean(x[row]^2) + eps)) * w, row = row_index ? row_index[r] : r.
 // Formula and multiplication order of src/kernel/cuda/norm.cu:31-48.
@@ -44,11 +57,31 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
     const int r = blockIdx.x;
     const int row = row_index ? row_index[r] : r;
     const float* xr = x + (size_t)row * dim;
+    TO* o = out + (size_t)r * dim;
     float ss = 0.f;
+    // four elements a thread at a time when the row allows 16-byte accesses (the order of the additions
+    // still depends on the row's width alone)
+    const bool vec = (dim & 3) == 0 && (((uintptr_t)xr | (uintptr_t)w) & 15) == 0 && ((uintptr_t)o & 7) == 0 &&
+                     (sizeof(TO) == 2 || ((uintptr_t)o & 15) == 0);
+    if (vec) {
+        const float4* x4 = reinterpret_cast<const float4*>(xr);
+        const float4* w4 = reinterpret_cast<const float4*>(w);
+        const int n4 = dim >> 2;
+        for (int i = threadIdx.x; i < n4; i += NT) {
+            const float4 v = x4[i];
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        }
+        ss = block_sum<NT>(ss, red);
+        const float rs = rsqrtf(ss / (float)dim + eps);
+        for (int i = threadIdx.x; i < n4; i += NT) {
+            const float4 v = x4[i], g = w4[i];
+            store4<TO>(o + 4 * i, (v.x * rs) * g.x, (v.y * rs) * g.y, (v.z * rs) * g.z, (v.w * rs) * g.w);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < dim; i += NT) { const float v = xr[i]; ss = fmaf(v, v, ss); }
     ss = block_sum<NT>(ss, red);
     const float rs = rsqrtf(ss / (float)dim + eps);
-    TO* o = out + (size_t)r * dim;
     for (int i = threadIdx.x; i < dim; i += NT) o[i] = from_f32<TO>((xr[i] * rs) * w[i]);
 }
 
@@ -220,18 +253,6 @@ __global__ void qk_norm_rope_kv_write_kernel(
 // in_is_f32: the projection row is float32 (else it has the activation type given by is_bf16).
 // The same for head size 128 with the whole head rotated (the common case): a lane owns four
 // consecutive elements (one 16-byte load of float32 accumulators), its rotation partner is lane ^ 16.
-template <typename T> __device__ __forceinline__ void store4(T* p, float a, float b, float c, float d);
-template <> __device__ __forceinline__ void store4<float>(float* p, float a, float b, float c, float d) {
-    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
-}
-template <> __device__ __forceinline__ void store4<bf16>(bf16* p, float a, float b, float c, float d) {
-    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
-    uint2 v;
-    v.x = *reinterpret_cast<uint32_t*>(&lo);
-    v.y = *reinterpret_cast<uint32_t*>(&hi);
-    *reinterpret_cast<uint2*>(p) = v;
-}
-
 template <typename T>
 __global__ void __launch_bounds__(256)
 qk_norm_rope_kv_write_d128_kernel(
