@@ -2,14 +2,15 @@
 // kv-head group packed into a 16-row tile) against a long run of keys, i.e. a stream of the
 // cache through the SM.  Same contract and numerics as the keys mode of attention_bf16.cu;
 // what differs is how the keys arrive:
-//   warp 4      producer: one TMA box per (page, 64-column half, K or V), issued by as many
-//               lanes as there are boxes, into a ring of 64-key stages guarded by mbarriers
+//   warp 4      producer: one TMA box per page (its keys and values of the kv head, 8 KB with
+//               16-token pages), issued by as many lanes as the block has pages, into a ring of
+//               64-key stages guarded by mbarriers
 //   warps 0-3   each takes 16 of the 64 keys of a stage: QK^T and PV on mma.sync m16n8k16,
 //               float32 online softmax; the four partial results are merged through shared
 //               memory at the end
-// The cache is seen by TMA as one matrix [pages * layers * 2 * kv_heads * page_size, head_dim]
-// whose rows of one page are contiguous, so a box of page_size rows x 64 columns is one page's
-// half head; the 128-byte swizzle TMA applies is the one ldmatrix is then addressed with.
+// The cache is seen by TMA as a 4-D tensor (64 columns, head_dim/64 halves, rows, {K, V}) over the
+// matrix [pages * layers * 2 * kv_heads * page_size, head_dim]; the 128-byte swizzle TMA applies is
+// the one ldmatrix is then addressed with.
 // Pages that are missing (given back by a sliding window, or beyond the sequence) are not
 // fetched; value rows beyond the request's last key or before its window are cleared in shared
 // memory, because a page's unused slots, and shared memory that was not written, may hold
@@ -22,7 +23,13 @@
 namespace {
 
 constexpr int BLOCK_N = 64;
-constexpr int NSTAGES = 3;
+#ifndef TFF_DEC_STAGES
+#define TFF_DEC_STAGES 3
+#endif
+#ifndef TFF_DEC_CTAS
+#define TFF_DEC_CTAS 2
+#endif
+constexpr int NSTAGES = TFF_DEC_STAGES;
 constexpr int NTHREADS = 160;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
@@ -56,11 +63,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     *abort_flag = 1;
     return false;
 }
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(tm), "r"(bar), "r"(x), "r"(y) : "memory");
-}
 __device__ __forceinline__ void compute_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
@@ -92,20 +94,27 @@ struct DecodeParams {
     int* error_flag;
 };
 
-// byte offset, inside a stage's K (or V) region, of 16-byte chunk ``c`` of key row ``kr`` (0..63):
-// tiles [page in block][64-column half] of page_size rows x 128 bytes, chunks XOR-swizzled by row % 8
+// Byte offset, inside a stage, of 16-byte chunk ``c`` of key row ``kr`` (0..63) of K (kv = 0) or V (kv = 1).
+// A stage holds, page after page of the block, what one TMA box brings: [K | V][page_size rows][halves][128 B];
+// the 16-byte chunks of every 128-byte line are XOR-swizzled by the line's index % 8 (TMA's 128-byte swizzle).
 template <int D>
-__device__ __forceinline__ uint32_t kv_off(int kr, int c, int page_shift) {
+__device__ __forceinline__ uint32_t kv_off(int kr, int c, int kv, int page_shift) {
     constexpr int HF = D / 64;
     const int j = kr >> page_shift, r = kr & ((1 << page_shift) - 1);
-    return (uint32_t)((((j * HF + (c >> 3)) << page_shift) + r) * 128 + ((((c & 7) ^ r) & 7) << 4));
+    const int line = r * HF + (c >> 3);                          // 128-byte line inside the page's K (or V)
+    return (uint32_t)((((j * 2 + kv) << page_shift) * HF + line) * 128 + ((((c & 7) ^ line) & 7) << 4));
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int x0, int x1, int x2, int x3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(tm), "r"(bar), "r"(x0), "r"(x1), "r"(x2), "r"(x3) : "memory");
 }
 
 template <int D>
-__global__ void __launch_bounds__(NTHREADS, 2)
+__global__ void __launch_bounds__(NTHREADS, TFF_DEC_CTAS)
 attn_decode_kernel(const __grid_constant__ CUtensorMap tm_cache, const DecodeParams p) {
     constexpr int CH = D / 8;
-    constexpr int HF = D / 64;
     constexpr int KV_BYTES = BLOCK_N * D * 2;                     // K (or V) of one stage
     constexpr int STAGE_BYTES = 2 * KV_BYTES;
     extern __shared__ uint8_t smem_raw[];
@@ -121,7 +130,6 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_cache, const DecodePar
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kvh = blockIdx.y, split = blockIdx.x;
-    const int ps = 1 << p.page_shift;
     const int G = p.nq / p.nkv;
 
     if (tid == 0) {
@@ -150,10 +158,9 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_cache, const DecodePar
 
     if (warp == 4) {
         // ------------------------------------------------------------ producer
-        const int ppb = BLOCK_N >> p.page_shift;                   // pages per 64-key block
-        const int nloads = ppb * HF * 2;                           // boxes per stage (<= 32)
-        const int j = lane / (HF * 2), rem = lane % (HF * 2);
-        const int kv = rem / HF, hf = rem % HF;
+        const int ppb = BLOCK_N >> p.page_shift;                   // pages per 64-key block = boxes per stage (<= 8)
+        const int j = lane;
+        const uint32_t box_bytes = (uint32_t)(2 * D * 2) << p.page_shift;      // K and V of one page
         for (int blk = kb_begin; blk < kb_end; ++blk) {
             const int i = blk - kb_begin, s = i % NSTAGES;
             const uint32_t round = i / NSTAGES;
@@ -165,15 +172,15 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_cache, const DecodePar
             if (!ok) break;
             const int n0 = blk * BLOCK_N + (j << p.page_shift);
             int page = -1;
-            if (lane < nloads && n0 <= hi) page = table[n0 >> p.page_shift];
+            if (lane < ppb && n0 <= hi) page = table[n0 >> p.page_shift];
             const bool valid = page >= 0;
             const unsigned mask = __ballot_sync(0xffffffffu, valid);
-            if (lane == 0) mbar_expect_tx(full_bar(s), (uint32_t)__popc(mask) * (uint32_t)(ps * 128));
+            if (lane == 0) mbar_expect_tx(full_bar(s), (uint32_t)__popc(mask) * box_bytes);
             __syncwarp();
             if (valid) {
-                const long long row = ((((long long)page * p.cache_layers + p.layer) * 2 + kv) * p.nkv + kvh) << p.page_shift;
-                const uint32_t dst = base + s * STAGE_BYTES + kv * KV_BYTES + (uint32_t)(((j * HF + hf) << p.page_shift) * 128);
-                tma_load_2d(dst, &tm_cache, full_bar(s), hf * 64, (int)row);
+                // first K row of (page, layer, kv head) in the cache seen as [rows, D]; the box brings its V too
+                const long long row = (((long long)page * p.cache_layers + p.layer) * 2 * p.nkv + kvh) << p.page_shift;
+                tma_load_4d(base + s * STAGE_BYTES + (uint32_t)j * box_bytes, &tm_cache, full_bar(s), 0, 0, (int)row, 0);
             }
         }
         return;
@@ -214,18 +221,18 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_cache, const DecodePar
         const int i = blk - kb_begin, s = i % NSTAGES;
         const uint32_t round = i / NSTAGES;
         if (!mbar_wait(full_bar(s), round & 1, abort_flag)) break;
-        const uint32_t tK = base + s * STAGE_BYTES, tV = tK + KV_BYTES;
+        const uint32_t tS = base + s * STAGE_BYTES;
         if (blk == kb_hi || blk == kb_lo) {
             // This warp's value rows that no query row may see -- beyond the last key, or before
             // the window -- are cleared: their page slots may hold anything, and pages that were
             // not fetched leave whatever shared memory held.  (Such key rows only produce scores
             // that the mask discards.)
-            uint8_t* gV = gbase + s * STAGE_BYTES + KV_BYTES;
+            uint8_t* gS = gbase + s * STAGE_BYTES;
             for (int idx = lane; idx < 16 * CH; idx += 32) {
                 const int kr = key_off + idx / CH, c = idx % CH;
                 const int n = blk * BLOCK_N + kr;
                 if (n > hi || n < lo_tile)
-                    *reinterpret_cast<uint4*>(gV + kv_off<D>(kr, c, p.page_shift)) = make_uint4(0u, 0u, 0u, 0u);
+                    *reinterpret_cast<uint4*>(gS + kv_off<D>(kr, c, 1, p.page_shift)) = make_uint4(0u, 0u, 0u, 0u);
             }
             __syncwarp();
         }
@@ -238,7 +245,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_cache, const DecodePar
             const int kr = key_off + (lane & 7) + (lane >> 4) * 8;
             const int chunk = kk * 2 + ((lane >> 3) & 1);
             uint32_t b0, b1, b2, b3;
-            ldsm_x4(tK + kv_off<D>(kr, chunk, p.page_shift), b0, b1, b2, b3);
+            ldsm_x4(tS + kv_off<D>(kr, chunk, 0, p.page_shift), b0, b1, b2, b3);
             mma_bf16(sc[0], qf[kk], b0, b1);
             mma_bf16(sc[1], qf[kk], b2, b3);
         }
@@ -286,7 +293,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_cache, const DecodePar
             const int kr = key_off + (lane & 7) + ((lane >> 3) & 1) * 8;
             const int chunk = dn * 2 + (lane >> 4);
             uint32_t b0, b1, b2, b3;
-            ldsm_x4_trans(tV + kv_off<D>(kr, chunk, p.page_shift), b0, b1, b2, b3);
+            ldsm_x4_trans(tS + kv_off<D>(kr, chunk, 1, p.page_shift), b0, b1, b2, b3);
             mma_bf16(o[2 * dn], a, b0, b1);
             mma_bf16(o[2 * dn + 1], a, b2, b3);
         }
@@ -373,7 +380,7 @@ int tff_attention_decode_launch(
     const long long rows = cache_pages * cache_layers * 2 * nkv * page_size;
     if (rows >= (1ll << 31)) return TFF_ERR_UNSUPPORTED;
     CUtensorMap tm;
-    if (!tff_tensor_map_2d(cache, rows, d, page_size, 64, 2, &tm)) return TFF_ERR_DRIVER;
+    if (!tff_tensor_map_kv_page(cache, rows, d, page_size, nkv, &tm)) return TFF_ERR_DRIVER;
     DecodeParams p;
     p.q = (const bf16*)q; p.q_row_stride = nq * d;
     p.q_start = q_start; p.pos_start = pos_start; p.req_ids = req_ids;

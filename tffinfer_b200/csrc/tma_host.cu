@@ -73,6 +73,36 @@ bool tff_tensor_map_2d(const void* ptr, long long rows, long long cols, int box_
     return true;
 }
 
+bool tff_tensor_map_kv_page(const void* cache, long long total_rows, int head_dim, int page_size, int kv_heads,
+                            CUtensorMap* out) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache_maps;
+    const MapKey key{cache, total_rows, head_dim, page_size, kv_heads, -4};
+    {
+        std::lock_guard<std::mutex> g(g_mu);
+        auto it = cache_maps.find(key);
+        if (it != cache_maps.end()) { *out = it->second; return true; }
+    }
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return false;
+    const int halves = head_dim / 64;
+    const cuuint64_t dims[4] = {64, (cuuint64_t)halves, (cuuint64_t)total_rows, 2};
+    const cuuint64_t strides[3] = {128, (cuuint64_t)head_dim * 2, (cuuint64_t)kv_heads * page_size * head_dim * 2};
+    const cuuint32_t box[4] = {64, (cuuint32_t)halves, (cuuint32_t)page_size, 2};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUtensorMap m;
+    if (enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(cache), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    {
+        std::lock_guard<std::mutex> g(g_mu);
+        if (cache_maps.size() > 256) cache_maps.clear();
+        cache_maps[key] = m;
+    }
+    *out = m;
+    return true;
+}
+
 int* tff_device_error_flag() {
     std::lock_guard<std::mutex> g(g_mu);
     if (g_error_flag) return g_error_flag;

@@ -11,6 +11,13 @@
 bool tff_tensor_map_2d(const void* ptr, long long rows, long long cols, int box_rows, int box_cols, int elt,
                        CUtensorMap* out);
 
+// Tensor map over a paged cache [pages, layers, 2 (K,V), kv_heads, page_size, head_dim] of bfloat16 whose
+// box is one (page, layer, kv head): 64 columns x (head_dim / 64) halves x page_size rows x {K, V}, with
+// 128-byte swizzle.  Coordinates are (0, 0, first K row, 0), rows counted over the whole tensor viewed as
+// [rows, head_dim].  False if the driver refuses.
+bool tff_tensor_map_kv_page(const void* cache, long long total_rows, int head_dim, int page_size, int kv_heads,
+                            CUtensorMap* out);
+
 // Device pointer to the error word (allocated and cleared at first use; nullptr on failure).
 int* tff_device_error_flag();
 
