@@ -47,7 +47,7 @@ def read_plain_weights(model_dir: str, dtype=torch.float64) -> Dict[str, torch.T
 def embedding(tokens: Sequence[int], table: torch.Tensor) -> torch.Tensor:
     """x[t] = E[token[t]], no scale factor (src/core/model/qwen3/QWen3Creator.cpp:283-321;
     src/kernel/cpu/embedding.cpp:35-49)."""
-    return table[torch.as_tensor(list(tokens), dtype=torch.long)]
+    return table[torch.as_tensor(list(tokens), dtype=torch.long, device=table.device)]
 
 
 def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
@@ -78,6 +78,7 @@ def rope_rotate_half(x: torch.Tensor, angles: torch.Tensor) -> torch.Tensor:
     (a cos - b sin, a sin + b cos) (src/kernel/cuda/paged_flash_attention.cu:300-384 for keys,
     :390-481 for queries).  x: [T, heads, d]; angles: [T, d/2]."""
     half = x.shape[-1] // 2
+    angles = angles.to(x.device)
     cos = torch.cos(angles.to(torch.float64)).to(x.dtype)[:, None, :]
     sin = torch.sin(angles.to(torch.float64)).to(x.dtype)[:, None, :]
     a, b = x[..., :half], x[..., half:]
@@ -92,7 +93,7 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: 
     T, H, d = q.shape
     G = H // k.shape[1]
     out = torch.empty_like(q)
-    pos = torch.arange(T)
+    pos = torch.arange(T, device=q.device)
     visible = pos[None, :] <= pos[:, None]
     if window > 0:
         visible &= pos[None, :] > pos[:, None] - window
@@ -159,12 +160,15 @@ def forward_logits(tokens: Sequence[int], w: Dict[str, torch.Tensor], cfg: dict)
 
 
 class PlainModel:
-    def __init__(self, model_dir: str, dtype=torch.float64):
+    """``device``: where the plain arithmetic runs; the large test shapes use the GPU's float64
+    units for it, the formulas are the same."""
+
+    def __init__(self, model_dir: str, dtype=torch.float64, device: str = "cpu"):
         self.cfg = read_plain_config(model_dir)
-        self.w = read_plain_weights(model_dir, dtype)
+        self.w = {k: v.to(device) for k, v in read_plain_weights(model_dir, dtype).items()}
 
     def logits(self, tokens: Sequence[int]) -> torch.Tensor:
-        return forward_logits(tokens, self.w, self.cfg)
+        return forward_logits(tokens, self.w, self.cfg).cpu()
 
 
 # --------------------------------------------------------------------------- sampling

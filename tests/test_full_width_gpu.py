@@ -1,0 +1,66 @@
+"""The engine at the layer sizes of an 8B model (width 4096, 32 query heads on 8 key/value
+heads of 128, feed-forward 12288) and of a 14B model (width 5120, 40 query heads, feed-forward
+17408), two layers and an odd vocabulary, against the plain
+implementation (which runs in float64 on the GPU here, the formulas being the same): the
+kernels take other paths at these sizes than at the tiny ones (tensor-core products with
+every epilogue, the head-128 attention kernels, split keys)."""
+import random
+
+import pytest
+import torch
+
+from helpers import trace_tail_decode, trace_portions, trace_mixed, run_trace, first_bad
+from plain_qwen3 import PlainModel
+from tffinfer_b200.config import Qwen3Config, EngineConfig
+from tffinfer_b200.engine import ModelRunner
+from tffinfer_b200.weights import write_random_model
+
+pytestmark = pytest.mark.gpu
+
+TOL = {"float32": 2e-5, "bfloat16": 4e-2}
+PAGE = 16
+PROMPTS = [300, 45, 131]
+DECODED = 8
+
+
+SHAPES = {"8b": (4096, 32, 12288, 32003), "14b": (5120, 40, 17408, 15013)}
+
+
+@pytest.fixture(scope="module", params=list(SHAPES))
+def wide(request, tmp_path_factory):
+    hidden, heads, inter, vocab = SHAPES[request.param]
+    cfg = Qwen3Config(architecture="Qwen3ForCausalLM", hidden_size=hidden, num_layers=2, num_heads=heads,
+                      num_kv_heads=8, head_dim=128, intermediate_size=inter, vocab_size=vocab,
+                      rms_norm_eps=1e-6, rope_theta=1e6, max_position=4096, tie_word_embeddings=False,
+                      layer_types=("full_attention",) * 2).validate()
+    d = write_random_model(str(tmp_path_factory.mktemp("wide")), cfg, seed=5)
+    rng = random.Random(11)
+    reqs = {f"w{i}": [rng.randrange(cfg.vocab_size) for _ in range(n + DECODED)] for i, n in enumerate(PROMPTS)}
+    pm = PlainModel(d, device="cuda")
+    want = {r: pm.logits(t) for r, t in reqs.items()}
+    del pm
+    torch.cuda.empty_cache()
+    return d, reqs, want
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("mode", ["tail", "portions", "mixed"])
+def test_full_width_layers_match_plain(wide, mode, dtype):
+    d, reqs, want = wide
+    most = max(-(-len(t) // PAGE) * PAGE for t in reqs.values())
+    pool = most + most // 2 if mode == "mixed" else most
+    if mode == "tail":
+        steps = trace_tail_decode(reqs, tail=DECODED)
+    elif mode == "portions":
+        steps = trace_portions(reqs, sizes=(70, 2, 33, 128, 3, 17))
+    else:
+        steps = trace_mixed(reqs, PROMPTS, max_live=3, page_size=PAGE, pool_tokens=pool, chunk=64)
+    runner = ModelRunner(d, EngineConfig(dtype=dtype, page_size=PAGE, max_cache_tokens=pool, max_live_requests=4,
+                                         use_cuda_graphs=False))
+    for c in runner.kv_caches:
+        c.fill_(float("nan"))
+    got = run_trace(runner, reqs, steps)
+    for r in reqs:
+        bad = first_bad(got[r], want[r], TOL[dtype])
+        assert bad is None, (f"{mode}/{dtype}/{r}: first wrong position {bad[0]} (rel err {bad[1]:.3e}) "
+                             f"of {len(reqs[r])}")
