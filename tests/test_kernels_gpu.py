@@ -159,9 +159,13 @@ def test_gemm_tc_all_epilogues(ops, M, N, K):
                                                   (200, 300, 512, 0, 256, 0), (16, 128, 64, 1, 32, 0),
                                                   (1, 24576, 4096, 1, 16, 1), (3, 40000, 256, 1, 16, 1),
                                                   (700, 1030, 520, 0, 128, 0), (700, 1030, 520, 0, 256, 0),
-                                                  (130, 24576, 128, 0, 256, 0), (128, 64, 4096, 1, 128, 1)])
+                                                  (130, 24576, 128, 0, 256, 0), (128, 64, 4096, 1, 128, 1),
+                                                  (700, 1030, 520, 0, 256, 3), (2500, 2304, 264, 0, 256, 5),
+                                                  (2500, 2304, 264, 0, 256, 8), (300, 311, 264, 0, 128, 8),
+                                                  (2048, 4096, 1024, 0, 256, 4), (512, 4096, 4096, 0, 256, 2)])
 def test_gemm_tc_explicit_plans(ops, M, N, K, swap, bn, splits):
-    """splits: 1 = stream-K shares with float32 adds, 0 = whole tiles"""
+    """splits: 0 = whole tiles; 1 = stream-K shares with float32 adds; S >= 2 = the tiles of the last wave
+    in S slices of their K range (more slices than K blocks leaves some empty)"""
     a, w = g((M, K), torch.bfloat16, 13), g((N, K), torch.bfloat16, 14, 0.05)
     ref = a.double() @ w.double().t()
     res = g((M, N), torch.float32, 15)

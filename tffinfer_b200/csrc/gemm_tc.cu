@@ -368,7 +368,8 @@ int dispatch_epi(const CUtensorMap& tl, const CUtensorMap& tc, const CUtensorMap
 //   swap      0: A rows on TMEM lanes (tiles 128 x bn over M x N); 1: W rows on lanes (tiles 128 x bn over N x M)
 //   bn        16, 32, 64, 128 or 256
 //   add       1: the product is added to what ``out`` (float32) holds -- a residual stream in place
-//   stream_k  1: (tile, K block) units are dealt in equal shares; tiles that are split between CTAs
+//   stream_k  1: (tile, K block) units are dealt in equal shares; S >= 2: the tiles of the last, partial wave
+//             are cut into S slices of their K range; tiles that are split between CTAs
 //             are accumulated with float32 adds, so ``out`` (float32) must hold the initial value
 //             (zero, or the residual with add = 1) before the call
 TFF_API int tff_gemm_tc(const void* A, const void* W, void* out, int out_is_bf16, int add,

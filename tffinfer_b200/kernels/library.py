@@ -135,8 +135,10 @@ class CudaKernels:
     SWAP_MAX_M = 256          # up to this many rows the weights are the 128-row operand
     NUM_SMS = 148
 
-    def tc_plan(self, M: int, N: int, K: int, out_is_f32: bool):
-        """(swap, bn, stream_k) of the tcgen05 product for a shape."""
+    def tc_plan(self, M: int, N: int, K: int, out_is_f32: bool, add: bool = False):
+        """(swap, bn, stream_k) of the tcgen05 product for a shape.  stream_k: 0 = whole tiles; 1 = the
+        (tile, K block) units in equal contiguous shares; S >= 2 = the tiles of the last, partial wave
+        in S slices of their K range."""
         if M <= self.SWAP_MAX_M:
             bn = 16
             while bn < M:
@@ -144,13 +146,33 @@ class CudaKernels:
             tiles = -(-N // 128)
             stream_k = 1 if (out_is_f32 and tiles < 4 * self.NUM_SMS) else 0
             return 1, bn, stream_k
-        return 0, (256 if N > 128 else 128), 0
+        bn = 256 if N > 128 else 128
+        if not (add and out_is_f32):
+            return 0, bn, 0
+        # added to a float32 buffer, shares of a tile can meet there: the last wave may be cut along K
+        return 0, bn, self.tail_slices(-(-M // 128) * -(-N // bn), -(-K // 64), self.NUM_SMS)
+
+    @staticmethod
+    def tail_slices(tiles: int, k_blocks: int, ctas: int) -> int:
+        """In how many slices the K range of the tiles of the last wave is cut (0: not at all).  A wave of
+        R tiles in S slices takes ceil(R*S/G)/S of a tile's time; every slice costs another pass of the
+        tile through the epilogue, here put at 2 % of a tile's time."""
+        tail = tiles % ctas
+        if tail == 0:
+            return 0
+        best, best_cost = 0, 1.0
+        for s in range(2, min(8, k_blocks) + 1):
+            cost = -(-tail * s // ctas) / s + 0.02 * s
+            if cost < best_cost - 1e-9:
+                best, best_cost = s, cost
+        return best
 
     def gemm_tc(self, a, w, out, residual=None, plan=None) -> None:
         """bfloat16 x bfloat16 product on the tensor cores (tcgen05), float32 accumulation."""
         M, K = a.shape
         N = w.shape[0]
-        swap, bn, stream_k = plan if plan is not None else self.tc_plan(M, N, K, out.dtype == torch.float32)
+        swap, bn, stream_k = plan if plan is not None else self.tc_plan(M, N, K, out.dtype == torch.float32,
+                                                                        residual is not None)
         add = 0
         if residual is not None:
             assert out.dtype == torch.float32
