@@ -1,7 +1,8 @@
 // Prompt-portion attention over the paged cache on the 5th-generation tensor cores.
 //
-// A CTA takes 128 packed query rows (row R of a request = token R / G, head kvh*G + R % G) of
-// one (request, kv head) and walks the keys in blocks of 64:
+// A CTA takes one or two tiles of 128 packed query rows (row R of a request = token R / G, head
+// kvh*G + R % G) of one (request, kv head) and walks the keys in blocks of 64, once for its tiles.
+// Per tile:
 //   S = Q K^T     tcgen05.mma, M = 128, N = 64, K = head size; both operands K-major in
 //                 128-byte-swizzled shared memory; S (float32) in tensor memory, two buffers
 //   softmax       four warps, one thread per row: S row from TMEM, causal/window mask by
@@ -14,8 +15,17 @@
 // exponentials use (the probabilities then stay below 2^8, harmless in float32/bfloat16), so
 // the read-modify-write of O in tensor memory is rare.
 //   warp 0      TMA producer: one box per (page, 64-column half, K or V) into a ring of stages
-//   warp 1      TMEM allocation, MMA issue (one lane)
-//   warps 2-5   softmax, rescale, epilogue (TMEM lane quarter = warp % 4)
+//   warp 1      TMEM allocation (all 512 columns: O and two S buffers per tile), MMA issue (one lane)
+//   warps 2-5   softmax, rescale, epilogue of the first tile (TMEM lane quarter = warp % 4)
+//   warps 6-9   the same for the second tile
+// What the schedule of the issuing thread rests on (measured on a B200): a product of this size
+// occupies the tensor core for 48 (S, bound by the 6 KB of operands it reads from shared memory)
+// or 64 cycles (PV), and issuing blocks while the one before runs; a run of products that starts
+// on an idle tensor core costs about 175 cycles extra.  So the thread waits once per key block
+// (for the probabilities of block j of its tiles and the keys of block j + 2) and then issues
+// PV(j) and S(j + 2) for its tiles in one run; the softmax warps find S(j + 1) finished when they
+// have written P(j), and with two tiles a CTA the run is twice as long for the same wait.
+// CTAs are handed out longest walk first over all kv heads.
 // Same contract as the rows mode of attention_bf16.cu, which it replaces when the page size
 // is 8/16/32/64.  Every mbarrier wait is bounded; a timeout raises the library's error word.
 #include "common.cuh"
@@ -27,7 +37,6 @@ namespace {
 constexpr int BLOCK_M = 128;
 constexpr int BLOCK_N = 64;
 constexpr int NSTAGES = 4;
-constexpr int NTHREADS = 192;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 constexpr float RESCALE_THRESHOLD = 8.0f;       // in log2 units
 
@@ -140,49 +149,49 @@ struct PrefillParams {
     int* error_flag;
 };
 
-template <int D>
-__global__ void __launch_bounds__(NTHREADS, 1)
+// QT: query tiles per CTA.  Two when that still gives every SM a CTA, one otherwise.
+template <int D, int QT>
+__global__ void __launch_bounds__(64 + QT * 128, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const PrefillParams p) {
     constexpr int HF = D / 64;                                   // 64-column halves of a head
     constexpr int CH = D / 8;                                    // 16-byte chunks per row
     constexpr int KV_BYTES = BLOCK_N * D * 2;                    // K (or V) of one stage: [half][64 keys][128 B]
     constexpr int STAGE_BYTES = 2 * KV_BYTES;
-    constexpr int Q_BYTES = BLOCK_M * D * 2;                     // [half][128 rows][128 B]
-    constexpr int P_BYTES = BLOCK_M * BLOCK_N * 2;               // [128 rows][128 B]
-    constexpr int TMEM_COLS = 256;                               // O: [0, D), S buffers at 128 and 192
+    constexpr int Q_BYTES = BLOCK_M * D * 2;                     // one query tile: [half][128 rows][128 B]
+    constexpr int P_BYTES = BLOCK_M * BLOCK_N * 2;               // one tile's probabilities: [128 rows][128 B]
+    constexpr int TMEM_COLS = 512;                               // O of tile x at 128 x; S buffers at 256 + 128 x + 64 sb
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
-    const uint32_t sQ = base + NSTAGES * STAGE_BYTES;
-    const uint32_t sP = sQ + Q_BYTES;                            // two buffers
-    const uint32_t bars = sP + 2 * P_BYTES;
+    const uint32_t sQ = base + NSTAGES * STAGE_BYTES;            // two query tiles
+    const uint32_t sP = sQ + QT * Q_BYTES;                       // one buffer per tile
+    const uint32_t bars = sP + QT * P_BYTES;
     uint8_t* gQ = gbase + NSTAGES * STAGE_BYTES;
-    uint8_t* gP = gQ + Q_BYTES;
-    // barriers: kv_full[NS], kv_empty[NS], s_full[2], s_empty[2], p_full[2], pv_done[2], q_ready
+    uint8_t* gP = gQ + QT * Q_BYTES;
+    // barriers: kv_full[NS], kv_empty[NS]; per tile x: s_full[2], p_full, pv_done, q_ready
     auto kv_full = [&](int s) { return bars + 8u * s; };
     auto kv_empty = [&](int s) { return bars + 8u * (NSTAGES + s); };
-    auto s_full = [&](int b) { return bars + 8u * (2 * NSTAGES + b); };
-    auto s_empty = [&](int b) { return bars + 8u * (2 * NSTAGES + 2 + b); };
-    auto p_full = [&](int b) { return bars + 8u * (2 * NSTAGES + 4 + b); };
-    auto pv_done = [&](int b) { return bars + 8u * (2 * NSTAGES + 6 + b); };
-    const uint32_t q_ready = bars + 8u * (2 * NSTAGES + 8);
-    volatile uint32_t* tmem_slot = (volatile uint32_t*)(gP + 2 * P_BYTES + 8 * (2 * NSTAGES + 9));
+    auto s_full = [&](int x, int b) { return bars + 8u * (2 * NSTAGES + 5 * x + b); };
+    auto p_full = [&](int x) { return bars + 8u * (2 * NSTAGES + 5 * x + 2); };
+    auto pv_done = [&](int x) { return bars + 8u * (2 * NSTAGES + 5 * x + 3); };
+    auto q_ready = [&](int x) { return bars + 8u * (2 * NSTAGES + 5 * x + 4); };
+    volatile uint32_t* tmem_slot = (volatile uint32_t*)(gP + QT * P_BYTES + 8 * (2 * NSTAGES + 5 * QT));
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int kvh = blockIdx.y;
-    const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;        // later tiles see more keys: issued first
+    // CTAs are handed out in the order x, y, z: all kv heads of the last rows (which see the most keys)
+    // first, the shortest walks last, so that the SMs finish together
+    const int kvh = blockIdx.x;
+    const int pair = (int)gridDim.y - 1 - (int)blockIdx.y;
     const int G = p.nq / p.nkv;
     const int ps = 1 << p.page_shift;
 
-    // request geometry: q_start and pos_start come with the step's batch (an earlier copy), not from
-    // the kernel ahead, but they are read after the dependency wait all the same
     if (tid == 0) {
         for (int s = 0; s < NSTAGES; ++s) { mbar_init(kv_full(s), 1); mbar_init(kv_empty(s), 1); }
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(s_full(i), 1); mbar_init(s_empty(i), 4); mbar_init(p_full(i), 4); mbar_init(pv_done(i), 1);
+        for (int x = 0; x < QT; ++x) {
+            mbar_init(s_full(x, 0), 1); mbar_init(s_full(x, 1), 1);
+            mbar_init(p_full(x), 4); mbar_init(pv_done(x), 1); mbar_init(q_ready(x), 4);
         }
-        mbar_init(q_ready, 4);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_cache) : "memory");
@@ -195,17 +204,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const Prefi
     pdl_launch_dependents();
     pdl_wait();
 
+    // request geometry (q_start and pos_start come with the step's batch, read after the dependency wait all the same)
     const int b = p.req_ids ? p.req_ids[blockIdx.z] : (int)blockIdx.z;
     const int q0 = p.q_start[b];
     const int q_len = p.q_start[b + 1] - q0;
     const int rows_total = q_len * G;
-    const bool active = tile * BLOCK_M < rows_total;              // uniform over the CTA
+    const int row0 = pair * QT * BLOCK_M;                         // first packed row of the CTA
+    const bool active = row0 < rows_total;                        // uniform over the CTA
+    const int n_act = !active ? 0 : (row0 + BLOCK_M < rows_total ? QT : 1);   // query tiles of the CTA that have rows
     const int pos0 = p.pos_start[b];
-    const int first_tok = (tile * BLOCK_M) / G;
-    const int last_tok = min(q_len - 1, (tile * BLOCK_M + BLOCK_M - 1) / G);
-    const int hi = pos0 + last_tok;
-    const int lo_tile = p.window > 0 ? max(0, pos0 + first_tok - p.window + 1) : 0;
-    const int kb_lo = lo_tile / BLOCK_N, kb_hi = hi / BLOCK_N;
+    const int first_tok = row0 / G;
+    const int last_tok = min(q_len - 1, (row0 + QT * BLOCK_M - 1) / G);
+    const int hi = pos0 + last_tok;                               // last key any row of the CTA sees
+    const int lo_cta = p.window > 0 ? max(0, pos0 + first_tok - p.window + 1) : 0;   // first key any row sees
+    const int kb_lo = lo_cta / BLOCK_N, kb_hi = hi / BLOCK_N;
     const int nb = active ? kb_hi - kb_lo + 1 : 0;
     const int* table = p.block_table + (size_t)b * p.table_width;
 
@@ -241,151 +253,176 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const Prefi
         }
     } else if (warp == 1) {
         // -------------------------------------------------------------- MMA issuer
+        // Starting a run of products after the tensor core has gone idle costs about 175 cycles, so the
+        // thread waits once per key block and then issues one long run: O_x += P_x(j) V_j for both tiles,
+        // then S_x(j+2) = Q_x K_(j+2)^T for both.  S runs two blocks ahead of the softmax (two S buffers
+        // per tile), so a tile's softmax warps find their next scores finished when they have written a
+        // block's probabilities.  S_x(j+2) overwrites the buffer of S_x(j), which the softmax warps have
+        // read before they announce P_x(j).
         if (lane == 0 && nb > 0) {
             constexpr uint32_t idesc_s = make_idesc(BLOCK_M, BLOCK_N, 0);
             constexpr uint32_t idesc_pv = make_idesc(BLOCK_M, D, 1);
-            bool ok = mbar_wait(q_ready, 0, abort_flag);
-            auto issue_pv = [&](int jj) {                          // O += P_jj V_jj
-                const int sb = jj & 1, st = jj % NSTAGES;
-                if (!mbar_wait(p_full(sb), (jj >> 1) & 1, abort_flag)) return false;
-                tc_fence_after();
-                const uint32_t v_addr = base + st * STAGE_BYTES + KV_BYTES;
-                const uint32_t p_addr = sP + sb * P_BYTES;
+            bool ok = true;
+            for (int x = 0; x < n_act && ok; ++x) ok = mbar_wait(q_ready(x), 0, abort_flag);
+            // descriptors are built once; a product costs one 64-bit add on each (the low bits of a
+            // descriptor are the shared-memory address in units of 16 bytes)
+            const uint64_t qdesc = make_smem_desc(sQ, 16);                         // + x * Q_BYTES
+            const uint64_t kdesc = make_smem_desc(base, 16);                       // + stage * STAGE_BYTES
+            const uint64_t vdesc = make_smem_desc(base + KV_BYTES, BLOCK_N * 128); // + stage * STAGE_BYTES
+            const uint64_t pdesc = make_smem_desc(sP, 16);                         // + x * P_BYTES
+            auto issue_s = [&](int jj) {                           // S_x(jj) for both tiles; K_jj has landed
+                const int sb = jj & 1;
+                const uint64_t kd = kdesc + (uint64_t)((jj % NSTAGES) * (STAGE_BYTES >> 4));
 #pragma unroll
-                for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
-                    const uint64_t adesc = make_smem_desc(p_addr + kk * 32, 16);
-                    const uint64_t bdesc = make_smem_desc(v_addr + kk * 16 * 128, BLOCK_N * 128);
-                    umma_bf16(tmem_base, adesc, bdesc, idesc_pv, (jj > 0 || kk > 0) ? 1u : 0u);
+                for (int x = 0; x < QT; ++x) {
+                    if (x < n_act) {
+                        const uint64_t qd = qdesc + (uint64_t)(x * (Q_BYTES >> 4));
+#pragma unroll
+                        for (int kk = 0; kk < D / 16; ++kk) {
+                            // Q: [half][128 rows][128 B], K: [half][64 keys][128 B]; 16 elements = 32 bytes along a row
+                            const uint32_t qoff = ((kk / 4) * (BLOCK_M * 128) + (kk % 4) * 32) >> 4;
+                            const uint32_t koff = ((kk / 4) * (BLOCK_N * 128) + (kk % 4) * 32) >> 4;
+                            umma_bf16(tmem_base + 256 + x * 128 + sb * 64, qd + qoff, kd + koff, idesc_s, kk > 0 ? 1u : 0u);
+                        }
+                        umma_commit(s_full(x, sb));
+                    }
                 }
-                umma_commit(kv_empty(st));                         // K and V of the stage have been read
-                umma_commit(pv_done(sb));                          // O holds block jj; the P buffer is free
-                return true;
             };
+            for (int jj = 0; jj < 2 && jj < nb && ok; ++jj) {
+                ok = mbar_wait(kv_full(jj), 0, abort_flag);
+                if (ok) { tc_fence_after(); issue_s(jj); }
+            }
             for (int j = 0; j < nb && ok; ++j) {
-                const int sb = j & 1, st = j % NSTAGES;
-                ok = mbar_wait(kv_full(st), (j / NSTAGES) & 1, abort_flag);
-                if (ok && j >= 2) ok = mbar_wait(s_empty(sb), ((j >> 1) - 1) & 1, abort_flag);
+                const int st = j % NSTAGES;
+                for (int x = 0; x < n_act && ok; ++x) ok = mbar_wait(p_full(x), j & 1, abort_flag);
+                if (ok && j + 2 < nb) ok = mbar_wait(kv_full((j + 2) % NSTAGES), ((j + 2) / NSTAGES) & 1, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t k_addr = base + st * STAGE_BYTES;
+                const uint64_t vd = vdesc + (uint64_t)(st * (STAGE_BYTES >> 4));
 #pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t off = (kk / 4) * (BLOCK_M * 128) + (kk % 4) * 32;      // Q: [half][128 rows][128 B]
-                    const uint32_t koff = (kk / 4) * (BLOCK_N * 128) + (kk % 4) * 32;     // K: [half][64 keys][128 B]
-                    umma_bf16(tmem_base + 128 + sb * 64, make_smem_desc(sQ + off, 16), make_smem_desc(k_addr + koff, 16),
-                              idesc_s, kk > 0 ? 1u : 0u);
+                for (int x = 0; x < QT; ++x) {
+                    if (x < n_act) {
+                        const uint64_t pd = pdesc + (uint64_t)(x * (P_BYTES >> 4));
+#pragma unroll
+                        for (int kk = 0; kk < BLOCK_N / 16; ++kk)
+                            umma_bf16(tmem_base + x * 128, pd + (uint64_t)(kk * 2), vd + (uint64_t)(kk * 128), idesc_pv,
+                                      kk > 0 ? 1u : (j > 0 ? 1u : 0u));
+                        umma_commit(pv_done(x));                   // O_x holds block j; the tile's P buffer is free
+                    }
                 }
-                umma_commit(s_full(sb));
-                if (j > 0) ok = issue_pv(j - 1);                   // overlaps the softmax of block j
+                umma_commit(kv_empty(st));                         // K and V of the stage have been read
+                if (j + 2 < nb) issue_s(j + 2);
             }
-            if (ok) issue_pv(nb - 1);
         }
     } else {
         // ------------------------------------------------- softmax / rescale / epilogue
-        const int q = warp & 3;
+        const int x = (warp - 2) >> 2;                             // query tile of this warp
+        const int q = warp & 3;                                    // TMEM lane quarter this warp may touch
         const int r = q * 32 + lane;                               // row of the tile = TMEM lane
-        const int R = tile * BLOCK_M + r;
-        const bool rv = active && R < rows_total;
+        const int R = row0 + x * BLOCK_M + r;
+        const bool tile_active = x < n_act;
+        const bool rv = tile_active && R < rows_total;
         const int pr = pos0 + R / G;
         const int lo_r = p.window > 0 ? max(0, pr - p.window + 1) : 0;
         const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
+        const uint32_t t_o = t_row + x * 128;
         // the query tile: this thread's row, 16-byte chunks XOR-swizzled by row % 8, one [128 x 128 B] block per half
-        if (active) {
+        if (tile_active) {
             const bf16* src = p.q + (size_t)(q0 + R / G) * p.q_row_stride + (size_t)(kvh * G + R % G) * D;
 #pragma unroll
             for (int c = 0; c < CH; ++c) {
                 uint4 v = make_uint4(0u, 0u, 0u, 0u);
                 if (rv) v = *reinterpret_cast<const uint4*>(src + c * 8);
-                *reinterpret_cast<uint4*>(gQ + (c >> 3) * (BLOCK_M * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
+                *reinterpret_cast<uint4*>(gQ + x * Q_BYTES + (c >> 3) * (BLOCK_M * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
             }
             fence_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(q_ready);
+            if (lane == 0) mbar_arrive(q_ready(x));
         }
         float m_used = -INFINITY, l = 0.f;
         bool ok = true;
-        for (int j = 0; j < nb && ok; ++j) {
+        const int nb_x = tile_active ? nb : 0;
+        for (int j = 0; j < nb_x && ok; ++j) {
             const int sb = j & 1, st = j % NSTAGES;
             const int blk = kb_lo + j;
-            if (blk == kb_hi || blk == kb_lo) {
-                // value rows no query row may see (beyond the last key, before the window): cleared, since
-                // page slots and unfetched shared memory may hold anything.  The stage has landed first.
+            if (x == 0 && (blk == kb_hi || blk == kb_lo)) {
+                // value rows no query row of the CTA may see (beyond the last key, before the first window):
+                // cleared by the warps of tile 0, since page slots and unfetched shared memory may hold anything.
+                // The stage has landed first; the product that reads it waits for these warps' probabilities.
                 ok = mbar_wait_warp(kv_full(st), (j / NSTAGES) & 1, abort_flag);
                 if (!ok) break;
                 uint8_t* gV = gbase + st * STAGE_BYTES + KV_BYTES;
                 for (int idx = tid - 64; idx < BLOCK_N * CH; idx += 128) {
                     const int kr = idx / CH, c = idx % CH;
                     const int n = blk * BLOCK_N + kr;
-                    if (n > hi || n < lo_tile)
+                    if (n > hi || n < lo_cta)
                         *reinterpret_cast<uint4*>(gV + (c >> 3) * (BLOCK_N * 128) + kr * 128 + (((c & 7) ^ (kr & 7)) << 4)) =
                             make_uint4(0u, 0u, 0u, 0u);
                 }
                 fence_async_smem();
             }
-            ok = mbar_wait_warp(s_full(sb), (j >> 1) & 1, abort_flag);
+            ok = mbar_wait_warp(s_full(x, sb), (j >> 1) & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
             float s[BLOCK_N];
 #pragma unroll
             for (int h = 0; h < BLOCK_N / 16; ++h) {
                 uint32_t v[16];
-                tmem_ld16(t_row + 128 + sb * 64 + h * 16, v);
+                tmem_ld16(t_row + 256 + x * 128 + sb * 64 + h * 16, v);
                 tmem_ld_wait();
 #pragma unroll
                 for (int i = 0; i < 16; ++i) s[h * 16 + i] = __uint_as_float(v[i]);
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(s_empty(sb));               // the S buffer may be overwritten
+            tc_fence_before();                                     // the scores are in registers (see the MMA issuer)
             // Scores stay unscaled in registers; the scale (> 0) is folded into the exponent below.  Key
             // blocks that every row of the warp sees whole need no mask.
-            float m_raw = -INFINITY;
+            // (four running maxima and, below, four partial sums: chains of 16 dependent operations, not 64)
+            float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             const int n_first = blk * BLOCK_N;
             if (__all_sync(0xffffffffu, rv && n_first + BLOCK_N - 1 <= pr && n_first >= lo_r)) {
 #pragma unroll
-                for (int i = 0; i < BLOCK_N; ++i) m_raw = fmaxf(m_raw, s[i]);
+                for (int i = 0; i < BLOCK_N; ++i) m4[i & 3] = fmaxf(m4[i & 3], s[i]);
             } else {
 #pragma unroll
                 for (int i = 0; i < BLOCK_N; ++i) {
                     const int n = n_first + i;
                     const bool vis = rv && n <= pr && n >= lo_r;
                     s[i] = vis ? s[i] : -INFINITY;
-                    m_raw = fmaxf(m_raw, s[i]);
+                    m4[i & 3] = fmaxf(m4[i & 3], s[i]);
                 }
             }
+            const float m_raw = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
             const float m_blk = m_raw * p.scale_log2;
             // lazy rescale: only when the maximum has grown by more than the threshold (warp-uniform decision)
             const bool grow = m_blk > m_used + RESCALE_THRESHOLD || (m_used == -INFINITY && m_blk > -INFINITY);
+            // O_x must hold every earlier block before it is rescaled, and the product of the block before
+            // this one must have read the tile's P buffer before it is written again
+            if (j > 0) {
+                ok = mbar_wait_warp(pv_done(x), (j - 1) & 1, abort_flag);
+                if (!ok) break;
+            }
             if (__any_sync(0xffffffffu, grow)) {
                 const float m_new = grow ? m_blk : m_used;
                 const float alpha = (m_used == -INFINITY) ? 0.f : exp2f(m_used - m_new);
                 if (j > 0) {
-                    // O must hold every earlier block before it is rescaled
-                    ok = mbar_wait_warp(pv_done((j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag);
-                    if (!ok) break;
                     tc_fence_after();
 #pragma unroll 1
                     for (int c0 = 0; c0 < D; c0 += 16) {
                         uint32_t v[16];
-                        tmem_ld16(t_row + c0, v);
+                        tmem_ld16(t_o + c0, v);
                         tmem_ld_wait();
 #pragma unroll
                         for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * (grow ? alpha : 1.f));
-                        tmem_st16(t_row + c0, v);
+                        tmem_st16(t_o + c0, v);
                     }
                     tmem_st_wait();
                     tc_fence_before();
                 }
                 if (grow) { l *= alpha; m_used = m_new; }
             }
-            // the P buffer must have been read by the PV product of two blocks ago
-            if (j >= 2) {
-                ok = mbar_wait_warp(pv_done(sb), ((j >> 1) - 1) & 1, abort_flag);
-                if (!ok) break;
-            }
             const float ms = m_used == -INFINITY ? 0.f : m_used;
-            uint8_t* prow = gP + sb * P_BYTES + r * 128;
-            float lsum = 0.f;
+            uint8_t* prow = gP + x * P_BYTES + r * 128;
+            float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 uint32_t w[4];
@@ -394,26 +431,26 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const Prefi
                     const float e0 = ex2_approx(fmaf(s[c * 8 + 2 * i], p.scale_log2, -ms));
                     const float e1 = ex2_approx(fmaf(s[c * 8 + 2 * i + 1], p.scale_log2, -ms));
                     __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
-                    lsum += e0 + e1;
+                    l4[i] += e0 + e1;
                     w[i] = *reinterpret_cast<uint32_t*>(&b2);
                 }
                 *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
-            l += lsum;
+            l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
             fence_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full(sb));
+            if (lane == 0) mbar_arrive(p_full(x));
         }
         // ---------------------------------------------------------------- epilogue
-        if (ok && nb > 0) ok = mbar_wait_warp(pv_done((nb - 1) & 1), ((nb - 1) >> 1) & 1, abort_flag);
-        if (ok && nb > 0) {
+        if (ok && nb_x > 0) ok = mbar_wait_warp(pv_done(x), (nb_x - 1) & 1, abort_flag);
+        if (ok && nb_x > 0) {
             tc_fence_after();
             const float inv = l > 0.f ? 1.f / l : 0.f;
             bf16* orow = p.out + ((size_t)(q0 + R / G) * p.nq + (kvh * G + R % G)) * D;
 #pragma unroll 1
             for (int c0 = 0; c0 < D; c0 += 16) {
                 uint32_t v[16];
-                tmem_ld16(t_row + c0, v);
+                tmem_ld16(t_o + c0, v);
                 tmem_ld_wait();
                 if (rv) {
                     uint32_t w[8];
@@ -443,18 +480,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const Prefi
     }
 }
 
-template <int D>
+template <int D, int QT>
 int launch_prefill(const CUtensorMap& tm, const PrefillParams& p, int q_tiles, int B, cudaStream_t stream) {
-    constexpr int smem = NSTAGES * 2 * BLOCK_N * D * 2 + BLOCK_M * D * 2 + 2 * BLOCK_M * BLOCK_N * 2 +
-                         8 * (2 * NSTAGES + 9) + 16 + 1024;
-    auto kern = attn_prefill_tc_kernel<D>;
+    constexpr int NTHREADS = 64 + QT * 128;
+    constexpr int smem = NSTAGES * 2 * BLOCK_N * D * 2 + QT * BLOCK_M * D * 2 + QT * BLOCK_M * BLOCK_N * 2 +
+                         8 * (2 * NSTAGES + 5 * QT) + 16 + 1024;
+    static_assert(smem <= 227 * 1024, "shared memory of the prompt attention kernel");
+    auto kern = attn_prefill_tc_kernel<D, QT>;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
             return TFF_ERR_LAUNCH;
         configured = true;
     }
-    return tff_launch_pdl(kern, dim3(q_tiles, p.nkv, B), dim3(NTHREADS), (size_t)smem, stream, tm, p);
+    return tff_launch_pdl(kern, dim3(p.nkv, q_tiles, B), dim3(NTHREADS), (size_t)smem, stream, tm, p);
 }
 
 }  // namespace
@@ -470,7 +509,7 @@ int tff_attention_prefill_launch(
     if (cache_pages <= 0 || !(scale > 0.f)) return TFF_ERR_UNSUPPORTED;     // the kernel folds a positive scale into the exponent
     if (((uintptr_t)cache & 15) || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) || (nq * d) % 8) return TFF_ERR_UNSUPPORTED;
     const long long rows = cache_pages * cache_layers * 2 * nkv * page_size;
-    if (rows >= (1ll << 31) || num_requests > 65535 || nkv > 65535) return TFF_ERR_UNSUPPORTED;
+    if (rows >= (1ll << 31) || num_requests > 65535 || (long long)max_q_len * (nq / nkv) > 65535ll * 256) return TFF_ERR_UNSUPPORTED;
     CUtensorMap tm;
     if (!tff_tensor_map_2d(cache, rows, d, page_size, 64, 2, &tm)) return TFF_ERR_DRIVER;
     PrefillParams p;
@@ -484,7 +523,16 @@ int tff_attention_prefill_launch(
     p.error_flag = tff_device_error_flag();
     if (p.error_flag == nullptr) return TFF_ERR_LAUNCH;
     const int G = nq / nkv;
-    const int q_tiles = (max_q_len * G + BLOCK_M - 1) / BLOCK_M;
-    return d == 128 ? launch_prefill<128>(tm, p, q_tiles, num_requests, stream)
-                    : launch_prefill<64>(tm, p, q_tiles, num_requests, stream);
+    const int tiles = (max_q_len * G + BLOCK_M - 1) / BLOCK_M;
+    const int pairs = (tiles + 1) / 2;
+    // Two query tiles a CTA share one walk over the keys (a pair costs about 1.7 times a single tile) but
+    // halve the number of CTAs: whichever fills the SMs in fewer rounds, weighed by that cost.
+    const long long sms = tff_num_sms() > 0 ? tff_num_sms() : 1;
+    const long long rounds2 = ((long long)pairs * nkv * num_requests + sms - 1) / sms;
+    const long long rounds1 = ((long long)tiles * nkv * num_requests + sms - 1) / sms;
+    if (rounds2 * 17 < rounds1 * 10)
+        return d == 128 ? launch_prefill<128, 2>(tm, p, pairs, num_requests, stream)
+                        : launch_prefill<64, 2>(tm, p, pairs, num_requests, stream);
+    return d == 128 ? launch_prefill<128, 1>(tm, p, tiles, num_requests, stream)
+                    : launch_prefill<64, 1>(tm, p, tiles, num_requests, stream);
 }
