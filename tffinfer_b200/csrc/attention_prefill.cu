@@ -21,8 +21,9 @@
 // What the schedule of the issuing thread rests on (measured on a B200): a product of this size
 // occupies the tensor core for 48 (S, bound by the 6 KB of operands it reads from shared memory)
 // or 64 cycles (PV), and issuing blocks while the one before runs; a run of products that starts
-// on an idle tensor core costs about 175 cycles extra.  So the thread waits once per key block
-// (for the probabilities of block j of its tiles and the keys of block j + 2) and then issues
+// on an idle tensor core costs about 175 cycles extra, and a barrier wait in between costs the
+// thread 100 cycles and more.  So the thread waits on one barrier per key block (the probabilities
+// of block j of its tiles; a softmax warp has looked after the keys of block j + 2) and then issues
 // PV(j) and S(j + 2) for its tiles in one run; the softmax warps find S(j + 1) finished when they
 // have written P(j), and with two tiles a CTA the run is twice as long for the same wait.
 // CTAs are handed out longest walk first over all kv heads.
@@ -168,14 +169,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const Prefi
     const uint32_t bars = sP + QT * P_BYTES;
     uint8_t* gQ = gbase + NSTAGES * STAGE_BYTES;
     uint8_t* gP = gQ + QT * Q_BYTES;
-    // barriers: kv_full[NS], kv_empty[NS]; per tile x: s_full[2], p_full, pv_done, q_ready
+    // barriers: kv_full[NS], kv_empty[NS], p_full; per tile x: s_full[2], pv_done, q_ready
     auto kv_full = [&](int s) { return bars + 8u * s; };
     auto kv_empty = [&](int s) { return bars + 8u * (NSTAGES + s); };
-    auto s_full = [&](int x, int b) { return bars + 8u * (2 * NSTAGES + 5 * x + b); };
-    auto p_full = [&](int x) { return bars + 8u * (2 * NSTAGES + 5 * x + 2); };
-    auto pv_done = [&](int x) { return bars + 8u * (2 * NSTAGES + 5 * x + 3); };
-    auto q_ready = [&](int x) { return bars + 8u * (2 * NSTAGES + 5 * x + 4); };
-    volatile uint32_t* tmem_slot = (volatile uint32_t*)(gP + QT * P_BYTES + 8 * (2 * NSTAGES + 5 * QT));
+    const uint32_t p_full = bars + 8u * (2 * NSTAGES);            // the probabilities of a block, of all tiles of the CTA
+    auto s_full = [&](int x, int b) { return bars + 8u * (2 * NSTAGES + 1 + 4 * x + b); };
+    auto pv_done = [&](int x) { return bars + 8u * (2 * NSTAGES + 1 + 4 * x + 2); };
+    auto q_ready = [&](int x) { return bars + 8u * (2 * NSTAGES + 1 + 4 * x + 3); };
+    volatile uint32_t* tmem_slot = (volatile uint32_t*)(gP + QT * P_BYTES + 8 * (2 * NSTAGES + 1 + 4 * QT));
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -190,7 +191,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const Prefi
         for (int s = 0; s < NSTAGES; ++s) { mbar_init(kv_full(s), 1); mbar_init(kv_empty(s), 1); }
         for (int x = 0; x < QT; ++x) {
             mbar_init(s_full(x, 0), 1); mbar_init(s_full(x, 1), 1);
-            mbar_init(p_full(x), 4); mbar_init(pv_done(x), 1); mbar_init(q_ready(x), 4);
+            mbar_init(pv_done(x), 1); mbar_init(q_ready(x), 4);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -220,6 +221,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const Prefi
     const int kb_lo = lo_cta / BLOCK_N, kb_hi = hi / BLOCK_N;
     const int nb = active ? kb_hi - kb_lo + 1 : 0;
     const int* table = p.block_table + (size_t)b * p.table_width;
+    // the issuing thread waits on ONE barrier per key block: the four softmax warps of every tile that has
+    // rows arrive there, the first of them only after it has also seen the keys of block j + 2 land
+    if (tid == 0) {
+        mbar_init(p_full, 4u * (uint32_t)(n_act > 0 ? n_act : 1));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -294,8 +302,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const Prefi
             }
             for (int j = 0; j < nb && ok; ++j) {
                 const int st = j % NSTAGES;
-                for (int x = 0; x < n_act && ok; ++x) ok = mbar_wait(p_full(x), j & 1, abort_flag);
-                if (ok && j + 2 < nb) ok = mbar_wait(kv_full((j + 2) % NSTAGES), ((j + 2) / NSTAGES) & 1, abort_flag);
+                ok = mbar_wait(p_full, j & 1, abort_flag);         // P_x(j) of every tile, and K, V of block j + 2
                 if (!ok) break;
                 tc_fence_after();
                 const uint64_t vd = vdesc + (uint64_t)(st * (STAGE_BYTES >> 4));
@@ -438,8 +445,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const Prefi
             }
             l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
             fence_async_smem();
+            if (warp == 2 && j + 2 < nb) {                          // on behalf of the issuing thread
+                ok = mbar_wait_warp(kv_full((j + 2) % NSTAGES), ((j + 2) / NSTAGES) & 1, abort_flag);
+                if (!ok) break;
+            }
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full(x));
+            if (lane == 0) mbar_arrive(p_full);
         }
         // ---------------------------------------------------------------- epilogue
         if (ok && nb_x > 0) ok = mbar_wait_warp(pv_done(x), (nb_x - 1) & 1, abort_flag);
@@ -484,7 +495,7 @@ template <int D, int QT>
 int launch_prefill(const CUtensorMap& tm, const PrefillParams& p, int q_tiles, int B, cudaStream_t stream) {
     constexpr int NTHREADS = 64 + QT * 128;
     constexpr int smem = NSTAGES * 2 * BLOCK_N * D * 2 + QT * BLOCK_M * D * 2 + QT * BLOCK_M * BLOCK_N * 2 +
-                         8 * (2 * NSTAGES + 5 * QT) + 16 + 1024;
+                         8 * (2 * NSTAGES + 1 + 4 * QT) + 16 + 1024;
     static_assert(smem <= 227 * 1024, "shared memory of the prompt attention kernel");
     auto kern = attn_prefill_tc_kernel<D, QT>;
     static bool configured = false;
