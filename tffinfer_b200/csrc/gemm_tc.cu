@@ -27,6 +27,7 @@
 // Every wait on an mbarrier is bounded; when one runs out the CTA raises a flag in global
 // memory, stops issuing work, lets its copies in flight land, frees its tensor memory and
 // returns.
+#include <type_traits>
 #include "tcgen05.cuh"
 
 namespace {
@@ -57,6 +58,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_lane,   // operand whose r
                const __grid_constant__ CUtensorMap tm_out,    // output, boxes of 128 bytes x 32 rows (TMA_OUT only)
                TC* __restrict__ out, int rows_lane, int rows_col, int K, int ldo, int stream_k, int* error_flag) {
     using Cfg = TileCfg<BN, TMA_OUT, SWAP>;
+    using SegIter = typename std::conditional<SWAP, SegIterShares, SegIterSlices>::type;
     constexpr int STAGES = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;

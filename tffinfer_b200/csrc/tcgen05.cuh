@@ -115,47 +115,65 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
          | ((uint32_t)(m >> 4) << 24);                // m_dim
 }
 
-// The segments of one CTA of a persistent kernel with G CTAs.
-//   mode 0:       whole tiles c, c+G, c+2G, ...
-//   mode 1:       the contiguous share [c*U/G, (c+1)*U/G) of the U = tiles * kb_per_tile (tile, K block)
-//                 units ("stream-K"): every CTA reads the same number of bytes; for products that stream
-//                 their weights once
-//   mode S >= 2:  the first floor(tiles / G) * G tiles as in mode 0; each tile of the last, partial wave
-//                 is cut into S slices of its K range, and the (slice, tile) items, tiles fastest, go
-//                 round-robin to the CTAs.  CTAs that run together then work on neighbouring tiles at
-//                 the same K blocks, as in the whole waves, and share operands in L2; a partial wave
-//                 costs ceil(R*S/G)/S of a tile's time instead of a whole one.
-struct SegIter {
-    int kbt, mode, stride, first_split, tail_tiles;
+// The segments of one CTA of a persistent kernel with G CTAs: which (tile, range of K blocks) it works
+// on, in order.  Two dealers, kept apart so that the kernels that stream weights carry only the short one.
+//
+// SegIterShares (products that stream their weights once):
+//   mode 0:  whole tiles c, c+G, c+2G, ...
+//   mode 1:  the contiguous share [c*U/G, (c+1)*U/G) of the U = tiles * kb_per_tile (tile, K block)
+//            units ("stream-K"): every CTA reads the same number of bytes
+struct SegIterShares {
+    int kbt, mode, stride;
     long long u, u_end;
     int tile, kb0, kb1;
-    bool whole;                      // still in the whole-tile part
-    __device__ SegIter(int n_tiles, int kbt_, int mode_, int cta, int n_ctas)
+    __device__ SegIterShares(int n_tiles, int kbt_, int mode_, int cta, int n_ctas)
         : kbt(kbt_), mode(mode_), stride(n_ctas) {
-        if (mode == 1) {
+        if (mode) {
             const long long U = (long long)n_tiles * kbt;
-            whole = false;
-            first_split = 0; tail_tiles = n_tiles;
             u = U * cta / n_ctas;
             u_end = U * (cta + 1) / n_ctas;
         } else {
-            first_split = mode == 0 ? n_tiles : (n_tiles / n_ctas) * n_ctas;
-            tail_tiles = n_tiles - first_split;
-            whole = true;
             u = cta;
-            u_end = first_split;
+            u_end = n_tiles;
         }
     }
     __device__ bool next() {
-        if (mode == 1) {
-            if (u >= u_end) return false;
+        if (u >= u_end) return false;
+        if (mode) {
             tile = (int)(u / kbt);
             kb0 = (int)(u % kbt);
             const long long left = u_end - u;
             kb1 = (long long)(kbt - kb0) < left ? kbt : kb0 + (int)left;
             u += kb1 - kb0;
-            return true;
+        } else {
+            tile = (int)u; kb0 = 0; kb1 = kbt;
+            u += stride;
         }
+        return true;
+    }
+};
+
+// SegIterSlices (products with many tiles, bound by the tensor core):
+//   mode 0:       whole tiles c, c+G, c+2G, ...
+//   mode S >= 1:  the first floor(tiles / G) * G tiles as in mode 0; each tile of the last, partial wave
+//                 is cut into max(S, 2) slices of its K range, and the (slice, tile) items, tiles fastest,
+//                 go round-robin to the CTAs.  CTAs that run together then work on neighbouring tiles at
+//                 the same K blocks, as in the whole waves, and share operands in L2; a partial wave of
+//                 R tiles costs ceil(R*S/G)/S of a tile's time instead of a whole one.
+struct SegIterSlices {
+    int kbt, slices, stride, first_split, tail_tiles;
+    long long u, u_end;
+    int tile, kb0, kb1;
+    bool whole;                      // still in the whole-tile part
+    __device__ SegIterSlices(int n_tiles, int kbt_, int mode, int cta, int n_ctas)
+        : kbt(kbt_), slices(mode == 1 ? 2 : mode), stride(n_ctas) {
+        first_split = mode == 0 ? n_tiles : (n_tiles / n_ctas) * n_ctas;
+        tail_tiles = n_tiles - first_split;
+        whole = true;
+        u = cta;
+        u_end = first_split;
+    }
+    __device__ bool next() {
         if (whole) {
             if (u < u_end) {
                 tile = (int)u; kb0 = 0; kb1 = kbt;
@@ -164,13 +182,13 @@ struct SegIter {
             }
             whole = false;
             u -= first_split;                                  // first item of this CTA: its index continues
-            u_end = (long long)tail_tiles * mode;
+            u_end = (long long)tail_tiles * slices;
         }
         while (u < u_end) {
             const int slice = (int)(u / tail_tiles);
             tile = first_split + (int)(u % tail_tiles);
-            kb0 = (int)((long long)slice * kbt / mode);
-            kb1 = (int)((long long)(slice + 1) * kbt / mode);
+            kb0 = (int)((long long)slice * kbt / slices);
+            kb1 = (int)((long long)(slice + 1) * kbt / slices);
             u += stride;
             if (kb1 > kb0) return true;                        // more slices than K blocks: empty ones are skipped
         }
