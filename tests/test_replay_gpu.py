@@ -75,3 +75,46 @@ def test_weights_stored_in_32_bits_stay_so_when_serving_in_bfloat16(tmp_path, na
     for r, t in reqs.items():
         bad = first_bad(got[r], pm.logits(t), TOL["bfloat16"])
         assert bad is None, (name, r, bad)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+def test_first_tokens_of_a_sequence(plain_logits, name, dtype):
+    """The very first tokens: a request that starts with single tokens from an empty cache (the decode
+    kernels with one, two, three keys), one that starts with a two-token portion, and a third that
+    arrives while the others are under way; every position against the plain implementation."""
+    d, reqs, want = plain_logits[name]
+    names = list(reqs)[:3]
+    some = {r: reqs[r][:min(len(reqs[r]), 12)] for r in names}
+    steps, done = [], {r: 0 for r in names}
+
+    def feed(r, n):
+        n = min(n, len(some[r]) - done[r])
+        if n > 0:
+            steps.append(([(r, done[r], n)], []))
+            done[r] += n
+
+    first, second = names[0], names[1 % len(names)]
+    for _ in range(3):
+        feed(first, 1)                      # one token at a time from position 0
+    if second != first:
+        feed(second, 2)                     # a two-token portion from position 0
+    for r in names[2:]:
+        feed(r, 1)
+    while any(done[r] < len(some[r]) for r in names):
+        entries = []
+        for r in names:
+            if done[r] < len(some[r]):
+                entries.append((r, done[r], 1))
+                done[r] += 1
+        steps.append((entries, []))
+    steps[-1] = (steps[-1][0], list(names))
+    ecfg = EngineConfig(dtype=dtype, page_size=PAGE_SIZE[name], max_cache_tokens=3 * 16 * 4, max_live_requests=4,
+                        use_cuda_graphs=False)
+    runner = ModelRunner(d, ecfg)
+    for c in runner.kv_caches:
+        c.fill_(float("nan"))
+    got = run_trace(runner, some, steps)
+    for r in names:
+        bad = first_bad(got[r], want[r][:len(some[r])], TOL[dtype])
+        assert bad is None, f"{name}/{dtype}/{r}: first wrong position {bad[0]} (rel err {bad[1]:.3e})"
