@@ -23,7 +23,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# BASELINE.json configs[2]: the Qwen3-8B shape
+# the headline configuration: the Qwen3-8B shape
 SHAPE = dict(num_layers=36, hidden_size=4096, num_heads=32, num_kv_heads=8, head_dim=128,
              intermediate_size=12288, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6, max_position=40960)
 CONTEXT = 4096
@@ -199,7 +199,7 @@ def prefill_run(engine, iters: int, warmup: int, seed: int):
     return statistics.median(times)
 
 
-# BASELINE.json configs[3] and configs[4]: whole-workload runs through the scheduler
+# whole-workload runs through the scheduler (a 14B shape with mixed prompts, a 32B shape with long prompts)
 WORKLOADS = {
     "mixed14b": dict(shape=dict(num_layers=40, hidden_size=5120, num_heads=40, num_kv_heads=8, head_dim=128,
                                 intermediate_size=17408, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6,
