@@ -209,6 +209,9 @@ WORKLOADS = {
                                intermediate_size=25600, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6,
                                max_position=40960),
                     requests=16, prompt_lens=(8192, 8192), new_tokens=256, chunk=2048, context=8448),
+    # the headline shape in true 32-bit (FFMA products, float32 attention and cache) on short prompts
+    "fp32_short": dict(shape=dict(SHAPE), requests=4, prompt_lens=(64, 192), new_tokens=16, chunk=256, context=512,
+                       dtype="float32"),
 }
 
 
@@ -227,9 +230,10 @@ def run_workload(name: str, layers: int = 0) -> int:
     rng = random.Random(0)
     lens = [rng.randint(*w["prompt_lens"]) for _ in range(w["requests"])]
     cache_tokens = sum(-(-(n + w["new_tokens"] + 1) // PAGE_SIZE) * PAGE_SIZE for n in lens)
-    ecfg = tff.EngineConfig(dtype="bfloat16", page_size=PAGE_SIZE, max_cache_tokens=cache_tokens,
+    dtype = w.get("dtype", "bfloat16")
+    ecfg = tff.EngineConfig(dtype=dtype, page_size=PAGE_SIZE, max_cache_tokens=cache_tokens,
                             max_live_requests=w["requests"], max_tokens_per_step=w["chunk"], max_model_len=w["context"])
-    tensors = random_tensors_on_device(cfg, 0, "cuda", "bfloat16")
+    tensors = random_tensors_on_device(cfg, 0, "cuda", dtype)
     engine = tff.Engine(runner=tff.ModelRunner(config=cfg, tensors=tensors, engine_config=ecfg))
     del tensors
     torch.cuda.empty_cache()
@@ -256,7 +260,8 @@ def run_workload(name: str, layers: int = 0) -> int:
                       "total_tok_s": round((sum(lens) + gen) / dt, 1), "generated_tok_s": round(gen / dt, 1),
                       "mean_time_to_first_token_s": round(sum(first_token_at.values()) / max(1, len(first_token_at)), 3),
                       "pages_high_water": st["pages_high_water"], "pages_total": st["pages_total"],
-                      "preemptions": st["preemptions"], "dtype": "bf16", "data": "synthetic"}))
+                      "preemptions": st["preemptions"], "dtype": "bf16" if dtype == "bfloat16" else "fp32",
+                      "data": "synthetic"}))
     return 0
 
 
