@@ -162,7 +162,13 @@ def test_gemm_tc_all_epilogues(ops, M, N, K):
                                                   (130, 24576, 128, 0, 256, 0), (128, 64, 4096, 1, 128, 1),
                                                   (700, 1030, 520, 0, 256, 3), (2500, 2304, 264, 0, 256, 5),
                                                   (2500, 2304, 264, 0, 256, 8), (300, 311, 264, 0, 128, 8),
-                                                  (2048, 4096, 1024, 0, 256, 4), (512, 4096, 4096, 0, 256, 2)])
+                                                  (2048, 4096, 1024, 0, 256, 4), (512, 4096, 4096, 0, 256, 2),
+                                                  # bn = 512: 256 x 256 tiles on pairs of SMs (cta_group::2); 311 columns
+                                                  # of float32 do not suit TMA: single CTAs take over
+                                                  (700, 1030, 520, 0, 512, 0), (700, 1030, 520, 0, 512, 3),
+                                                  (2500, 2304, 264, 0, 512, 5), (300, 311, 264, 0, 512, 2),
+                                                  (2048, 4096, 1024, 0, 512, 4), (257, 512, 4096, 0, 512, 0),
+                                                  (129, 256, 64, 0, 512, 0), (4096, 512, 128, 0, 512, 8)])
 def test_gemm_tc_explicit_plans(ops, M, N, K, swap, bn, splits):
     """splits: 0 = whole tiles; 1 = stream-K shares with float32 adds; S >= 2 = the tiles of the last wave
     in S slices of their K range (more slices than K blocks leaves some empty)"""

@@ -28,15 +28,12 @@
 // memory, stops issuing work, lets its copies in flight land, frees its tensor memory and
 // returns.
 #include <type_traits>
-#include "tcgen05.cuh"
+#include "gemm_epilogue.cuh"
+#include "gemm_tc_pair.h"
 
 namespace {
 
 using namespace tc5;
-
-// write the product | add it to what ``out`` holds | write silu(gate) * up of a product whose columns
-// alternate between 64 gate and 64 up features (normal orientation, bfloat16 out, through TMA)
-enum Epilogue : int { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2 };
 
 template <int BN, bool TMA_OUT, bool SWAP = false> struct TileCfg {
     static constexpr int kStageBytes = BM * BK * 2 + BN * BK * 2;
@@ -220,69 +217,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_lane,   // operand whose r
                     }
                 }
             } else if constexpr (TMA_OUT) {
-                // 128-byte-wide column chunks: 32 float32 or 64 bfloat16 per row
-                constexpr int CW = 128 / (int)sizeof(TC);      // output columns per chunk
-                constexpr int AW = EPI == EPI_SWIGLU ? 128 : CW;   // accumulator columns per chunk
-                const uint32_t my_stage = staging + (uint32_t)((warp - 2) * 2) * 4096u;
-#pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += AW, ++chunk_no) {
-                    const uint32_t buf = my_stage + (chunk_no & 1) * 4096u;
-                    if (chunk_no >= 2) {                       // the store that last used this buffer has read it
-                        if (lane == 0) bulk_wait_read<1>();
-                        __syncwarp();
-                    }
-                    uint32_t packed[32];                       // this thread's row: 128 bytes
-                    if constexpr (EPI == EPI_SWIGLU) {
-                        // columns [c0, c0+64) are the gate, [c0+64, c0+128) the up projection of the
-                        // same 64 features: silu(g) * u, silu(g) = g / (1 + exp(-g))
-#pragma unroll
-                        for (int h = 0; h < 4; ++h) {
-                            uint32_t g[16], u[16];
-                            tmem_ld16(t_addr + (uint32_t)(c0 + h * 16), g);
-                            tmem_ld16(t_addr + (uint32_t)(c0 + 64 + h * 16), u);
-                            tmem_ld_wait();
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                const float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
-                                const float a0 = (g0 / (1.0f + __expf(-g0))) * __uint_as_float(u[2 * j]);
-                                const float a1 = (g1 / (1.0f + __expf(-g1))) * __uint_as_float(u[2 * j + 1]);
-                                __nv_bfloat162 b2 = __floats2bfloat162_rn(a0, a1);
-                                packed[h * 8 + j] = *reinterpret_cast<uint32_t*>(&b2);
-                            }
-                        }
-                    } else {
-#pragma unroll
-                        for (int h = 0; h < CW / 16; ++h) {
-                            uint32_t v[16];
-                            tmem_ld16(t_addr + (uint32_t)(c0 + h * 16), v);
-                            tmem_ld_wait();
-                            if constexpr (sizeof(TC) == 4) {
-#pragma unroll
-                                for (int j = 0; j < 16; ++j) packed[h * 16 + j] = v[j];
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < 8; ++j) {
-                                    __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
-                                    packed[h * 8 + j] = *reinterpret_cast<uint32_t*>(&b2);
-                                }
-                            }
-                        }
-                    }
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) {              // 16-byte chunk c of row ``lane`` at chunk c ^ (lane % 8)
-                        const uint32_t dst = buf + (uint32_t)lane * 128u + (uint32_t)((c ^ (lane & 7)) << 4);
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[4 * c]),
-                                     "r"(packed[4 * c + 1]), "r"(packed[4 * c + 2]), "r"(packed[4 * c + 3]) : "memory");
-                    }
-                    fence_async_smem();
-                    __syncwarp();
-                    if (lane == 0) {
-                        if (EPI == EPI_SWIGLU) tma_store_2d(&tm_out, buf, (col_row0 + c0) / 2, lane_row0 + q * 32);
-                        else if (EPI == EPI_ADD || partial) tma_reduce_add_2d(&tm_out, buf, col_row0 + c0, lane_row0 + q * 32);
-                        else tma_store_2d(&tm_out, buf, col_row0 + c0, lane_row0 + q * 32);
-                        bulk_commit();
-                    }
-                }
+                epilogue_quarter_tma<BN, EPI, TC>(t_addr, staging + (uint32_t)((warp - 2) * 2) * 4096u, chunk_no, lane, q,
+                                                  lane_row0, col_row0, partial, &tm_out);
             } else {
                 const int lr = lane_row0 + q * 32 + lane;          // row of the lane operand
 #pragma unroll 1
@@ -368,7 +304,7 @@ int dispatch_epi(const CUtensorMap& tl, const CUtensorMap& tc, const CUtensorMap
 
 // out[M, N] (+)= A[M, K] * W[N, K]^T; A, W bfloat16.
 //   swap      0: A rows on TMEM lanes (tiles 128 x bn over M x N); 1: W rows on lanes (tiles 128 x bn over N x M)
-//   bn        16, 32, 64, 128 or 256
+//   bn        16, 32, 64, 128 or 256; 512 (normal orientation): 256 x 256 tiles on pairs of SMs
 //   add       1: the product is added to what ``out`` (float32) holds -- a residual stream in place
 //   stream_k  1: (tile, K block) units are dealt in equal shares; S >= 2: the tiles of the last, partial wave
 //             are cut into S slices of their K range; tiles that are split between CTAs
@@ -381,6 +317,18 @@ TFF_API int tff_gemm_tc(const void* A, const void* W, void* out, int out_is_bf16
     if (K % 8 != 0) return TFF_ERR_UNSUPPORTED;                         // TMA row pitch must be a multiple of 16 bytes
     if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return TFF_ERR_UNSUPPORTED;
     if (tff_device_error_flag() == nullptr) return TFF_ERR_LAUNCH;
+    if (bn == 512) {
+        // pairs of SMs: the output must suit TMA (row pitch a multiple of 16 bytes, aligned base); else single CTAs
+        const int elt = out_is_bf16 ? 2 : 4;
+        if (!swap && ((long long)N * elt) % 16 == 0 && ((uintptr_t)out & 15) == 0) {
+            CUtensorMap ta, tw, to2;
+            if (!tff_tensor_map_2d(A, M, K, BM, BK, 2, &ta)) return TFF_ERR_DRIVER;
+            if (!tff_tensor_map_2d(W, N, K, 128, BK, 2, &tw)) return TFF_ERR_DRIVER;
+            if (!tff_tensor_map_2d(out, M, N, 32, 128 / elt, elt, &to2)) return TFF_ERR_DRIVER;
+            return tff_gemm_tc_pair_launch(ta, tw, to2, add ? EPI_ADD : EPI_STORE, out_is_bf16, M, N, K, stream_k, stream);
+        }
+        bn = 256;
+    }
     const void* lane_ptr = swap ? W : A;
     const void* col_ptr = swap ? A : W;
     const int rows_lane = swap ? N : M, rows_col = swap ? M : N;
@@ -418,11 +366,16 @@ TFF_API int tff_gemm_tc(const void* A, const void* W, void* out, int out_is_bf16
 TFF_API int tff_gemm_tc_swiglu(const void* A, const void* W, void* out, int M, int I, int K, int bn, cudaStream_t stream) {
     if (M <= 0 || I <= 0) return TFF_OK;
     if (K <= 0) return TFF_ERR_BAD_ARGUMENT;
-    if (K % 8 != 0 || I % 64 != 0 || (bn != 128 && bn != 256)) return TFF_ERR_UNSUPPORTED;
+    if (K % 8 != 0 || I % 64 != 0 || (bn != 128 && bn != 256 && bn != 512)) return TFF_ERR_UNSUPPORTED;
     if (((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ((uintptr_t)out & 15)) return TFF_ERR_UNSUPPORTED;
     if (tff_device_error_flag() == nullptr) return TFF_ERR_LAUNCH;
     CUtensorMap tl, tc, to;
     if (!tff_tensor_map_2d(A, M, K, BM, BK, 2, &tl)) return TFF_ERR_DRIVER;
+    if (bn == 512) {                                  // 256 x 256 tiles on pairs of SMs
+        if (!tff_tensor_map_2d(W, 2ll * I, K, 128, BK, 2, &tc)) return TFF_ERR_DRIVER;
+        if (!tff_tensor_map_2d(out, M, I, 32, 64, 2, &to)) return TFF_ERR_DRIVER;
+        return tff_gemm_tc_pair_launch(tl, tc, to, EPI_SWIGLU, 1, M, 2 * I, K, 0, stream);
+    }
     if (!tff_tensor_map_2d(W, 2ll * I, K, bn, BK, 2, &tc)) return TFF_ERR_DRIVER;
     if (!tff_tensor_map_2d(out, M, I, 32, 64, 2, &to)) return TFF_ERR_DRIVER;
     if (bn == 256) return launch_tc<256, false, EPI_SWIGLU, bf16, true>(tl, tc, to, out, M, 2 * I, K, I, 0, stream);

@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 from typing import Optional
 
 import numpy as np
@@ -133,6 +134,7 @@ class CudaKernels:
         self.launches += 1
 
     SWAP_MAX_M = 256          # up to this many rows the weights are the 128-row operand
+    USE_SM_PAIRS = os.environ.get("TFFINFER_SM_PAIRS", "1") != "0"   # prompt-sized products on tcgen05 cta_group::2
     NUM_SMS = 148
 
     def tc_plan(self, M: int, N: int, K: int, out_is_f32: bool, add: bool = False):
@@ -146,11 +148,17 @@ class CudaKernels:
             tiles = -(-N // 128)
             stream_k = 1 if (out_is_f32 and tiles < 4 * self.NUM_SMS) else 0
             return 1, bn, stream_k
-        bn = 256 if N > 128 else 128
+        if N <= 128:
+            bn, tiles, ctas = 128, -(-M // 128), self.NUM_SMS
+        elif self.USE_SM_PAIRS:
+            # 256 x 256 tiles on pairs of SMs (bn = 512 stands for that)
+            bn, tiles, ctas = 512, -(-M // 256) * -(-N // 256), self.NUM_SMS // 2
+        else:
+            bn, tiles, ctas = 256, -(-M // 128) * -(-N // 256), self.NUM_SMS
         if not (add and out_is_f32):
             return 0, bn, 0
         # added to a float32 buffer, shares of a tile can meet there: the last wave may be cut along K
-        return 0, bn, self.tail_slices(-(-M // 128) * -(-N // bn), -(-K // 64), self.NUM_SMS)
+        return 0, bn, self.tail_slices(tiles, -(-K // 64), ctas)
 
     @staticmethod
     def tail_slices(tiles: int, k_blocks: int, ctas: int) -> int:
@@ -382,7 +390,8 @@ class CudaKernels:
         if tc and T > self.SWAP_MAX_M and block == 64 and out.dtype == torch.bfloat16 and out.data_ptr() % 16 == 0:
             # prompt-sized: the activation is applied in the product's epilogue
             self._check(self.lib.tff_gemm_tc_swiglu(_ptr(a), _ptr(w_gate_up), _ptr(out), _c_int(T), _c_int(I),
-                                                    _c_int(K), _c_int(256), self._stream()), "gemm_tc_swiglu")
+                                                    _c_int(K), _c_int(512 if self.USE_SM_PAIRS else 256), self._stream()),
+                        "gemm_tc_swiglu")
             self.launches += 1
             return
         small = tc and T <= self.SWAP_MAX_M
