@@ -62,6 +62,13 @@ class CpuOps:
         table[..., 0] = torch.cos(ang).to(torch.float32)
         table[..., 1] = torch.sin(ang).to(torch.float32)
 
+    def qkv_project(self, h, w_qkv, q_out, q_w, k_w, eps, table, rot_dim, batch, block_table, kv_cache,
+                    kv_layer, page_size, nq, nkv, d, write_cache):
+        qkv = self.projection_buffer(h.shape[0], (nq + 2 * nkv) * d, h.device, h.dtype)
+        self.gemm(h, w_qkv, qkv)
+        self.qk_norm_rope_kv_write(qkv, q_out, q_w, k_w, eps, table, rot_dim, batch, block_table, kv_cache,
+                                   kv_layer, page_size, nq, nkv, d, write_cache)
+
     def qk_norm_rope_kv_write(self, qkv, q_out, q_w, k_w, eps, table, rot_dim, batch, block_table, kv_cache,
                               kv_layer, page_size, nq, nkv, d, write_cache):
         T = qkv.shape[0]

@@ -249,6 +249,48 @@ def test_qk_norm_rope_write_then_attention(ops, case, dt):
     assert rel_err(out_g, out_c) < (3e-6 if dt == torch.float32 else 1e-2)
 
 
+@pytest.mark.parametrize("nq,nkv,page,new,old,K,norm,rope", [
+    (32, 8, 16, [300, 450], [17, 0], 1024, True, True),      # two requests, the first with tokens cached
+    (40, 8, 16, [777], [100], 512, True, True),              # 56 heads: 28 tiles of two heads
+    (5, 2, 32, [600], [0], 256, True, True),                 # 9 heads: the last tile holds one head
+    (8, 2, 8, [257], [3], 128, False, True),                 # no q/k norm
+    (8, 2, 16, [300], [0], 128, True, False),                # no rotation
+])
+def test_qkv_projection_with_norm_rope_and_cache_write_in_the_epilogue(ops, nq, nkv, page, new, old, K, norm, rope):
+    """Prompt-sized bfloat16 portions with heads of 128 run the projection, q/k RMSNorm, rotation and cache write
+    as one kernel (the product on pairs of SMs with its q/k/v epilogue); against the plain twin of the two steps."""
+    d, dt = 128, torch.bfloat16
+    entries, tables, cache, _ = _paged_case(nq, nkv, d, page, new, old, 0, dt, seed=50)
+    T = sum(new)
+    cpu = CpuOps()
+    table = torch.empty(2048, d // 2, 2); cpu.rope_table(table, 1e6, d)
+    qw, kw = 1 + 0.1 * g((d,), torch.float32, 51), 1 + 0.1 * g((d,), torch.float32, 52)
+    h = g((T, K), dt, 53)
+    w = g(((nq + 2 * nkv) * d, K), dt, 54, 0.05)
+    bc = build_step_batch(entries, old, list(range(len(new))), [tables], "cpu")
+    bg = build_step_batch(entries, old, list(range(len(new))), [tables], DEV)
+    q_c, cache_c = torch.empty(T, nq * d, dtype=dt), cache.clone()
+    cpu.qkv_project(h, w, q_c, qw if norm else None, kw if norm else None, 1e-6, table if rope else None,
+                    d if rope else 0, bc, bc.block_tables[0], cache_c, 1, page, nq, nkv, d, True)
+    q_g, cache_g = torch.full((T, nq * d), float("nan"), dtype=dt, device=DEV), cache.clone().to(DEV)
+    launches = ops.launches
+    ops.qkv_project(h.to(DEV), w.to(DEV), q_g, qw.to(DEV) if norm else None, kw.to(DEV) if norm else None, 1e-6,
+                    table.to(DEV) if rope else None, d if rope else 0, bg, bg.block_tables[0], cache_g, 1, page,
+                    nq, nkv, d, True)
+    assert ops.launches - launches == 1, "expected the one-kernel path"
+    ops.check_errors()
+    assert rel_err(q_g, q_c) < 1e-2
+    assert rel_err(cache_g, cache_c) < 1e-2
+    assert torch.equal(cache_g[:, 0].cpu(), cache[:, 0])            # the other layer is untouched
+    # without the cache write only q is produced
+    cache_g2 = cache.clone().to(DEV)
+    ops.qkv_project(h.to(DEV), w.to(DEV), q_g, qw.to(DEV) if norm else None, kw.to(DEV) if norm else None, 1e-6,
+                    table.to(DEV) if rope else None, d if rope else 0, bg, bg.block_tables[0], cache_g2, 1, page,
+                    nq, nkv, d, False)
+    assert torch.equal(cache_g2.cpu(), cache)
+    assert rel_err(q_g, q_c) < 1e-2
+
+
 FLASH_CASES = [
     # nq, nkv, d, page, new, old, window, splits
     (32, 8, 128, 16, [1, 1, 1], [300, 17, 2049], 0, 1),        # decode, keys mode

@@ -7,7 +7,9 @@ namespace tc5 {
 
 // write the product | add it to what ``out`` holds | write silu(gate) * up of a product whose columns
 // alternate between 64 gate and 64 up features (normal orientation, bfloat16 out, through TMA)
-enum Epilogue : int { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2 };
+// EPI_QKV: the product is a q/k/v projection with heads of 128: per-head RMSNorm of q and k, rotation, q to its
+// own tensor and k, v to the token's slot of the paged cache (epilogue_quarter_qkv below)
+enum Epilogue : int { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_QKV = 3 };
 
 // One warp's quarter (32 rows) of the tile: TMEM -> registers -> two alternating 4 KB boxes of swizzled
 // shared memory (``my_stage``) -> TMA stores, or float32 add-reductions when the product is added to what
@@ -76,6 +78,126 @@ __device__ __forceinline__ void epilogue_quarter_tma(uint32_t t_addr, uint32_t m
             else if (EPI == EPI_ADD || partial) tma_reduce_add_2d(tm_out, buf, col_row0 + c0, lane_row0 + q * 32);
             else tma_store_2d(tm_out, buf, col_row0 + c0, lane_row0 + q * 32);
             bulk_commit();
+        }
+    }
+}
+
+
+// What the q/k/v epilogue needs beside the accumulators.  Columns of the product are
+// [q heads | k heads | v heads] of 128 each, rows are tokens.
+struct QkvEpilogue {
+    bf16* q_out;                 // [T, nq * 128]
+    bf16* cache;                 // paged cache (may be null when write_cache == 0)
+    const float* q_w;            // norm weights of q and k heads [128] (null: no norm)
+    const float* k_w;
+    const float2* table;         // (cos, sin)[max_pos][64] (null: no rotation)
+    const int* positions;        // [T]
+    const int* tok_req;          // [T] row of the block table
+    const int* block_table;
+    KvLayout L;
+    float eps;
+    int table_width, layer, write_cache, nq, nkv, T, max_pos;
+};
+
+__device__ __forceinline__ void store16_bf16(bf16* dst, const float* v) {
+    uint32_t w[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        __nv_bfloat162 b2 = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+        w[j] = *reinterpret_cast<uint32_t*>(&b2);
+    }
+    *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+    *reinterpret_cast<uint4*>(dst + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+}
+
+// One warp's quarter (32 token rows) of a 128 x 256 accumulator tile = two heads of a q/k/v projection.
+// A thread owns a token's row, so the sum of squares of a head and the rotation partners (i, i + 64) are
+// its own: no exchange between threads.  Same arithmetic as qk_norm_rope_kv_write in elementwise.cu,
+// on the unrounded float32 accumulators.  TMEM loads are executed by the whole warp, stores by the
+// threads whose token exists (and whose page exists).
+__device__ __forceinline__ void epilogue_quarter_qkv(uint32_t t_addr, int lane, int q, int lane_row0, int col_row0,
+                                                     const QkvEpilogue& e) {
+    const int t = lane_row0 + q * 32 + lane;
+    const bool valid = t < e.T;
+    int pos = 0, req = 0;
+    if (valid) { pos = e.positions[t]; req = e.tok_req[t]; }
+    const bool rotate = e.table != nullptr && pos >= 0 && pos < e.max_pos;
+    const int heads = e.nq + 2 * e.nkv;
+#pragma unroll 1
+    for (int hh = 0; hh < 2; ++hh) {
+        const int head = col_row0 / 128 + hh;
+        if (head >= heads) break;
+        const bool is_q = head < e.nq, is_k = !is_q && head < e.nq + e.nkv;
+        if (!is_q && !e.write_cache) continue;
+        bf16* dst = nullptr;
+        if (valid) {
+            if (is_q) {
+                dst = e.q_out + (size_t)t * e.nq * 128 + (size_t)head * 128;
+            } else {
+                const int kvh = is_k ? head - e.nq : head - e.nq - e.nkv;
+                const int page = e.block_table[(size_t)req * e.table_width + pos / e.L.page_size];
+                if (page >= 0)
+                    dst = e.cache + (size_t)page * e.L.page_stride + (size_t)e.layer * e.L.layer_stride +
+                          (is_k ? 0 : e.L.kv_stride) + (size_t)kvh * e.L.head_stride + (size_t)(pos % e.L.page_size) * 128;
+            }
+        }
+        const uint32_t th = t_addr + (uint32_t)(hh * 128);
+        if (!is_q && !is_k) {                          // a v head: as it is
+#pragma unroll 1
+            for (int c0 = 0; c0 < 128; c0 += 16) {
+                uint32_t v[16];
+                tmem_ld16(th + (uint32_t)c0, v);
+                tmem_ld_wait();
+                float f[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) f[j] = __uint_as_float(v[j]);
+                if (dst) store16_bf16(dst + c0, f);
+            }
+            continue;
+        }
+        const float* w = is_q ? e.q_w : e.k_w;
+        float rs = 1.f;
+        if (w != nullptr) {
+            float ss = 0.f;
+#pragma unroll 1
+            for (int c0 = 0; c0 < 128; c0 += 16) {
+                uint32_t v[16];
+                tmem_ld16(th + (uint32_t)c0, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) ss = fmaf(__uint_as_float(v[j]), __uint_as_float(v[j]), ss);
+            }
+            rs = rsqrtf(ss / 128.f + e.eps);
+        }
+#pragma unroll 1
+        for (int i0 = 0; i0 < 64; i0 += 16) {
+            uint32_t lo[16], hi[16];
+            tmem_ld16(th + (uint32_t)i0, lo);
+            tmem_ld16(th + (uint32_t)(64 + i0), hi);
+            tmem_ld_wait();
+            float a[16], b[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) { a[j] = __uint_as_float(lo[j]); b[j] = __uint_as_float(hi[j]); }
+            if (w != nullptr) {
+#pragma unroll
+                for (int j = 0; j < 16; j += 4) {
+                    const float4 wa = *reinterpret_cast<const float4*>(w + i0 + j);
+                    const float4 wb = *reinterpret_cast<const float4*>(w + 64 + i0 + j);
+                    a[j] = (a[j] * rs) * wa.x; a[j + 1] = (a[j + 1] * rs) * wa.y; a[j + 2] = (a[j + 2] * rs) * wa.z; a[j + 3] = (a[j + 3] * rs) * wa.w;
+                    b[j] = (b[j] * rs) * wb.x; b[j + 1] = (b[j + 1] * rs) * wb.y; b[j + 2] = (b[j + 2] * rs) * wb.z; b[j + 3] = (b[j + 3] * rs) * wb.w;
+                }
+            }
+            if (rotate) {
+                const float4* cs = reinterpret_cast<const float4*>(e.table + (size_t)pos * 64 + i0);
+#pragma unroll
+                for (int j = 0; j < 16; j += 2) {
+                    const float4 c2 = cs[j >> 1];          // (cos, sin) of elements j and j + 1
+                    const float a0 = a[j], b0 = b[j], a1 = a[j + 1], b1 = b[j + 1];
+                    a[j] = a0 * c2.x - b0 * c2.y;  b[j] = a0 * c2.y + b0 * c2.x;
+                    a[j + 1] = a1 * c2.z - b1 * c2.w;  b[j + 1] = a1 * c2.w + b1 * c2.z;
+                }
+            }
+            if (dst) { store16_bf16(dst + i0, a); store16_bf16(dst + 64 + i0, b); }
         }
     }
 }

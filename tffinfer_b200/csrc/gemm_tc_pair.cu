@@ -87,7 +87,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a,     // activations [M, K], box 64 x 128
                     const __grid_constant__ CUtensorMap tm_w,     // weights [N, K], box 64 x 128 (half a tile's rows)
                     const __grid_constant__ CUtensorMap tm_out,   // output, boxes of 128 bytes x 32 rows
-                    int rows_m, int rows_n, int K, int stream_k, int* error_flag) {
+                    int rows_m, int rows_n, int K, int stream_k, int* error_flag,
+                    const QkvEpilogue qkv) {                  // EPI_QKV only
     constexpr int STAGES = P_STAGES;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -194,8 +195,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a,     // activations
             const int lane_row0 = ((it.tile % n_m_pairs) * 2 + (int)rank) * BM, col_row0 = (it.tile / n_m_pairs) * PBN;
             const uint32_t t_addr = tmem_base + acc * PBN + ((uint32_t)(q * 32) << 16);
             const bool partial = stream_k && (it.kb1 - it.kb0) < kbt;
-            epilogue_quarter_tma<PBN, EPI, TC>(t_addr, staging + (uint32_t)((warp - 2) * 2) * 4096u, chunk_no, lane, q,
-                                               lane_row0, col_row0, partial, &tm_out);
+            if constexpr (EPI == EPI_QKV)
+                epilogue_quarter_qkv(t_addr, lane, q, lane_row0, col_row0, qkv);
+            else
+                epilogue_quarter_tma<PBN, EPI, TC>(t_addr, staging + (uint32_t)((warp - 2) * 2) * 4096u, chunk_no, lane, q,
+                                                   lane_row0, col_row0, partial, &tm_out);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(first_tempty[acc]);
@@ -221,7 +225,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a,     // activations
 
 template <int EPI, typename TC>
 int launch_pair(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& to, int M, int N, int K, int stream_k,
-                cudaStream_t stream) {
+                cudaStream_t stream, const QkvEpilogue& qkv = QkvEpilogue()) {
     auto kern = gemm_tc_pair_kernel<EPI, TC>;
     static int max_clusters = -1;                 // clusters of this kernel the device runs at a time
     if (max_clusters < 0) {
@@ -246,10 +250,38 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap&
     if (clusters <= 0) return TFF_ERR_LAUNCH;
     if (clusters > units) clusters = units;
     return tff_launch_pdl(kern, dim3((unsigned)(2 * clusters)), dim3(NUM_THREADS), (size_t)P_SMEM_BYTES, stream, ta, tw, to,
-                          M, N, K, stream_k, tff_device_error_flag());
+                          M, N, K, stream_k, tff_device_error_flag(), qkv);
 }
 
 }  // namespace
+
+// The q/k/v projection of a prompt portion with everything up to the cache write in its epilogue:
+//   [q | k | v] = A[M, K] * W[(nq + 2 nkv) * 128, K]^T; q and k heads normalised (weights q_w, k_w of 128, or null)
+//   and rotated by ``table`` ((cos, sin)[max_pos][64], or null); q to q_out [M, nq * 128], k and v to the token's
+//   slot of the paged cache (write_cache != 0).  Heads of 128 only; bfloat16 in and out.
+TFF_API int tff_gemm_tc_qkv_rope(const void* A, const void* W, int M, int K, void* q_out, const float* q_w, const float* k_w,
+                                 float eps, const float* table, int max_pos, const int* positions, const int* tok_req,
+                                 const int* block_table, int table_width, void* cache, int cache_layers, int layer,
+                                 int page_size, int write_cache, int nq, int nkv, cudaStream_t stream) {
+    if (M <= 0) return TFF_OK;
+    if (K <= 0 || nq <= 0 || nkv <= 0 || positions == nullptr || q_out == nullptr) return TFF_ERR_BAD_ARGUMENT;
+    if (write_cache && (cache == nullptr || block_table == nullptr || tok_req == nullptr || page_size <= 0)) return TFF_ERR_BAD_ARGUMENT;
+    if (K % 8 != 0 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ((uintptr_t)q_out & 15) || ((uintptr_t)cache & 15) ||
+        ((uintptr_t)q_w & 15) || ((uintptr_t)k_w & 15) || ((uintptr_t)table & 15))
+        return TFF_ERR_UNSUPPORTED;
+    if (tff_device_error_flag() == nullptr) return TFF_ERR_LAUNCH;
+    const int N = (nq + 2 * nkv) * 128;
+    CUtensorMap ta, tw;
+    if (!tff_tensor_map_2d(A, M, K, BM, BK, 2, &ta)) return TFF_ERR_DRIVER;
+    if (!tff_tensor_map_2d(W, N, K, 128, BK, 2, &tw)) return TFF_ERR_DRIVER;
+    QkvEpilogue e;
+    e.q_out = (bf16*)q_out; e.cache = (bf16*)cache; e.q_w = q_w; e.k_w = k_w; e.table = (const float2*)table;
+    e.positions = positions; e.tok_req = tok_req; e.block_table = block_table;
+    e.L = make_kv_layout(cache_layers, nkv, page_size > 0 ? page_size : 1, 128);
+    e.eps = eps; e.table_width = table_width; e.layer = layer; e.write_cache = write_cache; e.nq = nq; e.nkv = nkv;
+    e.T = M; e.max_pos = max_pos;
+    return launch_pair<EPI_QKV, bf16>(ta, tw, ta, M, N, K, 0, stream, e);
+}
 
 int tff_gemm_tc_pair_launch(const CUtensorMap& tm_a, const CUtensorMap& tm_w_half, const CUtensorMap& tm_out, int epilogue,
                             int out_is_bf16, int M, int N, int K, int stream_k, cudaStream_t stream) {

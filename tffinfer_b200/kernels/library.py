@@ -306,6 +306,39 @@ class CudaKernels:
             self._acc_zero[qkv.data_ptr()] = True
         self.launches += 1
 
+    def qkv_project(self, h, w_qkv, q_out, q_w, k_w, eps, table, rot_dim, batch, block_table, kv_cache,
+                    kv_layer, page_size, nq, nkv, d, write_cache) -> None:
+        """The q/k/v projection of ``h`` with ``w_qkv`` ([q heads | k heads | v heads] rows), per-head RMSNorm of
+        q and k, rotation, q into ``q_out`` and k, v into the tokens' cache slots.  The projection's accumulators
+        stay in float32 until q and k have been normalised.  Prompt-sized bfloat16 batches with heads of 128 do all
+        of it in the epilogue of the product on pairs of SMs; everything else is the product into a float32 buffer
+        followed by qk_norm_rope_kv_write."""
+        T, K = h.shape
+        fused = (self.USE_SM_PAIRS and T > self.SWAP_MAX_M and d == 128 and h.dtype == torch.bfloat16
+                 and w_qkv.dtype == torch.bfloat16 and q_out.dtype == torch.bfloat16 and K % 8 == 0
+                 and (table is None or rot_dim == d) and (kv_cache is None or kv_cache.dtype == torch.bfloat16)
+                 and (not write_cache or kv_cache is not None)
+                 and all(t is None or t.data_ptr() % 16 == 0 for t in (h, w_qkv, q_out, q_w, k_w, table, kv_cache)))
+        if not fused:
+            qkv = self.projection_buffer(T, (nq + 2 * nkv) * d, h.device, h.dtype)
+            self.gemm(h, w_qkv, qkv)
+            self.qk_norm_rope_kv_write(qkv, q_out, q_w, k_w, eps, table, rot_dim, batch, block_table, kv_cache,
+                                       kv_layer, page_size, nq, nkv, d, write_cache)
+            return
+        self._need_cuda(h, w_qkv, q_out, q_w, k_w, table, block_table, kv_cache)
+        assert tuple(w_qkv.shape) == ((nq + 2 * nkv) * d, K) and tuple(q_out.shape) == (T, nq * d)
+        if write_cache:
+            assert tuple(kv_cache.shape[2:]) == (2, nkv, page_size, d)
+        layers = kv_cache.shape[1] if kv_cache is not None else 1
+        self._check(self.lib.tff_gemm_tc_qkv_rope(
+            _ptr(h), _ptr(w_qkv), _c_int(T), _c_int(K), _ptr(q_out), _ptr(q_w), _ptr(k_w), _c_float(eps),
+            _ptr(table), _c_int(table.shape[0] if table is not None else 0),
+            _ptr(batch.positions), _ptr(batch.tok_req), _ptr(block_table),
+            _c_int(block_table.shape[1] if block_table is not None else 0),
+            _ptr(kv_cache), _c_int(layers), _c_int(kv_layer), _c_int(page_size), _c_int(1 if write_cache else 0),
+            _c_int(nq), _c_int(nkv), self._stream()), "gemm_tc_qkv_rope")
+        self.launches += 1
+
     def attention(self, q, batch, block_table, kv_cache, kv_layer, page_size, out,
                   nq, nkv, d, scale, window) -> None:
         """q [T, nq*d] (normed, rotated) against the paged cache -> out [T, nq*d]."""

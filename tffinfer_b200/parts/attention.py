@@ -72,13 +72,12 @@ class GQAttention(Mixer):
     def forward(self, h, ctx: LayerContext, residual):
         ops, batch = ctx.ops, ctx.batch
         T = h.shape[0]
-        # the projection's accumulators stay in float32 until q and k have been normalised
-        qkv = ops.projection_buffer(T, self.q_width + 2 * self.kv_width, h.device, h.dtype)
-        ops.gemm(h, self.w_qkv, qkv)
+        # projection, q/k norm, rotation and cache write: the kernel library may do them in one kernel; the
+        # projection's accumulators stay in float32 until q and k have been normalised
         q = torch.empty((T, self.q_width), dtype=h.dtype, device=h.device)
         rot = ctx.position.rotary() if ctx.position is not None else None
-        ops.qk_norm_rope_kv_write(
-            qkv, q, self.q_norm_w, self.k_norm_w, self.qk_norm_eps,
+        ops.qkv_project(
+            h, self.w_qkv, q, self.q_norm_w, self.k_norm_w, self.qk_norm_eps,
             rot[0] if rot else None, rot[1] if rot else 0,
             batch, ctx.block_table, ctx.kv_cache, ctx.kv_layer, ctx.page_size,
             self.num_heads, self.num_kv_heads, self.head_dim, ctx.write_cache)
