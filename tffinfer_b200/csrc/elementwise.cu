@@ -67,13 +67,35 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
         const float4* x4 = reinterpret_cast<const float4*>(xr);
         const float4* w4 = reinterpret_cast<const float4*>(w);
         const int n4 = dim >> 2;
-        for (int i = threadIdx.x; i < n4; i += NT) {
+        // a thread's first KEEP pieces stay in registers between the two passes (rows up to 16 * KEEP * NT / 4
+        // elements are read from memory once); the loads of a pass are issued together
+        constexpr int KEEP = 4;
+        float4 keep[KEEP];
+#pragma unroll
+        for (int k = 0; k < KEEP; ++k) {
+            const int i = threadIdx.x + k * NT;
+            keep[k] = i < n4 ? x4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int k = 0; k < KEEP; ++k) {
+            ss = fmaf(keep[k].x, keep[k].x, ss); ss = fmaf(keep[k].y, keep[k].y, ss);
+            ss = fmaf(keep[k].z, keep[k].z, ss); ss = fmaf(keep[k].w, keep[k].w, ss);
+        }
+        for (int i = threadIdx.x + KEEP * NT; i < n4; i += NT) {
             const float4 v = x4[i];
             ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
         }
         ss = block_sum<NT>(ss, red);
         const float rs = rsqrtf(ss / (float)dim + eps);
-        for (int i = threadIdx.x; i < n4; i += NT) {
+#pragma unroll
+        for (int k = 0; k < KEEP; ++k) {
+            const int i = threadIdx.x + k * NT;
+            if (i < n4) {
+                const float4 v = keep[k], g = w4[i];
+                store4<TO>(o + 4 * i, (v.x * rs) * g.x, (v.y * rs) * g.y, (v.z * rs) * g.z, (v.w * rs) * g.w);
+            }
+        }
+        for (int i = threadIdx.x + KEEP * NT; i < n4; i += NT) {
             const float4 v = x4[i], g = w4[i];
             store4<TO>(o + 4 * i, (v.x * rs) * g.x, (v.y * rs) * g.y, (v.z * rs) * g.z, (v.w * rs) * g.w);
         }
