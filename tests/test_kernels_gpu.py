@@ -131,7 +131,7 @@ def test_gemm_simt_rows_do_not_depend_on_the_batch(ops):
 
 TC_SHAPES = [(1, 128, 64), (8, 6144, 4096), (5, 311, 80), (16, 256, 128), (17, 384, 200), (64, 4096, 1024),
              (100, 1000, 512), (256, 512, 4096), (257, 512, 256), (300, 311, 264), (1024, 768, 512),
-             (2048, 4096, 4096), (128, 128, 8), (130, 6144, 4096)]
+             (2048, 4096, 4096), (128, 128, 8), (130, 6144, 4096), (300, 1000, 264), (513, 1256, 72)]
 
 
 @pytest.mark.parametrize("M,N,K", TC_SHAPES)
