@@ -140,7 +140,9 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_cache, const DecodePar
     }
     __syncthreads();
     pdl_launch_dependents();
-    pdl_wait();
+    // What the kernel ahead wrote is the queries and the cache slots of the tokens this step brings; the
+    // step's batch arrays and the keys of earlier steps are older.  The producer therefore asks for its
+    // first stages before it waits for that kernel, the compute warps wait before they read the queries.
 
     const int b = p.req_ids ? p.req_ids[blockIdx.z] : (int)blockIdx.z;
     const int q0 = p.q_start[b];
@@ -161,10 +163,13 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_cache, const DecodePar
         const int ppb = BLOCK_N >> p.page_shift;                   // pages per 64-key block = boxes per stage (<= 8)
         const int j = lane;
         const uint32_t box_bytes = (uint32_t)(2 * D * 2) << p.page_shift;      // K and V of one page
+        const int first_new_blk = pos0 / BLOCK_N;                  // key blocks from here on hold slots written just now
+        bool waited = false;
         for (int blk = kb_begin; blk < kb_end; ++blk) {
             const int i = blk - kb_begin, s = i % NSTAGES;
             const uint32_t round = i / NSTAGES;
             bool ok = true;
+            if (!waited && (blk >= first_new_blk || round > 0)) { pdl_wait(); waited = true; }
             if (round > 0) {
                 if (lane == 0) ok = mbar_wait(empty_bar(s), (round - 1) & 1, abort_flag);
                 ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -187,6 +192,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_cache, const DecodePar
     }
 
     // ---------------------------------------------------------------- compute warps
+    pdl_wait();
     // the query tile: packed rows (token, head of the group), chunks XOR-swizzled by row % 8
     for (int idx = tid; idx < 16 * CH; idx += 128) {
         const int row = idx / CH, chunk = idx % CH;
