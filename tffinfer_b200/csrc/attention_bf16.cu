@@ -326,11 +326,13 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
                                     bf16* __restrict__ out, int num_splits, const int* __restrict__ q_start,
                                     const int* __restrict__ req_ids, int nq) {
     pdl_launch_dependents();          // the next kernel may become resident (it waits before it reads or writes)
-    pdl_wait();
+    // the step's batch arrays are older than the kernel ahead: they are read before waiting for it
     const int b = req_ids ? req_ids[blockIdx.y] : (int)blockIdx.y;
     const int t = blockIdx.x / nq, h = blockIdx.x % nq;
     const int q0 = q_start[b];
-    if (t >= q_start[b + 1] - q0) return;
+    const int q_len = q_start[b + 1] - q0;
+    pdl_wait();
+    if (t >= q_len) return;
     const size_t row = (size_t)(q0 + t) * nq + h;
     float M = -INFINITY;
     for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_ml[(row * num_splits + s) * 2]);

@@ -53,7 +53,7 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
                                int dim, float eps) {
     __shared__ float red[32];
     pdl_launch_dependents();          // the next kernel may become resident (it waits before it reads or writes)
-    pdl_wait();
+    // the row index and the weights are older than the kernel ahead: fetched before waiting for it
     const int r = blockIdx.x;
     const int row = row_index ? row_index[r] : r;
     const float* xr = x + (size_t)row * dim;
@@ -70,7 +70,13 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
         // a thread's first KEEP pieces stay in registers between the two passes (rows up to 16 * KEEP * NT / 4
         // elements are read from memory once); the loads of a pass are issued together
         constexpr int KEEP = 4;
-        float4 keep[KEEP];
+        float4 keep[KEEP], wk[KEEP];
+#pragma unroll
+        for (int k = 0; k < KEEP; ++k) {
+            const int i = threadIdx.x + k * NT;
+            wk[k] = i < n4 ? w4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        pdl_wait();
 #pragma unroll
         for (int k = 0; k < KEEP; ++k) {
             const int i = threadIdx.x + k * NT;
@@ -91,7 +97,7 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
         for (int k = 0; k < KEEP; ++k) {
             const int i = threadIdx.x + k * NT;
             if (i < n4) {
-                const float4 v = keep[k], g = w4[i];
+                const float4 v = keep[k], g = wk[k];
                 store4<TO>(o + 4 * i, (v.x * rs) * g.x, (v.y * rs) * g.y, (v.z * rs) * g.z, (v.w * rs) * g.w);
             }
         }
@@ -101,6 +107,7 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
         }
         return;
     }
+    pdl_wait();
     for (int i = threadIdx.x; i < dim; i += NT) { const float v = xr[i]; ss = fmaf(v, v, ss); }
     ss = block_sum<NT>(ss, red);
     const float rs = rsqrtf(ss / (float)dim + eps);
@@ -285,7 +292,8 @@ qk_norm_rope_kv_write_d128_kernel(
     const int* __restrict__ block_table, int table_width,
     T* __restrict__ cache, KvLayout L, int layer, int write_cache, int nq, int nkv, int max_pos) {
     pdl_launch_dependents();
-    pdl_wait();
+    // Everything but the projection row is older than the kernel ahead (the step's batch arrays, the block
+    // table, the norm weights, the rotation table): it is fetched first, the wait comes just before the row.
     constexpr int d = 128;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.y;
@@ -294,35 +302,42 @@ qk_norm_rope_kv_write_d128_kernel(
     if (head >= heads) return;
     const bool is_q = head < nq, is_k = !is_q && head < nq + nkv;
     float* src = qkv + (size_t)t * heads * d + (size_t)head * d + lane * 4;
-    const float4 x = *reinterpret_cast<const float4*>(src);
-    if (clear_input) *reinterpret_cast<float4*>(src) = make_float4(0.f, 0.f, 0.f, 0.f);   // this lane alone reads these four
-    if (!is_q && !write_cache) return;
-    const int pos = positions[t];
-    T* dst;
+    const bool wanted = is_q || write_cache;
+    const int pos = wanted ? positions[t] : 0;
+    T* dst = nullptr;
     if (is_q) {
         dst = q_out + (size_t)t * nq * d + (size_t)head * d + lane * 4;
-    } else {
+    } else if (wanted) {
         const int kvh = is_k ? head - nq : head - nq - nkv;
         const int page = block_table[(size_t)tok_req[t] * table_width + pos / L.page_size];
-        if (page < 0) return;
-        dst = cache + (size_t)page * L.page_stride + (size_t)layer * L.layer_stride +
-              (is_k ? 0 : L.kv_stride) + (size_t)kvh * L.head_stride + (size_t)(pos % L.page_size) * d + lane * 4;
+        if (page >= 0)
+            dst = cache + (size_t)page * L.page_stride + (size_t)layer * L.layer_stride +
+                  (is_k ? 0 : L.kv_stride) + (size_t)kvh * L.head_stride + (size_t)(pos % L.page_size) * d + lane * 4;
     }
+    const float* w = is_q ? q_w : (is_k ? k_w : nullptr);
+    float4 wv = make_float4(1.f, 1.f, 1.f, 1.f);
+    if (w) wv = *reinterpret_cast<const float4*>(w + lane * 4);
+    const bool rotate = (is_q || is_k) && table != nullptr && pos >= 0 && pos < max_pos;
+    float4 c01 = make_float4(1.f, 0.f, 1.f, 0.f), c23 = c01;
+    if (rotate) {
+        const float4* cs = reinterpret_cast<const float4*>(table + (size_t)pos * 64 + (lane & 15) * 4);
+        c01 = cs[0]; c23 = cs[1];                               // (cos0, sin0, cos1, sin1), (cos2, sin2, cos3, sin3)
+    }
+    pdl_wait();
+    const float4 x = *reinterpret_cast<const float4*>(src);
+    if (clear_input) *reinterpret_cast<float4*>(src) = make_float4(0.f, 0.f, 0.f, 0.f);   // this lane alone reads these four
+    if (dst == nullptr) return;
     if (!is_q && !is_k) { store4<T>(dst, x.x, x.y, x.z, x.w); return; }
-    const float* w = is_q ? q_w : k_w;
     float n0 = x.x, n1 = x.y, n2 = x.z, n3 = x.w;
     if (w) {
         float ss = fmaf(x.x, x.x, fmaf(x.y, x.y, fmaf(x.z, x.z, x.w * x.w)));
         ss = warp_sum(ss);
         const float rs = rsqrtf(ss / (float)d + eps);
-        const float4 wv = *reinterpret_cast<const float4*>(w + lane * 4);
         n0 = (x.x * rs) * wv.x; n1 = (x.y * rs) * wv.y; n2 = (x.z * rs) * wv.z; n3 = (x.w * rs) * wv.w;
     }
-    if (table != nullptr && pos >= 0 && pos < max_pos) {
+    if (rotate) {
         const float p0 = __shfl_xor_sync(0xffffffffu, n0, 16), p1 = __shfl_xor_sync(0xffffffffu, n1, 16);
         const float p2 = __shfl_xor_sync(0xffffffffu, n2, 16), p3 = __shfl_xor_sync(0xffffffffu, n3, 16);
-        const float4* cs = reinterpret_cast<const float4*>(table + (size_t)pos * 64 + (lane & 15) * 4);
-        const float4 c01 = cs[0], c23 = cs[1];                 // (cos0, sin0, cos1, sin1), (cos2, sin2, cos3, sin3)
         if (lane < 16) {                                        // first half: a cos - b sin, b = partner
             n0 = n0 * c01.x - p0 * c01.y; n1 = n1 * c01.z - p1 * c01.w;
             n2 = n2 * c23.x - p2 * c23.y; n3 = n3 * c23.z - p3 * c23.w;
