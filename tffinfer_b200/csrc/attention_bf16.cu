@@ -321,6 +321,37 @@ attn_fwd_kernel(const AttnParams p) {
 
 // out[row, :] = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s, M = max_s m_s, for the rows
 // (token, head) of the requests the launch covered: grid (nq * max_q_len, requests).
+// the merge of up to MAXS splits of one output row: all statistics, then all partial outputs, are asked for at
+// once (two round trips to memory, not two per split)
+template <int D, int MAXS>
+__device__ __forceinline__ void combine_row(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                            bf16* __restrict__ out, int num_splits, size_t row) {
+    float2 ml[MAXS];
+#pragma unroll
+    for (int s = 0; s < MAXS; ++s)
+        ml[s] = s < num_splits ? *reinterpret_cast<const float2*>(part_ml + (row * num_splits + s) * 2) : make_float2(-INFINITY, 0.f);
+    float M = -INFINITY;
+#pragma unroll
+    for (int s = 0; s < MAXS; ++s) M = fmaxf(M, ml[s].x);
+    const float Ms = M == -INFINITY ? 0.f : M;
+    float f[MAXS], lsum = 0.f;
+#pragma unroll
+    for (int s = 0; s < MAXS; ++s) {
+        f[s] = (s < num_splits && ml[s].y != 0.f) ? exp2f(ml[s].x - Ms) : 0.f;   // an empty split counts for nothing
+        lsum += f[s] * ml[s].y;
+    }
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        float po[MAXS];
+#pragma unroll
+        for (int s = 0; s < MAXS; ++s)                                      // (an empty split's O may be unwritten)
+            po[s] = f[s] != 0.f ? part_o[(row * num_splits + s) * D + c] : 0.f;
+        float acc = 0.f;
+#pragma unroll
+        for (int s = 0; s < MAXS; ++s) acc += f[s] * po[s];
+        out[row * D + c] = __float2bfloat16_rn(acc / lsum);
+    }
+}
+
 template <int D>
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     bf16* __restrict__ out, int num_splits, const int* __restrict__ q_start,
@@ -334,6 +365,9 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
     pdl_wait();
     if (t >= q_len) return;
     const size_t row = (size_t)(q0 + t) * nq + h;
+    if (num_splits <= 4) { combine_row<D, 4>(part_o, part_ml, out, num_splits, row); return; }
+    if (num_splits <= 8) { combine_row<D, 8>(part_o, part_ml, out, num_splits, row); return; }
+    if (num_splits <= 16) { combine_row<D, 16>(part_o, part_ml, out, num_splits, row); return; }
     float M = -INFINITY;
     for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_ml[(row * num_splits + s) * 2]);
     const float Ms = M == -INFINITY ? 0.f : M;
