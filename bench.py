@@ -169,7 +169,7 @@ def decode_run(engine, batch: int, steps: int, warmup: int, seed: int, sampler=N
         engine.abort(i)
     return {"tok_s": batch * steps / (dev_ms / 1e3), "ms_per_step": dev_ms / steps,
             "e2e_tok_s": batch * steps / wall, "launches": launches, "mean_context": (ctx0 + ctx1) / 2,
-            "h2d_bytes": h2d, "d2h_bytes": 4 * batch}
+            "h2d_bytes": h2d, "d2h_bytes": 4 * batch + 4}      # drawn tokens and the kernels' error word
 
 
 def prefill_run(engine, iters: int, warmup: int, seed: int):

@@ -123,6 +123,14 @@ int tff_num_sms() {
     return n;
 }
 
+// Copies the error word into pinned host memory in stream order (no synchronisation): the host looks at it
+// when it reads the results of the same step.
+TFF_API int tff_error_word_to_host_async(int* pinned_dst, cudaStream_t stream) {
+    int* flag = tff_device_error_flag();
+    if (!flag || !pinned_dst) return TFF_ERR_BAD_ARGUMENT;
+    return cudaMemcpyAsync(pinned_dst, flag, sizeof(int), cudaMemcpyDeviceToHost, stream) == cudaSuccess ? TFF_OK : TFF_ERR_LAUNCH;
+}
+
 // Reads (and clears) the error word: non-zero when a bounded wait inside a kernel ran out.
 // Synchronises the device.
 TFF_API int tff_kernel_error() {

@@ -107,10 +107,16 @@ class Engine:
                 i = self._host_flip                    # two pinned buffers in turn: the one of the step
                 self._host_flip ^= 1                   # before may not have been read yet
                 host = self._host_tokens[i]
-                if host is None or host.numel() < toks.numel():
-                    host = torch.empty(max(256, toks.numel()), dtype=torch.int32, pin_memory=True)
+                if host is None or host.numel() < toks.numel() + 1:
+                    host = torch.zeros(max(256, toks.numel() + 1), dtype=torch.int32, pin_memory=True)
                     self._host_tokens[i] = host
                 host[:toks.numel()].copy_(toks, non_blocking=True)
+                # the kernels' error word travels with the tokens (last element of the buffer): a bounded wait
+                # that ran out inside a kernel is reported when this step's tokens are read
+                word = getattr(self.runner.ops, "error_word_async", None)
+                if word is not None:
+                    word(host, host.numel() - 1)
+                    record["error_word"] = True
                 record["host"] = host
                 record["event"] = torch.cuda.Event()
                 record["event"].record()
@@ -133,6 +139,8 @@ class Engine:
         if record["samplers"]:
             if record["event"] is not None:
                 record["event"].synchronize()
+                if record.get("error_word") and int(record["host"][-1]) != 0:
+                    self.runner.ops.check_errors()             # raises
                 host = record["host"][:len(record["samplers"])].tolist()
             else:
                 host = record["tokens"].tolist()

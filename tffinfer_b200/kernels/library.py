@@ -211,6 +211,13 @@ class CudaKernels:
                                                _c_int(drawn.numel()), self._stream()), "gather_tokens")
         self.launches += 1
 
+    def error_word_async(self, pinned: torch.Tensor, index: int) -> None:
+        """Copies the kernels' error word into element ``index`` of a pinned int32 host tensor, in stream
+        order; non-zero there (once the stream has got that far) means check_errors() will raise."""
+        assert pinned.dtype == torch.int32 and pinned.is_pinned() and 0 <= index < pinned.numel()
+        self._check(self.lib.tff_error_word_to_host_async(_vp(pinned.data_ptr() + 4 * index), self._stream()),
+                    "error_word_to_host")
+
     def check_errors(self) -> None:
         """Synchronises and raises if a bounded wait inside a kernel ran out since the last check."""
         v = self.lib.tff_kernel_error()
