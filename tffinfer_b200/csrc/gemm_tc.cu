@@ -37,13 +37,21 @@ using namespace tc5;
 
 template <int BN, bool TMA_OUT, bool SWAP = false> struct TileCfg {
     static constexpr int kStageBytes = BM * BK * 2 + BN * BK * 2;
-    static constexpr int kStages = BN >= 256 ? 4 : BN >= 128 ? 5 : (BN >= 64 ? 8 : (BN >= 32 ? 5 : 4));
-    static constexpr int kCtasPerSm = BN >= 64 ? 1 : (BN >= 32 ? 2 : 3);
+    // Small column tiles stream weights: several CTAs on an SM keep more loads in flight than one CTA with a
+    // deep ring (measured: one CTA of 8 stages reads 4.5 TB/s at 64 tokens, two of 3 stages 4.8).  Stages are
+    // as many as let kCtasPerSm CTAs fit into the SM's 227 KB with their staging (2 x 5 stages of BN = 32
+    // did not: only one CTA was resident and the 296-CTA grid ran as two waves).
+    static constexpr int kStages = BN >= 256 ? 4 : BN >= 128 ? 5 : (BN >= 64 ? 3 : 4);
+    static constexpr int kCtasPerSm = BN >= 128 ? 1 : (BN >= 32 ? 2 : 3);
     static constexpr int kAccCols = BN < 32 ? 32 : BN;              // columns of one accumulator buffer
     static constexpr int kTmemCols = 2 * kAccCols;                  // 64 .. 512, a power of two
     // epilogue staging: 4 warps x (32 rows x 128 B); two buffers a warp in the normal orientation, one when swapped
     static constexpr int kStagingBytes = TMA_OUT ? (SWAP ? 4 * 4096 : 4 * 2 * 4096) : 0;
     static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    // an SM has 228 KB of shared memory, of which each resident CTA reserves 1 KB; checked for the
+    // configurations that the decode steps launch (swapped; through TMA from BN = 32 on)
+    static_assert(!SWAP || TMA_OUT != (BN >= 32) || kCtasPerSm * (kSmemBytes + 1024) <= 228 * 1024,
+                  "the CTAs meant to share an SM do not fit");
 };
 
 // out element (m, n): normal -> lane operand row = m, column operand row = n; swapped -> the reverse.
