@@ -440,6 +440,57 @@ def test_attention_finds_one_far_key_among_hundreds(ops):
             assert torch.allclose(out[0, h * d:(h + 1) * d].float().cpu(), want, atol=2e-2, rtol=2e-2)
 
 
+def _dense_attention_on_gpu(q, cache, table, layer, page, first_pos, nq, nkv, d):
+    """softmax(q k^T / sqrt(d)) v over keys 0..position, in float32 on the GPU, for one request whose
+    rows sit at positions first_pos, first_pos + 1, ... (plain formulas; blocks of rows bound the memory)."""
+    n = q.shape[0]
+    total = first_pos + n
+    pages = torch.tensor(table[:-(-total // page)], device=DEV)
+    kv = cache[pages, layer].float()                               # [blocks, 2, nkv, page, d]
+    k = kv[:, 0].permute(1, 0, 2, 3).reshape(nkv, -1, d)[:, :total]
+    v = kv[:, 1].permute(1, 0, 2, 3).reshape(nkv, -1, d)[:, :total]
+    qh = q.float().view(n, nq, d)
+    out = torch.empty(n, nq, d, device=DEV)
+    G = nq // nkv
+    keys = torch.arange(total, device=DEV)
+    for r0 in range(0, n, 256):
+        rows = slice(r0, min(n, r0 + 256))
+        pos = first_pos + torch.arange(rows.start, rows.stop, device=DEV)
+        for h in range(nq):
+            s = (qh[rows, h] @ k[h // G].t()) / math.sqrt(d)
+            s = s.masked_fill(keys[None, :] > pos[:, None], float("-inf"))
+            out[rows, h] = torch.softmax(s, dim=-1) @ v[h // G]
+    return out.view(n, nq * d)
+
+
+@pytest.mark.parametrize("new,old,splits", [(2085, 18000, None), (1, 33000, None), (1, 33000, 16), (9, 20000, 4)])
+def test_attention_at_long_context(ops, new, old, splits):
+    """Tens of thousands of keys behind the new tokens (a portion of a long prompt; a decoded token),
+    with two keys made to stand out, one at the far end and one in the middle: offsets into the cache
+    and the block table, the number of key blocks and the split of the key range at sizes that the
+    other tests do not reach."""
+    nq, nkv, d, page = 8, 2, 128, 16
+    dt = torch.bfloat16
+    entries, tables, cache, qkv = _paged_case(nq, nkv, d, page, [new], [old], 0, dt, seed=120, layers=2)
+    cache = cache.to(DEV)
+    q = qkv[:, :nq * d].contiguous().view(-1, nq, d)
+    q[:, :, 9] = 6.0                                               # score 6 * 24 / sqrt(128) = 12.7 against N(0, 1)
+    for pos, boost in ((11, 24.0), (old // 2 + 3, 24.5)):
+        cache[tables[0][pos // page], 1, 0, :, pos % page, 9] = boost
+    q = q.view(-1, nq * d).to(DEV)
+    bg = build_step_batch(entries, [old], [0], [tables], DEV)
+    out = torch.full((new, nq * d), float("nan"), dtype=dt, device=DEV)
+    if splits is None:
+        ops.attention(q, bg, bg.block_tables[0], cache, 1, page, out, nq, nkv, d, 1 / math.sqrt(d), 0)
+    else:
+        ops.attention_bf16(q, bg, bg.block_tables[0], cache, 1, page, out, nq, nkv, d, 1 / math.sqrt(d), 0,
+                           num_splits=splits)
+    ops.check_errors()
+    want = _dense_attention_on_gpu(q, cache, tables[0], 1, page, old, nq, nkv, d)
+    assert torch.isfinite(out).all()
+    assert rel_err(out, want) < 1e-2
+
+
 def test_window_edge_is_exact(ops):
     """With window w the key at p-w+1 counts and the key at p-w does not."""
     nq, nkv, d, page, w = 2, 1, 32, 8, 9
