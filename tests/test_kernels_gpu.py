@@ -304,6 +304,8 @@ FLASH_CASES = [
     (8, 2, 128, 16, [40, 1], [100, 150], 48, 1),               # sliding window, rows mode
     (8, 2, 128, 16, [1, 1], [100, 30], 48, 2),                 # sliding window, decode
     (4, 4, 128, 16, [130], [1], 0, 2),                         # rows mode with split keys
+    (32, 8, 128, 16, [1] * 6, [3000, 10, 200, 50, 7, 129], 0, None),      # unequal contexts: the split follows sum / longest
+    (32, 8, 128, 16, [70, 1, 1, 1], [40, 2500, 9, 300], 0, None),         # the same beside a portion (two launches)
 ]
 
 

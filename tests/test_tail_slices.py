@@ -26,3 +26,19 @@ def test_slices_shorten_the_last_wave_and_never_lengthen_it():
     assert CudaKernels.tail_slices(256, 64, 148) == 4
     # few K blocks bound the number of slices
     assert CudaKernels.tail_slices(20, 2, 148) in (0, 2)
+
+
+def test_key_split_follows_the_effective_number_of_requests():
+    """sum / longest of the contexts decides the split of the key range, rounded to powers of two
+    (the classes that decode graphs are captured for)."""
+    from tffinfer_b200.engine.batch import effective_requests
+    from tffinfer_b200.kernels.library import CudaKernels
+    assert effective_requests([2048] * 8) == 8.0
+    assert effective_requests([]) == 1.0
+    assert abs(effective_requests([4000, 10, 10, 10]) - 1.0075) < 1e-9
+    splits = lambda n: CudaKernels.attention_splits(CudaKernels, n, 1, 32, 8)
+    assert [splits(n) for n in (1, 2, 4, 8, 16, 32, 64)] == [16, 16, 9, 4, 2, 1, 1]
+    # 26 requests, one of them long: as few as 4 equal ones would be cut, not as 32
+    assert splits(effective_requests([4000] + [500] * 25)) == splits(4.2) == 4
+    # many tokens a request (portions): never cut
+    assert CudaKernels.attention_splits(CudaKernels, 1, 64, 32, 8) == 1

@@ -82,6 +82,11 @@ class StepBatch:
     h_q_lens: Optional[np.ndarray] = None
     h_pos_start: Optional[np.ndarray] = None
     h_sorted_q_lens: Optional[np.ndarray] = None     # q_lens in the order of req_order
+    h_sorted_kv_lens: Optional[np.ndarray] = None    # kv_len in the order of req_order (real requests only count)
+    # How many requests of the longest context the decoded tokens of this step weigh (see effective_requests),
+    # rounded up to a power of two.  Set by the runner for steps replayed as CUDA graphs, whose launch
+    # geometry is fixed when they are captured; None lets the kernel library work it out per launch.
+    key_split_class: Optional[int] = None
     all_decode: bool = False      # every request brings exactly one token
     real_requests: int = 0        # requests that are not padding
     real_logit_rows: int = 0
@@ -171,9 +176,21 @@ def pack_step(entries: Sequence[StepEntry], starts: Sequence[int], slots: Sequen
             if n:
                 bt[i, :n] = t
     info = dict(max_q_len=int(q_lens.max()), max_kv_len=int(kv_len.max()), q_lens=q_lens, pos_start=pos_start,
-                sorted_q_lens=q_lens[req_order], has_token_src=has_src,
+                sorted_q_lens=q_lens[req_order], sorted_kv_lens=np.where(req_order < nreal, kv_len[req_order], 0),
+                has_token_src=has_src,
                 all_decode=bool((q_lens == 1).all()), real_requests=nreal, real_logit_rows=real_rows)
     return out, layout, info
+
+
+def effective_requests(kv_lens) -> float:
+    """sum(context) / max(context): how many requests of the longest context read as many keys as these
+    do.  A step's decoded tokens are one (request, key/value head) work item each unless the key range is
+    shared out; the longest context sets how long the longest item runs, the sum how long all of them
+    take together, so this ratio, not the number of requests, says how many shares the key range needs."""
+    kv = np.asarray(kv_lens, dtype=np.float64)
+    if kv.size == 0 or kv.max() <= 0:
+        return 1.0
+    return float(kv.sum() / kv.max())
 
 
 def batch_from_device(dev: torch.Tensor, layout: BatchLayout, info) -> StepBatch:
@@ -184,7 +201,7 @@ def batch_from_device(dev: torch.Tensor, layout: BatchLayout, info) -> StepBatch
         token_ids=v[0], positions=v[1], tok_req=v[2], q_start=v[3], pos_start=v[4], kv_len=v[5],
         slots=v[6], logit_rows=v[7], req_order=v[8], tok_src=v[9] if info["has_token_src"] else None, block_tables=bts,
         h_q_lens=info["q_lens"], h_pos_start=info["pos_start"], h_sorted_q_lens=info["sorted_q_lens"],
-        all_decode=info["all_decode"],
+        h_sorted_kv_lens=info["sorted_kv_lens"], all_decode=info["all_decode"],
         real_requests=info["real_requests"], real_logit_rows=info["real_logit_rows"])
 
 

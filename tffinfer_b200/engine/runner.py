@@ -20,7 +20,8 @@ from ..config import EngineConfig, read_config_json
 from ..parts import Model, CacheBinding, KVNeed, StateNeed
 from ..registry import get_architecture
 from ..weights import load_model_weights
-from .batch import StepEntry, StepBatch, build_step_batch, pack_step, batch_from_device, BatchLayout
+from .batch import (StepEntry, StepBatch, build_step_batch, pack_step, batch_from_device, BatchLayout,
+                    effective_requests)
 
 _TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 _STATE_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": torch.int32}
@@ -124,8 +125,13 @@ class ModelRunner:
             n_pages = []
         # one page and one state slot more than the pools hand out: padding rows of a
         # fixed-size batch write there and nobody reads them
+        # [pages, layers, 2, kv heads, page, head] as the parts and kernels index it, stored with the layers
+        # outermost: the pages that one layer's attention reads then lie within that layer's share of the
+        # pool (with the pages outermost they were 64 KB out of every layers x 64 KB, each in another 2 MB
+        # page of the address space, and the attention of a 40-layer model read a quarter slower for it)
         self.kv_caches = [
-            torch.zeros((n + 1, g.num_layers, 2, g.num_kv_heads, ps, g.head_dim), dtype=self.act_dtype, device=self.device)
+            torch.zeros((g.num_layers, n + 1, 2, g.num_kv_heads, ps, g.head_dim), dtype=self.act_dtype,
+                        device=self.device).permute(1, 0, 2, 3, 4, 5)
             for n, g in zip(n_pages, groups)]
         self.dummy_pages = list(n_pages)
         self.dummy_slot = self.ecfg.max_live_requests
@@ -215,7 +221,9 @@ class ModelRunner:
 
     def _make_static_batch(self, entries, starts, slots, tables) -> StepBatch:
         """Decode-only steps use device arrays of fixed address and size, one set per
-        batch-size bucket, so that the step can be replayed as a CUDA graph."""
+        batch-size bucket, so that the step can be replayed as a CUDA graph.  A graph fixes the
+        geometry of its launches, and how the attention shares out the key range depends on how
+        unequal the contexts are: a bucket has one graph per class of that (batch.key_split_class)."""
         bucket = next(b for b in self.graph_buckets if b >= len(entries))
         st = self._graphs.get(bucket)
         if st is None:
@@ -223,7 +231,7 @@ class ModelRunner:
             st = {"layout": layout,
                   "host": torch.empty(layout.total, dtype=torch.int32, pin_memory=True),
                   "dev": torch.empty(layout.total, dtype=torch.int32, device=self.device),
-                  "graph": None, "logits": None}
+                  "graphs": {}}
             self._graphs[bucket] = st
         if st.get("copied") is not None:
             st["copied"].synchronize()              # the last copy out of the staging buffer has finished
@@ -237,11 +245,16 @@ class ModelRunner:
         self.last_h2d_bytes = layout.total * 4
         batch = batch_from_device(st["dev"], layout, info)
         batch.graph_bucket = bucket
+        eff, cls = effective_requests(batch.h_sorted_kv_lens), 1
+        while cls < eff:
+            cls *= 2
+        batch.key_split_class = min(cls, bucket)
         return batch
 
     def _run_graph(self, batch: StepBatch) -> torch.Tensor:
-        st = self._graphs[batch.graph_bucket]
-        if st["graph"] is None:
+        graphs = self._graphs[batch.graph_bucket]["graphs"]
+        st = graphs.get(batch.key_split_class)
+        if st is None:
             self._forward(batch)                    # warm-up outside the capture (same writes, same values)
             torch.cuda.current_stream().synchronize()
             g = torch.cuda.CUDAGraph()
@@ -249,9 +262,9 @@ class ModelRunner:
                 self._graph_pool = torch.cuda.graph_pool_handle()
             launches = getattr(self.ops, "launches", 0)
             with torch.cuda.graph(g, pool=self._graph_pool):
-                st["logits"] = self._forward(batch)
-            st["graph"] = g
-            st["launches"] = getattr(self.ops, "launches", 0) - launches
+                logits = self._forward(batch)
+            st = {"graph": g, "logits": logits, "launches": getattr(self.ops, "launches", 0) - launches}
+            graphs[batch.key_split_class] = st
         st["graph"].replay()
         if hasattr(self.ops, "launches"):
             self.ops.launches += st["launches"]

@@ -84,6 +84,31 @@ class CudaKernels:
             if t is not None and not t.is_contiguous():
                 raise KernelError("kernels take contiguous tensors")
 
+    @staticmethod
+    def _cache_args(kv_cache, kv_layer: int):
+        """(pointer, pages, layers, layer) of a paged cache [pages, layers, 2, kv heads, page, head] as the
+        launchers take them.  The tensor is either contiguous as it reads (pages outermost), or that shape
+        as a view of storage with the layers outermost, each layer's pages then lying together (what the
+        engine allocates: a layer's attention reads addresses within one layer's share of the pool and not
+        64 KB out of every ``layers`` x 64 KB).  For the second the launcher is given the layer's own
+        [pages, 1, ...] block."""
+        if kv_cache is None:
+            return _vp(0), 0, 1, kv_layer
+        if not kv_cache.is_cuda:
+            raise KernelError("a tensor given to a CUDA kernel is not on a CUDA device")
+        if kv_cache.is_contiguous():
+            return _vp(kv_cache.data_ptr()), kv_cache.shape[0], kv_cache.shape[1], kv_layer
+        st, block = kv_cache.stride(), 1
+        for i in range(kv_cache.dim() - 1, 1, -1):             # the [2, kv heads, page, head] block of a page is dense
+            if st[i] != block:
+                break
+            block *= kv_cache.shape[i]
+        else:
+            if st[0] == block and st[1] == block * kv_cache.shape[0]:
+                return (_vp(kv_cache.data_ptr() + kv_layer * st[1] * kv_cache.element_size()),
+                        kv_cache.shape[0], 1, 0)
+        raise KernelError("the cache is neither contiguous nor a view of layer-major storage")
+
     # -------------------------------------------------------------- kernels
     def embed(self, token_ids, table, out) -> None:
         self._need_cuda(token_ids, table, out)
@@ -292,14 +317,14 @@ class CudaKernels:
                               kv_layer, page_size, nq, nkv, d, write_cache) -> None:
         """qkv [T, (nq+2nkv)*d] float32 or activation type -> q_out [T, nq*d] (normed, rotated) and the
         token's K/V page slots."""
-        self._need_cuda(qkv, q_out, q_w, k_w, table, block_table, kv_cache)
+        self._need_cuda(qkv, q_out, q_w, k_w, table, block_table)
+        c_ptr, _, c_layers, c_layer = self._cache_args(kv_cache, kv_layer)
         T = qkv.shape[0]
         assert qkv.shape[1] == (nq + 2 * nkv) * d and tuple(q_out.shape) == (T, nq * d)
         assert qkv.dtype in (torch.float32, q_out.dtype)
         if write_cache:
             assert kv_cache is not None and kv_cache.dtype == q_out.dtype, "cache dtype must match activations"
             assert tuple(kv_cache.shape[2:]) == (2, nkv, page_size, d)
-        layers = kv_cache.shape[1] if kv_cache is not None else 1
         clear = 1 if qkv.data_ptr() in self._acc_zero else 0
         self._check(self.lib.tff_qk_norm_rope_kv_write(
             _ptr(qkv), _c_int(1 if qkv.dtype == torch.float32 else 0), _c_int(clear), _ptr(q_out), _c_int(_dt(q_out)),
@@ -307,7 +332,7 @@ class CudaKernels:
             _ptr(table), _c_int(rot_dim), _c_int(table.shape[0] if table is not None else 0),
             _ptr(batch.positions), _ptr(batch.tok_req), _ptr(block_table),
             _c_int(block_table.shape[1] if block_table is not None else 0),
-            _ptr(kv_cache), _c_int(layers), _c_int(kv_layer), _c_int(page_size), _c_int(1 if write_cache else 0),
+            c_ptr, _c_int(c_layers), _c_int(c_layer), _c_int(page_size), _c_int(1 if write_cache else 0),
             _c_int(T), _c_int(nq), _c_int(nkv), _c_int(d), self._stream()), "qk_norm_rope_kv_write")
         if clear:
             self._acc_zero[qkv.data_ptr()] = True
@@ -325,31 +350,32 @@ class CudaKernels:
                  and w_qkv.dtype == torch.bfloat16 and q_out.dtype == torch.bfloat16 and K % 8 == 0
                  and (table is None or rot_dim == d) and (kv_cache is None or kv_cache.dtype == torch.bfloat16)
                  and (not write_cache or kv_cache is not None)
-                 and all(t is None or t.data_ptr() % 16 == 0 for t in (h, w_qkv, q_out, q_w, k_w, table, kv_cache)))
+                 and all(t is None or t.data_ptr() % 16 == 0 for t in (h, w_qkv, q_out, q_w, k_w, table, kv_cache))
+                 and (kv_cache is None or kv_cache.stride(0) % 8 == 0 and kv_cache.stride(1) % 8 == 0))
         if not fused:
             qkv = self.projection_buffer(T, (nq + 2 * nkv) * d, h.device, h.dtype)
             self.gemm(h, w_qkv, qkv)
             self.qk_norm_rope_kv_write(qkv, q_out, q_w, k_w, eps, table, rot_dim, batch, block_table, kv_cache,
                                        kv_layer, page_size, nq, nkv, d, write_cache)
             return
-        self._need_cuda(h, w_qkv, q_out, q_w, k_w, table, block_table, kv_cache)
+        self._need_cuda(h, w_qkv, q_out, q_w, k_w, table, block_table)
+        c_ptr, _, c_layers, c_layer = self._cache_args(kv_cache, kv_layer)
         assert tuple(w_qkv.shape) == ((nq + 2 * nkv) * d, K) and tuple(q_out.shape) == (T, nq * d)
         if write_cache:
             assert tuple(kv_cache.shape[2:]) == (2, nkv, page_size, d)
-        layers = kv_cache.shape[1] if kv_cache is not None else 1
         self._check(self.lib.tff_gemm_tc_qkv_rope(
             _ptr(h), _ptr(w_qkv), _c_int(T), _c_int(K), _ptr(q_out), _ptr(q_w), _ptr(k_w), _c_float(eps),
             _ptr(table), _c_int(table.shape[0] if table is not None else 0),
             _ptr(batch.positions), _ptr(batch.tok_req), _ptr(block_table),
             _c_int(block_table.shape[1] if block_table is not None else 0),
-            _ptr(kv_cache), _c_int(layers), _c_int(kv_layer), _c_int(page_size), _c_int(1 if write_cache else 0),
+            c_ptr, _c_int(c_layers), _c_int(c_layer), _c_int(page_size), _c_int(1 if write_cache else 0),
             _c_int(nq), _c_int(nkv), self._stream()), "gemm_tc_qkv_rope")
         self.launches += 1
 
     def attention(self, q, batch, block_table, kv_cache, kv_layer, page_size, out,
                   nq, nkv, d, scale, window) -> None:
         """q [T, nq*d] (normed, rotated) against the paged cache -> out [T, nq*d]."""
-        self._need_cuda(q, block_table, kv_cache, out)
+        self._need_cuda(q, block_table, out)
         T = q.shape[0]
         assert kv_cache.dtype == q.dtype == out.dtype
         assert tuple(q.shape) == (T, nq * d) and tuple(out.shape) == (T, nq * d)
@@ -364,15 +390,28 @@ class CudaKernels:
         else:
             self.attention_generic(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, scale, window)
 
-    def attention_splits(self, num_requests: int, max_q_len: int, nq: int, nkv: int) -> int:
-        """Shares of the key range per tile.  A function of the batch's size class only (never
-        of the context), so that a replayed CUDA graph and an eager step cut alike."""
+    def attention_splits(self, num_requests: float, max_q_len: int, nq: int, nkv: int) -> int:
+        """Shares of the key range per tile, for ``num_requests`` requests of one context length (for
+        unequal contexts: sum / longest, engine.batch.effective_requests).  The count is rounded up to a
+        power of two, so that a step replayed as a CUDA graph, captured for such a class, and an eager
+        step cut alike."""
         if max_q_len * (nq // nkv) > 16:
             return 1                                   # portions: enough tiles already
         b = 1
         while b < num_requests:
             b *= 2
         return max(1, min(16, 2 * self.NUM_SMS // (b * nkv)))     # one wave of two CTAs per SM
+
+    def _decode_splits(self, batch, first: int, count: int, max_q_len: int, nq: int, nkv: int) -> int:
+        """The key split for requests [first, first + count) in the order of ``batch.req_order``."""
+        if batch.key_split_class is not None:
+            eff = batch.key_split_class
+        elif batch.h_sorted_kv_lens is not None:
+            from ..engine.batch import effective_requests
+            eff = effective_requests(batch.h_sorted_kv_lens[first:first + count])
+        else:
+            eff = count
+        return self.attention_splits(eff, max_q_len, nq, nkv)
 
     def attention_bf16(self, q, batch, block_table, kv_cache, kv_layer, page_size, out,
                        nq, nkv, d, scale, window, num_splits=None) -> None:
@@ -385,24 +424,28 @@ class CudaKernels:
         n_short = int(np.searchsorted(sq, 16 // G, side="right")) if (sq is not None and num_splits is None) else 0
         if 0 < n_short < B and batch.req_order is not None:
             self._attention_bf16_launch(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, scale,
-                                        window, None, batch.req_order[:n_short], n_short, int(sq[n_short - 1]))
+                                        window, self._decode_splits(batch, 0, n_short, int(sq[n_short - 1]), nq, nkv),
+                                        batch.req_order[:n_short], n_short, int(sq[n_short - 1]))
             self._attention_bf16_launch(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, scale,
-                                        window, None, batch.req_order[n_short:], B - n_short, int(sq[-1]))
+                                        window, 1, batch.req_order[n_short:], B - n_short, int(sq[-1]))
         else:
+            if num_splits is None:
+                num_splits = self._decode_splits(batch, 0, B, batch.max_q_len, nq, nkv)
             self._attention_bf16_launch(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, scale,
                                         window, num_splits, None, B, batch.max_q_len)
 
     def _attention_bf16_launch(self, q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, scale,
                                window, num_splits, req_ids, num_requests, max_q_len) -> None:
         T = q.shape[0]
-        splits = num_splits if num_splits is not None else self.attention_splits(num_requests, max_q_len, nq, nkv)
+        splits = num_splits
+        c_ptr, c_pages, c_layers, c_layer = self._cache_args(kv_cache, kv_layer)
         ws = None
         if splits > 1:
             ws = torch.empty(T * nq * splits * (d + 2), dtype=torch.float32, device=q.device)
         self._check(self.lib.tff_attention_bf16_paged(
             _ptr(q), _ptr(batch.q_start), _ptr(batch.pos_start), _ptr(req_ids), _ptr(block_table),
             _c_int(block_table.shape[1]),
-            _ptr(kv_cache), ctypes.c_longlong(kv_cache.shape[0]), _c_int(kv_cache.shape[1]), _c_int(kv_layer),
+            c_ptr, ctypes.c_longlong(c_pages), _c_int(c_layers), _c_int(c_layer),
             _c_int(page_size),
             _ptr(out), _ptr(ws), _c_int(T), _c_int(num_requests), _c_int(max_q_len), _c_int(splits),
             _c_int(nq), _c_int(nkv), _c_int(d), _c_float(scale), _c_int(window), self._stream()), "attention_bf16")
@@ -411,10 +454,11 @@ class CudaKernels:
     def attention_generic(self, q, batch, block_table, kv_cache, kv_layer, page_size, out,
                           nq, nkv, d, scale, window) -> None:
         T = q.shape[0]
+        c_ptr, _, c_layers, c_layer = self._cache_args(kv_cache, kv_layer)
         self._check(self.lib.tff_attention_generic(
             _ptr(q), _c_int(_dt(q)), _c_int(q.shape[1]),
             _ptr(batch.positions), _ptr(batch.tok_req), _ptr(block_table), _c_int(block_table.shape[1]),
-            _ptr(kv_cache), _c_int(kv_cache.shape[1]), _c_int(kv_layer), _c_int(page_size),
+            c_ptr, _c_int(c_layers), _c_int(c_layer), _c_int(page_size),
             _ptr(out), _c_int(T), _c_int(nq), _c_int(nkv), _c_int(d), _c_float(scale), _c_int(window),
             self._stream()), "attention_generic")
         self.launches += 1
