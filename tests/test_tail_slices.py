@@ -37,8 +37,9 @@ def test_key_split_follows_the_effective_number_of_requests():
     assert effective_requests([]) == 1.0
     assert abs(effective_requests([4000, 10, 10, 10]) - 1.0075) < 1e-9
     splits = lambda n: CudaKernels.attention_splits(CudaKernels, n, 1, 32, 8)
-    assert [splits(n) for n in (1, 2, 4, 8, 16, 32, 64)] == [16, 16, 9, 4, 2, 1, 1]
-    # 26 requests, one of them long: as few as 4 equal ones would be cut, not as 32
-    assert splits(effective_requests([4000] + [500] * 25)) == splits(4.2) == 4
+    assert [splits(n) for n in (1, 2, 4, 8, 16, 24, 32, 64)] == [16, 16, 9, 4, 2, 1, 1, 1]
+    # 26 requests, one of them long: cut as 4 equal ones would be, not as 32
+    assert splits(effective_requests([4000] + [500] * 25)) == splits(4.2) == splits(4) == 9
+    assert splits(20) == splits(16) and splits(23) == splits(32)
     # many tokens a request (portions): never cut
     assert CudaKernels.attention_splits(CudaKernels, 1, 64, 32, 8) == 1

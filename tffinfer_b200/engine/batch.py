@@ -75,7 +75,7 @@ class StepBatch:
     kv_len: torch.Tensor          # int32 [B]   tokens of each request in the cache after this step
     slots: torch.Tensor           # int32 [B]   state slot of each request
     logit_rows: torch.Tensor      # int32 [R]   flat rows whose logits are wanted
-    req_order: Optional[torch.Tensor] = None   # int32 [B] request rows ordered by their number of new tokens
+    req_order: Optional[torch.Tensor] = None   # int32 [B] request rows by number of new tokens, then longest context first
     tok_src: Optional[torch.Tensor] = None     # int32 [T] rows of the previous step's drawn tokens (-1: none), or None
     block_tables: List[torch.Tensor] = field(default_factory=list)   # per group int32 [B, width]
     # host copies, for launch decisions
@@ -152,7 +152,9 @@ def pack_step(entries: Sequence[StepEntry], starts: Sequence[int], slots: Sequen
     slot_arr[:nreal] = np.asarray(slots, dtype=np.int32)
     # requests ordered by the number of tokens they bring (shortest first): kernels that treat
     # single decoded tokens and long portions differently take a prefix or a suffix of this order
-    req_order = np.argsort(q_lens, kind="stable").astype(np.int32)
+    # by the number of new tokens, and among equals the longest context first: the attention launches take
+    # their requests in this order, and work items that start first should be the long ones
+    req_order = np.lexsort((-kv_len, q_lens)).astype(np.int32)
     tok_src = np.full(T, -1, dtype=np.int32)
     has_src = False
     for i, e in enumerate(entries):

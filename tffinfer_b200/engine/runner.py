@@ -246,9 +246,9 @@ class ModelRunner:
         batch = batch_from_device(st["dev"], layout, info)
         batch.graph_bucket = bucket
         eff, cls = effective_requests(batch.h_sorted_kv_lens), 1
-        while cls < eff:
+        while cls * 1.4142 < eff:                   # to the nearest power of two, as the kernel library rounds
             cls *= 2
-        batch.key_split_class = min(cls, bucket)
+        batch.key_split_class = cls
         return batch
 
     def _run_graph(self, batch: StepBatch) -> torch.Tensor:

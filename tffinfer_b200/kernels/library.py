@@ -392,13 +392,13 @@ class CudaKernels:
 
     def attention_splits(self, num_requests: float, max_q_len: int, nq: int, nkv: int) -> int:
         """Shares of the key range per tile, for ``num_requests`` requests of one context length (for
-        unequal contexts: sum / longest, engine.batch.effective_requests).  The count is rounded up to a
+        unequal contexts: sum / longest, engine.batch.effective_requests).  The count is rounded to a
         power of two, so that a step replayed as a CUDA graph, captured for such a class, and an eager
         step cut alike."""
         if max_q_len * (nq // nkv) > 16:
             return 1                                   # portions: enough tiles already
         b = 1
-        while b < num_requests:
+        while b * 1.4142 < num_requests:               # to the nearest power of two
             b *= 2
         return max(1, min(16, 2 * self.NUM_SMS // (b * nkv)))     # one wave of two CTAs per SM
 
@@ -431,8 +431,10 @@ class CudaKernels:
         else:
             if num_splits is None:
                 num_splits = self._decode_splits(batch, 0, B, batch.max_q_len, nq, nkv)
+            # decoded tokens only: longest contexts first (the order the batch was packed with)
+            order = batch.req_order if n_short == B else None
             self._attention_bf16_launch(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, scale,
-                                        window, num_splits, None, B, batch.max_q_len)
+                                        window, num_splits, order, B, batch.max_q_len)
 
     def _attention_bf16_launch(self, q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, scale,
                                window, num_splits, req_ids, num_requests, max_q_len) -> None:
