@@ -402,6 +402,13 @@ class CudaKernels:
             b *= 2
         return max(1, min(16, 2 * self.NUM_SMS // (b * nkv)))     # one wave of two CTAs per SM
 
+    def _side_stream(self, device):
+        """The second stream (and the two events to fork to it and join from it), made at first use."""
+        if getattr(self, "_side", None) is None:
+            self._side = torch.cuda.Stream(device=device)
+            self._fork, self._join = torch.cuda.Event(), torch.cuda.Event()
+        return self._side
+
     def _decode_splits(self, batch, first: int, count: int, max_q_len: int, nq: int, nkv: int) -> int:
         """The key split for requests [first, first + count) in the order of ``batch.req_order``."""
         if batch.key_split_class is not None:
@@ -423,11 +430,29 @@ class CudaKernels:
         B = batch.num_requests
         n_short = int(np.searchsorted(sq, 16 // G, side="right")) if (sq is not None and num_splits is None) else 0
         if 0 < n_short < B and batch.req_order is not None:
-            self._attention_bf16_launch(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, scale,
-                                        window, self._decode_splits(batch, 0, n_short, int(sq[n_short - 1]), nq, nkv),
-                                        batch.req_order[:n_short], n_short, int(sq[n_short - 1]))
+            # The two launches write different rows of ``out`` and read what the kernels before them wrote:
+            # they run side by side, the decoded tokens' on a second stream.  The portions' kernel is
+            # launched first; it seldom fills the SMs (a 512-token portion is 80 to 160 CTAs of one an SM),
+            # and the other one, bound by memory, runs on what is left.
+            main = torch.cuda.current_stream()
+            side = None if torch.cuda.is_current_stream_capturing() else self._side_stream(q.device)
+            if side is not None:
+                self._fork.record(main)
             self._attention_bf16_launch(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, scale,
                                         window, 1, batch.req_order[n_short:], B - n_short, int(sq[-1]))
+            splits = self._decode_splits(batch, 0, n_short, int(sq[n_short - 1]), nq, nkv)
+            if side is None:
+                self._attention_bf16_launch(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d,
+                                            scale, window, splits, batch.req_order[:n_short], n_short,
+                                            int(sq[n_short - 1]))
+            else:
+                side.wait_event(self._fork)
+                with torch.cuda.stream(side):
+                    self._attention_bf16_launch(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv,
+                                                d, scale, window, splits, batch.req_order[:n_short], n_short,
+                                                int(sq[n_short - 1]))
+                    self._join.record(side)
+                main.wait_event(self._join)
         else:
             if num_splits is None:
                 num_splits = self._decode_splits(batch, 0, B, batch.max_q_len, nq, nkv)
