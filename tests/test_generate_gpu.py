@@ -62,6 +62,32 @@ def test_greedy_bfloat16_follows_plain_and_graphs_change_nothing(tmp_path, name)
         assert _follows_plain(pm, p, g, 3e-2)
 
 
+def test_decode_graphs_with_unequal_contexts(tmp_path):
+    """Heads of 64 in bfloat16 (the split-key decode attention) with contexts from 5 to 610 tokens in one
+    batch: decode-only steps are replayed as graphs captured per class of sum / longest context, requests
+    finish at different times, and every token still follows the plain implementation."""
+    d = make_model_dir(tmp_path, "D")
+    pm = PlainModel(d)
+    cfg = tiny_config("D")
+    rng = random.Random(16)
+    lens = (600, 37, 580, 5, 610, 90)
+    prompts = [[rng.randrange(cfg.vocab_size) for _ in range(n)] for n in lens]
+    news = [6, 14, 9, 14, 4, 12]
+    for graphs in (True, False):
+        eng = _engine(d, "D", "bfloat16", use_cuda_graphs=graphs, max_tokens_per_step=256, max_cache_tokens=4096,
+                      max_live_requests=6)
+        ids = [eng.add_request(p, SamplingParams(max_new_tokens=n)) for p, n in zip(prompts, news)]
+        while eng.has_unfinished():
+            eng.step()
+        eng.runner.ops.check_errors()
+        for i, p, n in zip(ids, prompts, news):
+            g = eng.requests[i].generated
+            assert len(g) == n and _follows_plain(pm, p, g, 3e-2)
+        if graphs:
+            classes = {(b, c) for b, st in eng.runner._graphs.items() for c in st["graphs"]}
+            assert len({c for _, c in classes}) >= 2, classes      # more than one class was captured and replayed
+
+
 def test_temperature_sampling_float32_equals_plain_whatever_the_batching(tmp_path):
     d = make_model_dir(tmp_path, "B")
     pm = PlainModel(d)
