@@ -1,4 +1,5 @@
-"""How the tensor-core product cuts the tiles of a last, partial wave (host-side decision)."""
+"""Launch decisions taken on the host: how the tensor-core product cuts the tiles of a last, partial wave,
+and how the decode attention shares out the key range."""
 from tffinfer_b200.kernels.library import CudaKernels
 
 
