@@ -32,8 +32,7 @@ def test_slices_shorten_the_last_wave_and_never_lengthen_it():
 def test_key_split_follows_the_effective_number_of_requests():
     """sum / longest of the contexts decides the split of the key range, rounded to powers of two
     (the classes that decode graphs are captured for)."""
-    from tffinfer_b200.engine.batch import effective_requests
-    from tffinfer_b200.kernels.library import CudaKernels
+    from tffinfer_b200.kernels.library import CudaKernels, effective_requests
     assert effective_requests([2048] * 8) == 8.0
     assert effective_requests([]) == 1.0
     assert abs(effective_requests([4000, 10, 10, 10]) - 1.0075) < 1e-9
@@ -42,5 +41,6 @@ def test_key_split_follows_the_effective_number_of_requests():
     # 26 requests, one of them long: cut as 4 equal ones would be, not as 32
     assert splits(effective_requests([4000] + [500] * 25)) == splits(4.2) == splits(4) == 9
     assert splits(20) == splits(16) and splits(23) == splits(32)
+    assert CudaKernels.key_split_class([600, 37, 580, 5, 610, 90]) == 4 and CudaKernels.key_split_class([9] * 24) == 32
     # many tokens a request (portions): never cut
     assert CudaKernels.attention_splits(CudaKernels, 1, 64, 32, 8) == 1

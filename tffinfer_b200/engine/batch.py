@@ -83,8 +83,8 @@ class StepBatch:
     h_pos_start: Optional[np.ndarray] = None
     h_sorted_q_lens: Optional[np.ndarray] = None     # q_lens in the order of req_order
     h_sorted_kv_lens: Optional[np.ndarray] = None    # kv_len in the order of req_order (real requests only count)
-    # How many requests of the longest context the decoded tokens of this step weigh (see effective_requests),
-    # rounded up to a power of two.  Set by the runner for steps replayed as CUDA graphs, whose launch
+    # How many requests of the longest context the decoded tokens of this step weigh (sum / longest of the
+    # contexts), rounded to a power of two: CudaKernels.key_split_class.  Set by the runner for steps replayed as CUDA graphs, whose launch
     # geometry is fixed when they are captured; None lets the kernel library work it out per launch.
     key_split_class: Optional[int] = None
     all_decode: bool = False      # every request brings exactly one token
@@ -182,17 +182,6 @@ def pack_step(entries: Sequence[StepEntry], starts: Sequence[int], slots: Sequen
                 has_token_src=has_src,
                 all_decode=bool((q_lens == 1).all()), real_requests=nreal, real_logit_rows=real_rows)
     return out, layout, info
-
-
-def effective_requests(kv_lens) -> float:
-    """sum(context) / max(context): how many requests of the longest context read as many keys as these
-    do.  A step's decoded tokens are one (request, key/value head) work item each unless the key range is
-    shared out; the longest context sets how long the longest item runs, the sum how long all of them
-    take together, so this ratio, not the number of requests, says how many shares the key range needs."""
-    kv = np.asarray(kv_lens, dtype=np.float64)
-    if kv.size == 0 or kv.max() <= 0:
-        return 1.0
-    return float(kv.sum() / kv.max())
 
 
 def batch_from_device(dev: torch.Tensor, layout: BatchLayout, info) -> StepBatch:

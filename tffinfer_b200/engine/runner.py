@@ -20,8 +20,7 @@ from ..config import EngineConfig, read_config_json
 from ..parts import Model, CacheBinding, KVNeed, StateNeed
 from ..registry import get_architecture
 from ..weights import load_model_weights
-from .batch import (StepEntry, StepBatch, build_step_batch, pack_step, batch_from_device, BatchLayout,
-                    effective_requests)
+from .batch import StepEntry, StepBatch, build_step_batch, pack_step, batch_from_device, BatchLayout
 
 _TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 _STATE_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": torch.int32}
@@ -245,10 +244,8 @@ class ModelRunner:
         self.last_h2d_bytes = layout.total * 4
         batch = batch_from_device(st["dev"], layout, info)
         batch.graph_bucket = bucket
-        eff, cls = effective_requests(batch.h_sorted_kv_lens), 1
-        while cls * 1.4142 < eff:                   # to the nearest power of two, as the kernel library rounds
-            cls *= 2
-        batch.key_split_class = cls
+        classify = getattr(self.ops, "key_split_class", None)
+        batch.key_split_class = classify(batch.h_sorted_kv_lens) if classify is not None else 1
         return batch
 
     def _run_graph(self, batch: StepBatch) -> torch.Tensor:

@@ -50,6 +50,24 @@ def _ptr(t: Optional[torch.Tensor]):
     return _vp(t.data_ptr()) if t is not None else _vp(0)
 
 
+def effective_requests(kv_lens) -> float:
+    """sum(context) / max(context): how many requests of the longest context read as many keys as these
+    do.  A step's decoded tokens are one (request, key/value head) work item each unless the key range is
+    shared out; the longest context sets how long the longest item runs, the sum how long all of them
+    take together, so this ratio, not the number of requests, says how many shares the key range needs."""
+    kv = np.asarray(kv_lens, dtype=np.float64)
+    if kv.size == 0 or kv.max() <= 0:
+        return 1.0
+    return float(kv.sum() / kv.max())
+
+
+def nearest_power_of_two(x: float) -> int:
+    b = 1
+    while b * 1.4142 < x:
+        b *= 2
+    return b
+
+
 class CudaKernels:
     """Loads (building first if needed) the sm_100a kernel library."""
 
@@ -392,15 +410,19 @@ class CudaKernels:
 
     def attention_splits(self, num_requests: float, max_q_len: int, nq: int, nkv: int) -> int:
         """Shares of the key range per tile, for ``num_requests`` requests of one context length (for
-        unequal contexts: sum / longest, engine.batch.effective_requests).  The count is rounded to a
+        unequal contexts: sum / longest, effective_requests above).  The count is rounded to a
         power of two, so that a step replayed as a CUDA graph, captured for such a class, and an eager
         step cut alike."""
         if max_q_len * (nq // nkv) > 16:
             return 1                                   # portions: enough tiles already
-        b = 1
-        while b * 1.4142 < num_requests:               # to the nearest power of two
-            b *= 2
+        b = nearest_power_of_two(num_requests)
         return max(1, min(16, 2 * self.NUM_SMS // (b * nkv)))     # one wave of two CTAs per SM
+
+    @staticmethod
+    def key_split_class(kv_lens) -> int:
+        """The class of a batch of decoded tokens that fixes how their key ranges are shared out: a step
+        replayed as a CUDA graph is captured per class."""
+        return nearest_power_of_two(effective_requests(kv_lens))
 
     def _side_stream(self, device):
         """The second stream (and the two events to fork to it and join from it), made at first use."""
@@ -414,7 +436,6 @@ class CudaKernels:
         if batch.key_split_class is not None:
             eff = batch.key_split_class
         elif batch.h_sorted_kv_lens is not None:
-            from ..engine.batch import effective_requests
             eff = effective_requests(batch.h_sorted_kv_lens[first:first + count])
         else:
             eff = count
