@@ -155,3 +155,40 @@ def test_infer_runtime_and_cli(tmp_path, capsys):
     import json
     rec = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert rec["outputs"] == out
+
+
+@pytest.mark.parametrize("seed", [4, 8, 13, 15, 18, 30, 36])
+def test_random_workloads_follow_plain(tmp_path, seed):
+    """Prompts, numbers of new tokens, pool size, live requests, token budget, dtype and graphs drawn at
+    random (the seeds kept are ones in which pages run out and requests are recomputed): every token
+    is the plain implementation's choice and every page comes back."""
+    rng = random.Random(1000 + seed)
+    name = rng.choice("ABCD")
+    dtype = rng.choice(["float32", "bfloat16"])
+    cfg = tiny_config(name)
+    d = make_model_dir(tmp_path, name)
+    pm = PlainModel(d)
+    page = PAGE_SIZE[name]
+    n = rng.randint(2, 7)
+    cap = min(cfg.max_position - 40, 300)
+    lens = [rng.randint(1, cap) if rng.random() < 0.5 else rng.randint(1, 30) for _ in range(n)]
+    news = [rng.randint(1, 30) for _ in range(n)]
+    longest = max(-(-(l + m + 1) // page) * page for l, m in zip(lens, news))
+    pool = longest + rng.choice([0, page, longest // 2, 2 * longest])
+    live = rng.randint(1, 6)
+    budget = rng.choice([2, 5, 16, 64, 256])
+    prompts = [[rng.randrange(cfg.vocab_size) for _ in range(l)] for l in lens]
+    eng = Engine(d, EngineConfig(dtype=dtype, page_size=page, max_cache_tokens=pool, max_live_requests=live,
+                                 max_tokens_per_step=budget, use_cuda_graphs=rng.random() < 0.7))
+    ids = [eng.add_request(p, SamplingParams(max_new_tokens=m)) for p, m in zip(prompts, news)]
+    steps = 0
+    while eng.has_unfinished():
+        eng.step()
+        steps += 1
+        assert steps < 5000
+    eng.runner.ops.check_errors()
+    assert eng.scheduler.counters["preemptions"] > 0
+    for i, p, m in zip(ids, prompts, news):
+        g = eng.requests[i].generated
+        assert len(g) == m and _follows_plain(pm, p, g, 1e-5 if dtype == "float32" else 3e-2)
+    assert all(pl.num_free == pl.num_pages for pl in eng.runner.cache.pools)
