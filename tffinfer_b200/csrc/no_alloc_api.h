@@ -42,6 +42,9 @@ extern "C" {
 //   q [tokens, nq*d] bf16 (normalised, rotated), out [tokens, nq*d] bf16, paged cache
 //   [pages, cache_layers, 2, nkv, page_size, d] bf16, block_table int32 [requests, table_width],
 //   q_start int32 [requests+1], pos_start int32 [requests].
+// A cache stored with the layers outermost ([cache_layers, pages, 2, nkv, page_size, d], as the engine
+// allocates it) is passed as the block of the layer wanted: cache = that layer's [pages, 2, ...] block,
+// cache_layers = 1, layer = 0.
 // Returns 0 when the kernels were launched, TFF_ERR_SCRATCH_TOO_SMALL when the call needs
 // more scratch than the library holds, or the error codes of tff_attention_bf16.
 __attribute__((visibility("default")))
