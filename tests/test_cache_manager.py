@@ -1,10 +1,17 @@
 """The cache manager on the host: no page lost, held twice or freed twice, under random
-orders of requests; windows give pages back; exhaustion is all-or-nothing."""
+orders of requests; windows give pages back; exhaustion is all-or-nothing.  Every test of the
+manager runs on the C++ host runtime and on its Python twin."""
 import random
 
 import pytest
 
-from tffinfer_b200.cache import CacheManager, GroupSpec, PagePool, SlotPool, CacheAccountingError, NO_PAGE
+from tffinfer_b200.cache import (CacheManager, NativeCacheManager, GroupSpec, PagePool, SlotPool, CacheAccountingError,
+                                 NO_PAGE)
+
+
+@pytest.fixture(params=[NativeCacheManager, CacheManager], ids=["native", "python"])
+def Manager(request):
+    return request.param
 
 
 def test_pool_lifo_and_double_free():
@@ -33,13 +40,13 @@ def test_slots():
     s.check()
 
 
-def _mgr(pages=8, page=4, groups=None, live=4):
+def _mgr(Manager, pages=8, page=4, groups=None, live=4):
     groups = groups or [GroupSpec(2, 2, 16, 0)]
-    return CacheManager(groups, page, [pages] * len(groups), live)
+    return Manager(groups, page, [pages] * len(groups), live)
 
 
-def test_reserve_is_all_or_nothing_across_groups():
-    m = CacheManager([GroupSpec(2, 2, 16, 0), GroupSpec(1, 2, 16, 8)], 4, [8, 2], 4)
+def test_reserve_is_all_or_nothing_across_groups(Manager):
+    m = Manager([GroupSpec(2, 2, 16, 0), GroupSpec(1, 2, 16, 8)], 4, [8, 2], 4)
     assert m.admit("a") == 0
     assert m.reserve("a", 8)            # 2 pages in each group
     m.commit("a", 8)
@@ -53,8 +60,8 @@ def test_reserve_is_all_or_nothing_across_groups():
     m.check()
 
 
-def test_growth_page_by_page_and_block_table():
-    m = _mgr()
+def test_growth_page_by_page_and_block_table(Manager):
+    m = _mgr(Manager)
     m.admit("a")
     for n in range(1, 14):
         assert m.reserve("a", 1)
@@ -68,8 +75,8 @@ def test_growth_page_by_page_and_block_table():
     m.check()
 
 
-def test_window_gives_pages_back_when_passed():
-    m = CacheManager([GroupSpec(1, 1, 16, 0), GroupSpec(1, 1, 16, 6)], 4, [16, 16], 2)
+def test_window_gives_pages_back_when_passed(Manager):
+    m = Manager([GroupSpec(1, 1, 16, 0), GroupSpec(1, 1, 16, 6)], 4, [16, 16], 2)
     m.admit("a")
     assert m.reserve("a", 20)
     m.commit("a", 20)
@@ -88,9 +95,9 @@ def test_window_gives_pages_back_when_passed():
     m.check()
 
 
-def test_random_orders_never_lose_or_double_book_a_page():
+def test_random_orders_never_lose_or_double_book_a_page(Manager):
     rng = random.Random(11)
-    m = CacheManager([GroupSpec(3, 2, 16, 0), GroupSpec(2, 2, 16, 10)], 4, [24, 12], 5)
+    m = Manager([GroupSpec(3, 2, 16, 0), GroupSpec(2, 2, 16, 10)], 4, [24, 12], 5)
     live, next_id, refused = {}, 0, 0
     for _ in range(3000):
         op = rng.random()
@@ -123,3 +130,26 @@ def test_random_orders_never_lose_or_double_book_a_page():
         m.release(r)
     m.check()
     assert all(p.num_free == p.num_pages for p in m.pools) and m.slots.num_free == 5
+
+
+def test_misuse_is_an_error_not_a_wrong_result(Manager):
+    m = _mgr(Manager, live=2)
+    assert m.admit("a") == 0
+    with pytest.raises(CacheAccountingError, match="already live"):
+        m.admit("a")
+    with pytest.raises(KeyError):
+        m.num_tokens("nobody")
+    with pytest.raises(KeyError):
+        m.reserve("nobody", 1)
+    with pytest.raises(ValueError):
+        m.reserve("a", -1)
+    assert m.reserve("a", 3)
+    with pytest.raises(CacheAccountingError, match="reserved"):
+        m.commit("a", 5)
+    assert m.admit("b") == 1 and m.admit("c") is None          # no slot left: nothing taken
+    assert not m.is_live("c")
+    m.release("a")
+    with pytest.raises(KeyError):
+        m.release("a")
+    m.check()
+    assert m.stats()["live_requests"] == 1 and m.pools[0].num_free == 8

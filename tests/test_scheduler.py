@@ -1,19 +1,30 @@
 """The scheduler's decisions on the host (a cache manager, no model), and generation
-through the entry point with the kernels' plain twins."""
+through the entry point with the kernels' plain twins.  Every test runs with the cache manager
+of the C++ host runtime and with its Python twin."""
 import pytest
 import torch
 
 from cpu_ops import CpuOps
 from helpers import tiny_config, make_model_dir, PAGE_SIZE
 from plain_qwen3 import PlainModel, sample_temperature, sample_greedy
-from tffinfer_b200.cache import CacheManager, GroupSpec
+from tffinfer_b200.cache import make_cache_manager, GroupSpec
 from tffinfer_b200.config import EngineConfig
 from tffinfer_b200.engine import Scheduler, Request, Engine, ModelRunner
 from tffinfer_b200.sampling import SamplingParams, uniform_for
 
 
+NATIVE = True
+
+
+@pytest.fixture(autouse=True, params=[True, False], ids=["native", "python"])
+def _which_manager(request):
+    global NATIVE
+    NATIVE = request.param
+    yield
+
+
 def _sched(pages=16, page=4, live=4, budget=8, max_len=64):
-    cache = CacheManager([GroupSpec(2, 2, 16, 0)], page, [pages], live)
+    cache = make_cache_manager([GroupSpec(2, 2, 16, 0)], page, [pages], live, native=NATIVE)
     return Scheduler(cache, budget, max_len), cache
 
 
@@ -121,7 +132,7 @@ def test_a_request_that_cannot_fit_alone_ends_with_out_of_memory():
 # ------------------------------------------------------------------ through the entry point
 def _engine(tmp_path, name, **kw):
     d = make_model_dir(tmp_path, name)
-    ecfg = EngineConfig(dtype="float32", page_size=PAGE_SIZE[name], device="cpu", **kw)
+    ecfg = EngineConfig(dtype="float32", page_size=PAGE_SIZE[name], device="cpu", native_host=NATIVE, **kw)
     return d, Engine(runner=ModelRunner(d, ecfg, ops=CpuOps()))
 
 

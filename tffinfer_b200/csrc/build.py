@@ -150,5 +150,55 @@ def compile_all(bdir: str, verbose: bool = True, extra_flags: Optional[List[str]
     return os.path.join(bdir, LIB_NAME)
 
 
+# ------------------------------------------------------------------ host runtime (no CUDA)
+HOST_DIR = os.path.join(CSRC_DIR, "host")
+HOST_LIB_NAME = "libtffinfer_host.so"
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden"]
+
+
+def find_cxx() -> str:
+    for c in (os.environ.get("CXX"), "g++", "c++", "clang++"):
+        w = shutil.which(c) if c else None
+        if w:
+            return w
+    raise RuntimeError("no C++ compiler found (looked at CXX, g++, c++, clang++): "
+                       "the host runtime of tffinfer_b200 cannot be compiled")
+
+
+def host_library_path(build: bool = True, verbose: bool = True) -> str:
+    """Path of an up-to-date host-runtime library (page pools, block tables, step packing; csrc/host/),
+    compiled with the host compiler alone, so it also builds where there is no CUDA toolkit."""
+    bdir = build_dir()
+    lib = os.path.join(bdir, HOST_LIB_NAME)
+    stamp = os.path.join(bdir, "host_stamp.txt")
+    files = sorted(f for f in os.listdir(HOST_DIR) if f.endswith((".cpp", ".h")))
+    h = hashlib.sha256()
+    for f in files:
+        h.update(f.encode())
+        with open(os.path.join(HOST_DIR, f), "rb") as fh:
+            h.update(fh.read())
+    h.update(" ".join(HOST_FLAGS).encode())
+    want = h.hexdigest()
+    if os.path.isfile(lib) and os.path.isfile(stamp):
+        with open(stamp) as f:
+            if f.read().strip() == want:
+                return lib
+    if not build:
+        raise RuntimeError(f"{lib} is missing or out of date")
+    cxx = find_cxx()
+    tmp = os.path.join(bdir, f".{HOST_LIB_NAME}.{os.getpid()}")
+    srcs = [os.path.join(HOST_DIR, f) for f in files if f.endswith(".cpp")]
+    p = subprocess.run([cxx] + HOST_FLAGS + ["-I", HOST_DIR] + srcs + ["-o", tmp],
+                       stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if p.returncode != 0:
+        raise RuntimeError(f"compiling the host runtime failed:\n{p.stdout}")
+    os.replace(tmp, lib)
+    with open(stamp, "w") as f:
+        f.write(want + "\n")
+    _say(f"built {HOST_LIB_NAME}", verbose)
+    return lib
+
+
 if __name__ == "__main__":
+    print(host_library_path(build=True, verbose=True))
     print(library_path(build=True, verbose=True))

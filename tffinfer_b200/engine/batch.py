@@ -196,10 +196,8 @@ def batch_from_device(dev: torch.Tensor, layout: BatchLayout, info) -> StepBatch
         real_requests=info["real_requests"], real_logit_rows=info["real_logit_rows"])
 
 
-def build_step_batch(entries: Sequence[StepEntry], starts: Sequence[int], slots: Sequence[int],
-                     tables: Sequence[Sequence[Sequence[int]]], device, pinned: bool = False) -> StepBatch:
-    """Packs the step and copies it to ``device`` in one transfer."""
-    arr, layout, info = pack_step(entries, starts, slots, tables)
+def packed_to_device(arr: np.ndarray, layout: BatchLayout, info, device, pinned: bool = False) -> StepBatch:
+    """The packed step on ``device``, in one transfer."""
     host = torch.from_numpy(arr)
     if str(device) == "cpu":
         dev = host
@@ -208,3 +206,10 @@ def build_step_batch(entries: Sequence[StepEntry], starts: Sequence[int], slots:
     else:
         dev = host.to(device)
     return batch_from_device(dev, layout, info)
+
+
+def build_step_batch(entries: Sequence[StepEntry], starts: Sequence[int], slots: Sequence[int],
+                     tables: Sequence[Sequence[Sequence[int]]], device, pinned: bool = False) -> StepBatch:
+    """Packs the step and copies it to ``device`` in one transfer."""
+    arr, layout, info = pack_step(entries, starts, slots, tables)
+    return packed_to_device(arr, layout, info, device, pinned)

@@ -15,12 +15,12 @@ from typing import Dict, Hashable, List, Optional, Sequence
 import numpy as np
 import torch
 
-from ..cache import CacheManager, GroupSpec
+from ..cache import make_cache_manager, GroupSpec
 from ..config import EngineConfig, read_config_json
 from ..parts import Model, CacheBinding, KVNeed, StateNeed
 from ..registry import get_architecture
 from ..weights import load_model_weights
-from .batch import StepEntry, StepBatch, build_step_batch, pack_step, batch_from_device, BatchLayout
+from .batch import StepEntry, StepBatch, pack_step, packed_to_device, batch_from_device, BatchLayout
 
 _TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 _STATE_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": torch.int32}
@@ -144,7 +144,8 @@ class ModelRunner:
         if self.graph_buckets[-1] < min(self.ecfg.max_live_requests, 256):
             self.graph_buckets.append(min(self.ecfg.max_live_requests, 256))
         self.table_width = max(1, -(-self.max_model_len // ps))
-        self.cache = CacheManager(groups, ps, n_pages, self.ecfg.max_live_requests)
+        self.cache = make_cache_manager(groups, ps, n_pages, self.ecfg.max_live_requests,
+                                        native=self.ecfg.native_host)
         self.groups = groups
 
     # --------------------------------------------------------------- requests
@@ -196,15 +197,12 @@ class ModelRunner:
         for e in entries:
             ok = self.cache.reserve(e.req, len(e.tokens))
             assert ok
-        starts = [self.cache.num_tokens(e.req) for e in entries]
-        slots = [self.cache.slot_of(e.req) for e in entries]
-        tables = [[self.cache.block_table(e.req, g) for e in entries] for g in range(len(self.groups))]
         if self._graph_eligible(entries):
-            batch = self._make_static_batch(entries, starts, slots, tables)
+            batch = self._make_static_batch(entries)
             if batch.tok_src is not None:
                 self.ops.gather_tokens(batch.token_ids, prev_tokens, batch.tok_src)
             return batch
-        batch = build_step_batch(entries, starts, slots, tables, self.device, pinned=self.device.type == "cuda")
+        batch = packed_to_device(*self._pack(entries), self.device, pinned=self.device.type == "cuda")
         if batch.tok_src is not None:
             self.ops.gather_tokens(batch.token_ids, prev_tokens, batch.tok_src)
         self.last_h2d_bytes = batch.token_ids.numel() * 0 + 4 * (
@@ -218,7 +216,18 @@ class ModelRunner:
                 and len(entries) <= self.graph_buckets[-1]
                 and all(len(e.tokens) == 1 and len(e.want) == 1 for e in entries))
 
-    def _make_static_batch(self, entries, starts, slots, tables) -> StepBatch:
+    def _pack(self, entries, **kw):
+        """The step's integer arrays in one host buffer: by the C++ host runtime, which holds the positions,
+        slots and block tables itself, or by its Python twin from lists read out of the cache manager."""
+        native = getattr(self.cache, "pack_step", None)
+        if native is not None:
+            return native(entries, **kw)
+        starts = [self.cache.num_tokens(e.req) for e in entries]
+        slots = [self.cache.slot_of(e.req) for e in entries]
+        tables = [[self.cache.block_table(e.req, g) for e in entries] for g in range(len(self.groups))]
+        return pack_step(entries, starts, slots, tables, **kw)
+
+    def _make_static_batch(self, entries) -> StepBatch:
         """Decode-only steps use device arrays of fixed address and size, one set per
         batch-size bucket, so that the step can be replayed as a CUDA graph.  A graph fixes the
         geometry of its launches, and how the attention shares out the key range depends on how
@@ -234,9 +243,9 @@ class ModelRunner:
             self._graphs[bucket] = st
         if st.get("copied") is not None:
             st["copied"].synchronize()              # the last copy out of the staging buffer has finished
-        arr, layout, info = pack_step(entries, starts, slots, tables, pad_requests=bucket,
-                                      widths=st["layout"].widths, dummy_pages=self.dummy_pages,
-                                      dummy_slot=self.dummy_slot, out=st["host"].numpy())
+        arr, layout, info = self._pack(entries, pad_requests=bucket, widths=st["layout"].widths,
+                                       dummy_pages=self.dummy_pages, dummy_slot=self.dummy_slot,
+                                       out=st["host"].numpy())
         st["dev"].copy_(st["host"], non_blocking=True)
         if st.get("copied") is None:
             st["copied"] = torch.cuda.Event()
