@@ -116,7 +116,10 @@ class NativeCacheManager:
     def __del__(self):
         h, self._h = getattr(self, "_h", None), None
         if h:
-            self.lib.tffh_cache_destroy(h)
+            try:
+                self.lib.tffh_cache_destroy(h)
+            except Exception:        # the interpreter is shutting down and the library is gone
+                pass
 
     # ------------------------------------------------------------- plumbing
     def _raise(self, code: int):
