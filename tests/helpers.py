@@ -5,12 +5,11 @@ from __future__ import annotations
 
 import os
 import random
-from typing import Dict, List, Sequence, Tuple
+from typing import Dict, List, Sequence
 
-import numpy as np
 import torch
 
-from tffinfer_b200.config import Qwen3Config, EngineConfig
+from tffinfer_b200.config import Qwen3Config
 from tffinfer_b200.engine import ModelRunner, StepEntry
 from tffinfer_b200.weights import write_random_model
 

@@ -15,7 +15,7 @@ from __future__ import annotations
 import json
 import math
 import os
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, Sequence
 
 import torch
 

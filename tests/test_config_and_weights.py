@@ -8,8 +8,8 @@ import torch
 from helpers import tiny_config, make_model_dir
 from tffinfer_b200 import get_architecture, registered_architectures, RegistryError, ConfigError, WeightError
 from tffinfer_b200.config import Qwen3Config, read_config_json, EngineConfig
-from tffinfer_b200.parts import Model, MATRIX, VECTOR
-from tffinfer_b200.weights import (write_random_model, load_model_weights, write_safetensors, SafetensorsFile,
+from tffinfer_b200.parts import Model, MATRIX
+from tffinfer_b200.weights import (load_model_weights, write_safetensors, SafetensorsFile,
                                    random_state_dict, held_dtype)
 
 

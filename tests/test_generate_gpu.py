@@ -3,10 +3,9 @@ plain implementation, with and without CUDA graphs, long decoding, preemption.""
 import random
 
 import pytest
-import torch
 
 from helpers import tiny_config, make_model_dir, PAGE_SIZE
-from plain_qwen3 import PlainModel, sample_greedy, sample_temperature
+from plain_qwen3 import PlainModel, sample_temperature
 from tffinfer_b200 import Engine, EngineConfig, SamplingParams
 from tffinfer_b200.sampling import uniform_for
 

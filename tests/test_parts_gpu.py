@@ -1,6 +1,5 @@
 """Each part of a layer alone, built through the registry with sizes of its own, against
 the plain function of the same part (tests/plain_qwen3.py), in 32-bit and in bfloat16."""
-import math
 
 import pytest
 import torch

@@ -3,9 +3,9 @@ for every way of cutting the same requests into steps."""
 import pytest
 import torch
 
-from helpers import (tiny_config, make_model_dir, make_requests, PAGE_SIZE, PROMPT_LENS,
+from helpers import (make_model_dir, make_requests, PAGE_SIZE, PROMPT_LENS,
                      trace_whole, trace_tail_decode, trace_portions, trace_mixed, run_trace,
-                     max_rel_err, first_bad)
+                     first_bad)
 from plain_qwen3 import PlainModel
 from tffinfer_b200.config import EngineConfig
 from tffinfer_b200.engine import ModelRunner

@@ -2,10 +2,9 @@
 through the entry point with the kernels' plain twins.  Every test runs with the cache manager
 of the C++ host runtime and with its Python twin."""
 import pytest
-import torch
 
 from cpu_ops import CpuOps
-from helpers import tiny_config, make_model_dir, PAGE_SIZE
+from helpers import make_model_dir, PAGE_SIZE
 from plain_qwen3 import PlainModel, sample_temperature, sample_greedy
 from tffinfer_b200.cache import make_cache_manager, GroupSpec
 from tffinfer_b200.config import EngineConfig

@@ -10,7 +10,6 @@ tolerance that all other tests use."""
 import os
 
 import pytest
-import torch
 
 from helpers import (tiny_config, make_requests, PAGE_SIZE, PROMPT_LENS, trace_tail_decode, trace_portions,
                      trace_mixed, run_trace, first_bad, max_rel_err)

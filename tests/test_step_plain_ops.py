@@ -2,10 +2,9 @@
 kernels replaced by their plain twins (tests/cpu_ops.py): every way of cutting the
 same requests into steps gives the logits of the plain whole-sequence implementation."""
 import pytest
-import torch
 
 from cpu_ops import CpuOps
-from helpers import (tiny_config, make_model_dir, make_requests, PAGE_SIZE, PROMPT_LENS,
+from helpers import (make_model_dir, make_requests, PAGE_SIZE, PROMPT_LENS,
                      trace_whole, trace_tail_decode, trace_portions, trace_mixed, run_trace, max_rel_err)
 from plain_qwen3 import PlainModel
 from tffinfer_b200.config import EngineConfig

@@ -6,7 +6,6 @@ import os
 import random
 
 import pytest
-import torch
 
 from toy_parts import register_toy, ToyConfig, toy_plain_logits
 from helpers import run_trace, trace_whole, trace_portions, trace_mixed, max_rel_err

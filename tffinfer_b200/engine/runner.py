@@ -12,7 +12,6 @@ from __future__ import annotations
 
 from typing import Dict, Hashable, List, Optional, Sequence
 
-import numpy as np
 import torch
 
 from ..cache import make_cache_manager, GroupSpec

@@ -7,7 +7,7 @@ in through ``ops`` (kernels/library.py): a part never touches a device API itsel
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Dict, Optional, Tuple
 
 import torch

@@ -13,7 +13,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..registry import get_part
-from .base import (Part, Block, LayerContext, WeightSpec, MATRIX, KVNeed, StateNeed)
+from .base import Part, Block, LayerContext, WeightSpec, MATRIX
 from .description import ModelDescription, PartSpec
 
 

@@ -6,7 +6,7 @@ repetition penalty and multinomial draws exist unused (LLMSampler.cpp:21-54).  H
 they are honoured."""
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Tuple
 
 GREEDY = "greedy"

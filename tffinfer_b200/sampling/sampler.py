@@ -7,7 +7,7 @@ a request's tokens do not depend on which other requests share its steps, and a
 request that was preempted and recomputed continues with the same draws."""
 from __future__ import annotations
 
-from typing import List, Optional, Sequence
+from typing import Optional, Sequence
 
 import numpy as np
 import torch

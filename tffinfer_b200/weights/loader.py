@@ -18,7 +18,7 @@ from typing import Dict, List
 
 import torch
 
-from ..parts.base import WeightSpec, MATRIX, VECTOR, INT_TABLE
+from ..parts.base import WeightSpec, VECTOR, INT_TABLE
 from .safetensors_io import SafetensorsFile, open_model_files
 
 

@@ -11,7 +11,7 @@ import json
 import mmap
 import os
 import struct
-from typing import Dict, Iterable, List, Tuple
+from typing import Dict, List, Tuple
 
 import numpy as np
 import torch
