@@ -96,3 +96,55 @@ def test_native_packer_refuses_what_the_python_one_refuses():
         m.pack_step([StepEntry("a", [1, 2], [1])], out=np.zeros(5, dtype=np.int32))
     arr, layout, info = m.pack_step([StepEntry("a", [1, 2], [1])])
     assert layout.T == 2 and layout.B == 1 and info["real_logit_rows"] == 1 and not info["all_decode"]
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2, 3])
+def test_native_planning_equals_the_python_scheduler_in_lockstep(seed):
+    """Two schedulers over two cache managers, one deciding in C++ and one in Python, fed the same requests
+    and the same drawn tokens: every plan (who runs, from where, how many tokens, who is preempted, who ends
+    and why) and the caches' accounts are the same step after step, through preemptions and refusals."""
+    from tffinfer_b200.engine import Scheduler, Request
+    from tffinfer_b200.sampling import SamplingParams
+    rng = random.Random(50 + seed)
+    page = rng.choice([2, 4, 8])
+    pages = rng.randint(6, 24)
+    live = rng.randint(1, 4)
+    budget = rng.choice([3, 8, 20])
+    max_len = rng.choice([40, 200])
+    groups = [GroupSpec(2, 2, 16, 0)] + ([GroupSpec(1, 2, 16, 7)] if seed % 2 else [])
+    sizes = [pages] + ([max(3, pages // 2)] if seed % 2 else [])
+    sa = Scheduler(CacheManager(groups, page, sizes, live), budget, max_len)
+    sb = Scheduler(NativeCacheManager(groups, page, sizes, live), budget, max_len)
+    assert sb.native_plan and not sa.native_plan
+
+    def both(i, n, new):
+        for s in (sa, sb):
+            s.add(Request(id=f"r{i}", prompt=list(range(1, n + 1)), params=SamplingParams(max_new_tokens=new), key=i))
+
+    added = preempted = refused = 0
+    for step in range(400):
+        if rng.random() < 0.3:
+            n = rng.choice([0, 1, 3, 9, 17, 30, 60, 150]) if rng.random() < 0.2 else rng.randint(1, 25)
+            both(added, n, rng.randint(1, 6))
+            added += 1
+        pa, pb = sa.schedule(), sb.schedule()
+        assert [(e.request.id, e.start, e.tokens, e.samples) for e in pa.entries] == \
+               [(e.request.id, e.start, e.tokens, e.samples) for e in pb.entries], step
+        assert [r.id for r in pa.preempted] == [r.id for r in pb.preempted]
+        assert [(r.id, r.finish_reason) for r in pa.finished] == [(r.id, r.finish_reason) for r in pb.finished]
+        assert [r.id for r in sa.running] == [r.id for r in sb.running]
+        assert [r.id for r in sa.waiting] == [r.id for r in sb.waiting]
+        preempted += len(pb.preempted)
+        refused += len(pb.finished)
+        drawn = {e.request.id: rng.randrange(50) for e in pa.entries if e.samples}
+        oa, ob = sa.update(pa, drawn), sb.update(pb, drawn)
+        assert [(o.request_id, o.token, o.finished, o.finish_reason) for o in oa] == \
+               [(o.request_id, o.token, o.finished, o.finish_reason) for o in ob]
+        assert sa.cache.stats() == sb.cache.stats()
+        for r in sb.running:
+            for g in range(len(groups)):
+                assert sa.cache.block_table(r.id, g) == sb.cache.block_table(r.id, g)
+        if step % 20 == 0:
+            sa.cache.check(); sb.cache.check()
+    assert added > 50 and sa.counters == sb.counters
+    assert preempted + refused > 0

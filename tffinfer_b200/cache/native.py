@@ -42,6 +42,8 @@ def host_library():
         lib.tffh_block_table.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, _i32p, ctypes.c_int]
         lib.tffh_check.argtypes = [ctypes.c_void_p]
         lib.tffh_count.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
+        lib.tffh_plan_step.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, _i64p, _i32p,
+                                       ctypes.c_int, _i64p, _i32p, _i32p, _i32p, ctypes.c_int]
         lib.tffh_pack_step.restype = ctypes.c_int64
         lib.tffh_pack_step.argtypes = [ctypes.c_void_p, ctypes.c_int, _i64p, _i32p, _i32p, _i32p, _i32p, _i32p,
                                        ctypes.c_int, _i32p, _i32p, ctypes.c_int, _i32p, ctypes.c_int64, _i32p]
@@ -222,6 +224,42 @@ class NativeCacheManager:
                 "pages_free": [p.num_free for p in self.pools],
                 "pages_high_water": [p.high_water for p in self.pools],
                 "slots_free": self.slots.num_free, "live_requests": self._count(4, 0)}
+
+    # ------------------------------------------------------------- planning
+    EVENT_PREEMPT, EVENT_FINISH, EVENT_ADMIT, EVENT_RUN = 1, 2, 3, 4
+    REASONS = {1: "out_of_memory", 2: "too_long", 3: "empty_prompt"}
+
+    def plan_step(self, budget_tokens: int, max_model_len: int, running: Sequence, running_len: Sequence[int],
+                  waiting: Sequence, waiting_len: Sequence[int], waiting_prompt_len: Sequence[int]):
+        """The decisions of one scheduler pass, taken by the C++ host runtime (tffh_plan_step): which running
+        requests bring how many tokens, who is preempted, who ends without running, who is admitted; the pages
+        of the chosen are taken.  ``running`` are live request names in the order of their admission,
+        ``waiting`` the queue in arrival order.  Returns events (kind, name, a, b) in the order they happened:
+        (EVENT_PREEMPT, name, 0, 0), (EVENT_FINISH, name, reason, was_running), (EVENT_ADMIT, name, slot, 0),
+        (EVENT_RUN, name, tokens, start)."""
+        nr, nw = len(running), len(waiting)
+        rh = np.fromiter((self._h_of(r) for r in running), dtype=np.int64, count=nr) if nr else np.zeros(1, np.int64)
+        rl = np.asarray(list(running_len) or [0], dtype=np.int32)
+        wh = np.arange(self._next, self._next + max(1, nw), dtype=np.int64)     # handles the admitted would get
+        wl = np.asarray(list(waiting_len) or [0], dtype=np.int32)
+        wp = np.asarray(list(waiting_prompt_len) or [0], dtype=np.int32)
+        cap = 2 * (nr + nw) + 4
+        ev = np.zeros(4 * cap, dtype=np.int32)
+        n = self.lib.tffh_plan_step(self._h, int(budget_tokens), int(max_model_len), nr, rh.ctypes.data_as(_i64p),
+                                    _p32(rl), nw, wh.ctypes.data_as(_i64p), _p32(wl), _p32(wp), _p32(ev), cap)
+        self._next += nw
+        if n < 0:
+            self._raise(n)
+        out = []
+        for kind, uid, a, b in ev[:4 * n].reshape(n, 4).tolist():
+            name = running[uid] if uid < nr else waiting[uid - nr]
+            handle = int(rh[uid]) if uid < nr else int(wh[uid - nr])
+            if kind == self.EVENT_PREEMPT or (kind == self.EVENT_FINISH and b):
+                del self._handle[name]
+            elif kind == self.EVENT_ADMIT:
+                self._handle[name] = handle
+            out.append((kind, name, self.REASONS[a] if kind == self.EVENT_FINISH else a, b))
+        return out
 
     # -------------------------------------------------------------- packing
     def pack_step(self, entries, *, pad_requests: int = 0, widths: Optional[Sequence[int]] = None,

@@ -376,3 +376,114 @@ TFFH_API int64_t tffh_pack_step(void* cache, int n, const int64_t* reqs, const i
     info[7] = real_rows;
     return total;
 }
+
+// ---------------------------------------------------------------------------------------------- planning
+namespace {
+struct Candidate {
+    int uid;            // index into running[] or n_running + index into waiting[]
+    int64_t handle;
+    int len;            // prompt + generated tokens
+    int prompt_len;
+};
+}  // namespace
+
+TFFH_API int tffh_plan_step(void* cache, int budget_tokens, int max_model_len,
+                            int n_running, const int64_t* running, const int* running_len,
+                            int n_waiting, const int64_t* waiting, const int* waiting_len, const int* waiting_prompt_len,
+                            int* events, int capacity) {
+    Cache* c = as_cache(cache);
+    const int G = (int)c->pools.size();
+    std::vector<Candidate> run, wait;
+    for (int i = 0; i < n_running; ++i) {
+        if (!c->find(running[i])) return c->fail(TFFH_ERR_UNKNOWN, "request " + std::to_string(running[i]) + " is not live");
+        run.push_back({i, running[i], running_len[i], 1});      // a live request has a prompt
+    }
+    for (int j = 0; j < n_waiting; ++j) wait.push_back({n_running + j, waiting[j], waiting_len[j], waiting_prompt_len[j]});
+    int n_events = 0;
+    auto emit = [&](int kind, int uid, int a, int b) -> bool {
+        if (n_events >= capacity) return false;
+        int* e = events + 4 * n_events++;
+        e[0] = kind; e[1] = uid; e[2] = a; e[3] = b;
+        return true;
+    };
+    const char* too_many = "more events than the buffer given holds";
+    int capacity_tokens = INT32_MAX;
+    for (const Pool& p : c->pools) capacity_tokens = std::min<int64_t>(capacity_tokens, (int64_t)p.total * c->page_size);
+
+    std::vector<std::pair<int, int>> chosen;        // (position in run, tokens)
+    std::vector<int> free_pages(G), need(G);
+    for (;;) {
+        int budget = budget_tokens;
+        for (int g = 0; g < G; ++g) free_pages[g] = c->pools[g].num_free();
+        chosen.clear();
+        bool ok = true;
+        // running requests, oldest admission first: decoded tokens (one each), then portions of prompts
+        for (int pass = 0; pass < 2 && ok; ++pass)
+            for (int i = 0; i < (int)run.size(); ++i) {
+                const RequestCache* rc = c->find(run[i].handle);
+                const int left = run[i].len - rc->num_tokens;
+                if (pass == 0 ? left != 1 : left <= 1) continue;
+                if (budget <= 0) { pass = 2; break; }
+                const int n = std::min(left, budget);
+                c->pages_needed(*rc, n, need.data());
+                for (int g = 0; g < G; ++g) ok = ok && need[g] <= free_pages[g];
+                if (!ok) break;
+                for (int g = 0; g < G; ++g) free_pages[g] -= need[g];
+                budget -= n;
+                chosen.emplace_back(i, n);
+            }
+        if (!ok) {
+            // pages ran out: the request admitted last gives way (alone, it is too large for the pool)
+            const Candidate victim = run.back();
+            run.pop_back();
+            if (tffh_release(cache, victim.handle) < 0) return TFFH_ERR_ACCOUNTING;
+            if (run.empty()) {
+                if (!emit(TFFH_EVENT_FINISH, victim.uid, TFFH_REASON_OUT_OF_MEMORY, 1)) return c->fail(TFFH_ERR_TOO_SMALL, too_many);
+            } else {
+                if (!emit(TFFH_EVENT_PREEMPT, victim.uid, 0, 0)) return c->fail(TFFH_ERR_TOO_SMALL, too_many);
+                wait.insert(wait.begin(), victim);
+            }
+            continue;
+        }
+        // admissions, in arrival order, while a slot, budget and pages are there
+        size_t w = 0;
+        while (w < wait.size() && budget > 0) {
+            const Candidate r = wait[w];
+            if (r.prompt_len == 0 || r.len > max_model_len) {
+                if (!emit(TFFH_EVENT_FINISH, r.uid, r.prompt_len ? TFFH_REASON_TOO_LONG : TFFH_REASON_EMPTY_PROMPT, 0))
+                    return c->fail(TFFH_ERR_TOO_SMALL, too_many);
+                ++w;
+                continue;
+            }
+            if (r.len > capacity_tokens) {
+                if (!emit(TFFH_EVENT_FINISH, r.uid, TFFH_REASON_OUT_OF_MEMORY, 0)) return c->fail(TFFH_ERR_TOO_SMALL, too_many);
+                ++w;
+                continue;
+            }
+            if (c->slots.num_free() == 0) break;
+            const int n = std::min(r.len, budget);
+            const int blocks = (n + c->page_size - 1) / c->page_size;
+            bool fits = true;
+            for (int g = 0; g < G; ++g) fits = fits && blocks <= free_pages[g];
+            if (!fits) break;
+            const int slot = tffh_admit(cache, r.handle);
+            if (slot < 0) return slot == -100 ? c->fail(TFFH_ERR_ACCOUNTING, "a free slot vanished") : slot;
+            if (!emit(TFFH_EVENT_ADMIT, r.uid, slot, 0)) return c->fail(TFFH_ERR_TOO_SMALL, too_many);
+            for (int g = 0; g < G; ++g) free_pages[g] -= blocks;
+            budget -= n;
+            run.push_back(r);
+            chosen.emplace_back((int)run.size() - 1, n);
+            ++w;
+        }
+        break;
+    }
+    for (const auto& ch : chosen) {
+        const Candidate& r = run[ch.first];
+        const int start = c->find(r.handle)->num_tokens;
+        const int got = tffh_reserve(cache, r.handle, ch.second);
+        if (got < 0) return got;
+        if (got == 0) return c->fail(TFFH_ERR_ACCOUNTING, "pages were counted but could not be taken");
+        if (!emit(TFFH_EVENT_RUN, r.uid, ch.second, start)) return c->fail(TFFH_ERR_TOO_SMALL, too_many);
+    }
+    return n_events;
+}

@@ -64,3 +64,23 @@ TFFH_API int64_t tffh_pack_step(void* cache, int n, const int64_t* reqs, const i
                                 const int* want_start, const int* want, const int* tok_src,
                                 int pad_requests, int* widths, const int* dummy_pages, int dummy_slot,
                                 int* out, int64_t out_capacity, int* info);
+
+// ---- planning a step (the decisions of engine/scheduler.py: Scheduler.schedule, its Python twin)
+// running[0..n_running): the live requests in the order of their admission, with their lengths (prompt +
+// generated tokens); waiting[0..n_waiting): the queue in arrival order, with the handle each would be admitted
+// under, its length and the length of its prompt.  Decoded tokens first (one each), then portions of prompts
+// under budget_tokens, then admissions while a slot, budget and pages are there; when the pages do not
+// suffice the request admitted last is released and goes to the front of the queue (alone, it ends: out of
+// memory) and the pass starts again.  Pages of the chosen requests are taken.  Writes events of four ints
+// (kind, uid, a, b), uid being the index into running[] or n_running + the index into waiting[], in the order
+// in which they happened, and returns their number:
+//   TFFH_EVENT_PREEMPT  uid                      released, now first in the queue
+//   TFFH_EVENT_FINISH   uid, reason, was_running ended without running (released if it was running)
+//   TFFH_EVENT_ADMIT    uid, slot                 now live
+//   TFFH_EVENT_RUN      uid, tokens, start        brings ``tokens`` tokens from position ``start`` in this step
+enum { TFFH_EVENT_PREEMPT = 1, TFFH_EVENT_FINISH = 2, TFFH_EVENT_ADMIT = 3, TFFH_EVENT_RUN = 4 };
+enum { TFFH_REASON_OUT_OF_MEMORY = 1, TFFH_REASON_TOO_LONG = 2, TFFH_REASON_EMPTY_PROMPT = 3 };
+TFFH_API int tffh_plan_step(void* cache, int budget_tokens, int max_model_len,
+                            int n_running, const int64_t* running, const int* running_len,
+                            int n_waiting, const int64_t* waiting, const int* waiting_len, const int* waiting_prompt_len,
+                            int* events, int capacity);

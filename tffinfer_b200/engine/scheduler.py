@@ -88,8 +88,13 @@ class StepOutput:
 
 
 class Scheduler:
-    def __init__(self, cache: CacheManager, max_tokens_per_step: int, max_model_len: int):
+    def __init__(self, cache: CacheManager, max_tokens_per_step: int, max_model_len: int,
+                 native_plan: Optional[bool] = None):
         self.cache = cache
+        # decisions by the C++ host runtime when the cache manager is its (None: whenever it is)
+        self.native_plan = hasattr(cache, "plan_step") if native_plan is None else bool(native_plan)
+        if self.native_plan and not hasattr(cache, "plan_step"):
+            raise ValueError("native planning needs the cache manager of the C++ host runtime")
         self.max_tokens_per_step = int(max_tokens_per_step)
         self.max_model_len = int(max_model_len)
         self.waiting: Deque[Request] = deque()
@@ -133,7 +138,12 @@ class Scheduler:
 
     def schedule(self) -> StepPlan:
         """Decides the next step and takes its pages.  The plan's entries are ready to be
-        run; after the step, call :meth:`update` with the drawn tokens."""
+        run; after the step, call :meth:`update` with the drawn tokens.  With the cache manager of the
+        C++ host runtime the decisions are taken there (tffh_plan_step in csrc/host/host_runtime.cpp) and
+        applied to the requests here; the loop below is their Python twin, and the tests run both in
+        lockstep."""
+        if self.native_plan:
+            return self._schedule_native()
         preempted: List[Request] = []
         finished: List[Request] = []
         while True:
@@ -203,6 +213,41 @@ class Scheduler:
             assert got, "pages were counted but could not be taken"
             toks = r.tokens[start:start + n]
             entries.append(PlanEntry(r, start, toks, samples=(start + n == len(r))))
+        return StepPlan(entries, preempted, finished)
+
+    def _schedule_native(self) -> StepPlan:
+        cache = self.cache
+        order = sorted(self.running, key=lambda r: r.admitted_at)
+        waiting = list(self.waiting)
+        events = cache.plan_step(self.max_tokens_per_step, self.max_model_len,
+                                 [r.id for r in order], [len(r) for r in order],
+                                 [r.id for r in waiting], [len(r) for r in waiting], [len(r.prompt) for r in waiting])
+        by_id = {r.id: r for r in order + waiting}
+        preempted: List[Request] = []
+        finished: List[Request] = []
+        entries: List[PlanEntry] = []
+        for kind, name, a, b in events:
+            r = by_id[name]
+            if kind == cache.EVENT_PREEMPT:
+                self.running.remove(r)
+                r.status = WAITING
+                r.num_preemptions += 1
+                self.counters["preemptions"] += 1
+                self.waiting.appendleft(r)
+                preempted.append(r)
+            elif kind == cache.EVENT_FINISH:
+                (self.running if b else self.waiting).remove(r)
+                r.status = FINISHED
+                r.finish_reason = a
+                finished.append(r)
+            elif kind == cache.EVENT_ADMIT:
+                self.waiting.remove(r)
+                r.status = RUNNING
+                r.admitted_at = self._admissions
+                self._admissions += 1
+                self.running.append(r)
+            else:                                   # EVENT_RUN: a tokens from position b
+                entries.append(PlanEntry(r, b, r.tokens[b:b + a], samples=(b + a == len(r))))
         return StepPlan(entries, preempted, finished)
 
     # ---------------------------------------------------------------- update
