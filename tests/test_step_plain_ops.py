@@ -53,3 +53,33 @@ def test_cut_modes_match_plain(plain_logits, name, mode):
     assert runner.cache.slots.num_free == 4
     if mode == "mixed":
         assert any(p.high_water == p.num_pages or p.high_water > p.num_pages // 2 for p in runner.cache.pools)
+
+
+@pytest.mark.parametrize("native", [True, False], ids=["native", "python"])
+def test_a_step_that_cannot_run_is_refused_without_side_effects(tmp_path, native):
+    """What the step function refuses, with the C++ host runtime and with its Python twin: a request that
+    is not live, one that comes twice, no tokens, beyond the longest sequence, a token id outside the
+    vocabulary, and more pages than are free -- and in every case nothing has been taken."""
+    from tffinfer_b200.engine import StepEntry, OutOfPages, RequestError
+    d = make_model_dir(tmp_path, "A")
+    ecfg = EngineConfig(dtype="float32", page_size=4, max_cache_tokens=24, max_live_requests=3, device="cpu",
+                        max_model_len=20, native_host=native)
+    runner = ModelRunner(d, ecfg, ops=CpuOps())
+    runner.add_request("a"); runner.add_request("b")
+    free = lambda: [p.num_free for p in runner.cache.pools]
+    before = free()
+    for entries, err, words in [
+            ([StepEntry("nobody", [1], [0])], RequestError, "not live"),
+            ([StepEntry("a", [1, 2], []), StepEntry("a", [3], [0])], RequestError, "twice"),
+            ([StepEntry("a", [], [])], RequestError, "no tokens"),
+            ([StepEntry("a", list(range(21)), [0])], RequestError, "maximum length"),
+            ([StepEntry("a", [1, 256], [0])], RequestError, "token id outside"),
+            ([StepEntry("a", [1, -2], [0])], RequestError, "token id outside"),
+            ([StepEntry("a", [1], [0], token_src=[0])], RequestError, "previous step"),
+            ([StepEntry("a", list(range(1, 17)), [0]), StepEntry("b", list(range(1, 14)), [0])], OutOfPages, "pages")]:
+        with pytest.raises(err, match=words):
+            runner.make_batch(entries)
+        assert free() == before and runner.num_tokens("a") == 0 and runner.num_tokens("b") == 0
+    # what fits still runs afterwards
+    logits = runner.step([StepEntry("a", list(range(1, 17)), [15]), StepEntry("b", [5, 6], [1])])
+    assert tuple(logits.shape) == (2, 256) and runner.num_tokens("a") == 16 and runner.num_tokens("b") == 2

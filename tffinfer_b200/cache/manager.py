@@ -123,6 +123,11 @@ class CacheManager:
                 for b in range(min(first, len(t))):
                     t[b] = NO_PAGE
 
+    def commit_step(self, reqs: Sequence[Hashable], counts: Sequence[int]) -> None:
+        """``counts[i]`` tokens of ``reqs[i]`` were written by one step."""
+        for r, n in zip(reqs, counts):
+            self.commit(r, n)
+
     def release(self, req: Hashable) -> None:
         """The request ended (finished, aborted or preempted): everything goes back."""
         rc = self.requests.pop(req)

@@ -44,6 +44,8 @@ def host_library():
         lib.tffh_count.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
         lib.tffh_plan_step.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, _i64p, _i32p,
                                        ctypes.c_int, _i64p, _i32p, _i32p, _i32p, ctypes.c_int]
+        lib.tffh_reserve_step.argtypes = [ctypes.c_void_p, ctypes.c_int, _i64p, _i32p, ctypes.c_int, _i32p]
+        lib.tffh_commit_step.argtypes = [ctypes.c_void_p, ctypes.c_int, _i64p, _i32p]
         lib.tffh_pack_step.restype = ctypes.c_int64
         lib.tffh_pack_step.argtypes = [ctypes.c_void_p, ctypes.c_int, _i64p, _i32p, _i32p, _i32p, _i32p, _i32p,
                                        ctypes.c_int, _i32p, _i32p, ctypes.c_int, _i32p, ctypes.c_int64, _i32p]
@@ -53,6 +55,15 @@ def host_library():
 
 def _p32(a: Optional[np.ndarray]):
     return a.ctypes.data_as(_i32p) if a is not None else None
+
+
+class StepArrays:
+    """The entries of a step as flat arrays (NativeCacheManager.gather_step)."""
+    __slots__ = ("n", "reqs", "q_lens", "tokens", "want_start", "want", "tok_src", "has_src")
+
+    def __init__(self, n, reqs, q_lens, tokens, want_start, want, tok_src, has_src):
+        self.n, self.reqs, self.q_lens, self.tokens = n, reqs, q_lens, tokens
+        self.want_start, self.want, self.tok_src, self.has_src = want_start, want, tok_src, has_src
 
 
 class _PoolView:
@@ -261,24 +272,22 @@ class NativeCacheManager:
             out.append((kind, name, self.REASONS[a] if kind == self.EVENT_FINISH else a, b))
         return out
 
-    # -------------------------------------------------------------- packing
-    def pack_step(self, entries, *, pad_requests: int = 0, widths: Optional[Sequence[int]] = None,
-                  dummy_pages: Optional[Sequence[int]] = None, dummy_slot: int = 0,
-                  out: Optional[np.ndarray] = None):
-        """engine.batch.pack_step with positions, slots and block tables taken from this manager: returns
-        (array, layout, info) of the same meaning."""
-        from ..engine.batch import BatchLayout
+    # ------------------------------------------------------ a whole step at once
+    def gather_step(self, entries) -> "StepArrays":
+        """The entries of a step as flat arrays (handles, token counts, token ids, wanted places, source rows):
+        gathered once, used by the checks, by reserve_step and by pack_step.  A request that is not live
+        gets the handle 0, which never is: the library then says which entry it was."""
         n = len(entries)
         if n == 0:
             raise ValueError("a step needs at least one request and every request at least one token")
-        reqs = np.fromiter((self._h_of(e.req) for e in entries), dtype=np.int64, count=n)
+        handle = self._handle
+        reqs = np.fromiter((handle.get(e.req, 0) for e in entries), dtype=np.int64, count=n)
         q_lens = np.fromiter((len(e.tokens) for e in entries), dtype=np.int32, count=n)
-        if (q_lens <= 0).any():
-            raise ValueError("a step needs at least one request and every request at least one token")
-        if int(q_lens.sum()) == n:
+        if int(q_lens.sum()) == n and int(q_lens.min()) == 1:
             tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=n).astype(np.int32)
         else:
-            tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries]).astype(np.int32)
+            tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries] +
+                                    [np.zeros(1, dtype=np.int64)]).astype(np.int32)[:int(q_lens.sum())]
         want_start = np.zeros(n + 1, dtype=np.int32)
         np.cumsum(np.fromiter((len(e.want) for e in entries), dtype=np.int32, count=n), out=want_start[1:])
         want = np.fromiter((int(w) for e in entries for w in e.want), dtype=np.int32, count=int(want_start[-1]))
@@ -289,6 +298,49 @@ class NativeCacheManager:
         if has_src:
             tok_src = np.concatenate([np.asarray(e.token_src, dtype=np.int32) if e.token_src is not None
                                       else np.full(len(e.tokens), -1, dtype=np.int32) for e in entries])
+        return StepArrays(n, reqs, q_lens, tokens, want_start, want, tok_src, has_src)
+
+    def reserve_step(self, arrays: "StepArrays", max_model_len: int = 0):
+        """Checks the step's requests and takes the pages all of them need, or none (tffh_reserve_step).
+        Returns (1, None) when taken, (0, (group, needed, free)) when the pages do not suffice, and
+        (code, index of the entry) for a request that is not live (-2), appears twice (-6), brings no
+        tokens (-1) or would grow beyond ``max_model_len`` (-7)."""
+        detail = np.zeros(3, dtype=np.int32)
+        st = self.lib.tffh_reserve_step(self._h, arrays.n, arrays.reqs.ctypes.data_as(_i64p), _p32(arrays.q_lens),
+                                        int(max_model_len), _p32(detail))
+        if st == 1:
+            return 1, None
+        if st == 0:
+            return 0, tuple(int(x) for x in detail)
+        if st == _ERR_ACCOUNTING:
+            self._raise(st)
+        return st, int(detail[0])
+
+    def commit_step(self, reqs: Sequence[Hashable], counts: Sequence[int]) -> None:
+        n = len(reqs)
+        if n == 0:
+            return
+        h = np.fromiter((self._h_of(r) for r in reqs), dtype=np.int64, count=n)
+        c = np.asarray(list(counts), dtype=np.int32)
+        st = self.lib.tffh_commit_step(self._h, n, h.ctypes.data_as(_i64p), _p32(c))
+        if st < 0:
+            self._raise(st)
+
+    # -------------------------------------------------------------- packing
+    def pack_step(self, entries, *, pad_requests: int = 0, widths: Optional[Sequence[int]] = None,
+                  dummy_pages: Optional[Sequence[int]] = None, dummy_slot: int = 0,
+                  out: Optional[np.ndarray] = None, arrays: Optional["StepArrays"] = None):
+        """engine.batch.pack_step with positions, slots and block tables taken from this manager: returns
+        (array, layout, info) of the same meaning.  ``arrays``: what gather_step made of the entries."""
+        from ..engine.batch import BatchLayout
+        if arrays is None:
+            arrays = self.gather_step(entries)
+        n, reqs, q_lens, tokens = arrays.n, arrays.reqs, arrays.q_lens, arrays.tokens
+        want_start, want, tok_src, has_src = arrays.want_start, arrays.want, arrays.tok_src, arrays.has_src
+        if (q_lens <= 0).any():
+            raise ValueError("a step needs at least one request and every request at least one token")
+        if (reqs == 0).any():
+            raise KeyError(entries[int(np.argmax(reqs == 0))].req)
         G = len(self.groups)
         w = np.asarray(list(widths) if widths is not None else [0] * G, dtype=np.int32)
         if w.shape[0] == 0:

@@ -487,3 +487,42 @@ TFFH_API int tffh_plan_step(void* cache, int budget_tokens, int max_model_len,
     }
     return n_events;
 }
+
+// ------------------------------------------------------------------------------- a whole step at once
+TFFH_API int tffh_reserve_step(void* cache, int n, const int64_t* reqs, const int* q_lens, int max_model_len,
+                               int* detail) {
+    Cache* c = as_cache(cache);
+    const int G = (int)c->pools.size();
+    std::vector<RequestCache*> rcs(n);
+    std::vector<int> total(G, 0), need(G);
+    for (int i = 0; i < n; ++i) {
+        detail[0] = i;
+        rcs[i] = c->find(reqs[i]);
+        if (!rcs[i]) return c->fail(TFFH_ERR_UNKNOWN, "request " + std::to_string(reqs[i]) + " is not live");
+        for (int j = 0; j < i; ++j)
+            if (reqs[j] == reqs[i]) return c->fail(TFFH_ERR_DUPLICATE, "a request appears twice in one step");
+        if (q_lens[i] <= 0) return c->fail(TFFH_ERR_ARGUMENT, "a request brings no tokens");
+        if (max_model_len > 0 && rcs[i]->num_tokens + q_lens[i] > max_model_len)
+            return c->fail(TFFH_ERR_TOO_LONG, "a request would exceed the maximum length");
+        c->pages_needed(*rcs[i], q_lens[i], need.data());
+        for (int g = 0; g < G; ++g) total[g] += need[g];
+    }
+    for (int g = 0; g < G; ++g)
+        if (total[g] > c->pools[g].num_free()) {            // all or nothing over the whole step
+            detail[0] = g; detail[1] = total[g]; detail[2] = c->pools[g].num_free();
+            return 0;
+        }
+    for (int i = 0; i < n; ++i) {
+        const int got = tffh_reserve(cache, reqs[i], q_lens[i]);
+        if (got <= 0) return got < 0 ? got : c->fail(TFFH_ERR_ACCOUNTING, "pages were counted but could not be taken");
+    }
+    return 1;
+}
+
+TFFH_API int tffh_commit_step(void* cache, int n, const int64_t* reqs, const int* counts) {
+    for (int i = 0; i < n; ++i) {
+        const int st = tffh_commit(cache, reqs[i], counts[i]);
+        if (st < 0) return st;
+    }
+    return 0;
+}

@@ -25,6 +25,8 @@ enum {
     TFFH_ERR_LIVE = -3,          // the request is live already
     TFFH_ERR_ACCOUNTING = -4,    // a page or slot freed twice, held twice, lost, or tokens committed beyond the reserved
     TFFH_ERR_TOO_SMALL = -5,     // the caller's buffer is too small
+    TFFH_ERR_DUPLICATE = -6,     // a request appears twice in one step
+    TFFH_ERR_TOO_LONG = -7,      // a request would grow beyond the longest sequence allowed
 };
 
 // ---- cache manager
@@ -47,6 +49,16 @@ TFFH_API int tffh_check(void* cache);                                 // 0 when 
 // what: 0 pages in all, 1 free pages, 2 most pages ever taken (group is the pool);
 //       3 free slots, 4 live requests (group ignored)
 TFFH_API int tffh_count(void* cache, int what, int group);
+
+// ---- a whole step at once
+// Checks the requests of a step (live, each once, at least one token, not beyond max_model_len when that is
+// > 0) and takes the pages that all of them need, in every group, or none at all.  Returns 1 when the pages
+// were taken; 0 when they do not suffice (detail: group, pages needed, pages free; nothing taken); a negative
+// error with detail[0] = the index of the request it is about.
+TFFH_API int tffh_reserve_step(void* cache, int n, const int64_t* reqs, const int* q_lens, int max_model_len,
+                               int* detail);
+// counts[i] tokens of request reqs[i] were written (tffh_commit for each).
+TFFH_API int tffh_commit_step(void* cache, int n, const int64_t* reqs, const int* counts);
 
 // ---- packing a step
 // Requests reqs[0..n) bring q_lens[i] tokens each (tokens: all of them, flat); want_start[i]..want_start[i+1]

@@ -168,6 +168,27 @@ class ModelRunner:
         """Checks the entries, takes the pages they need (all or nothing) and builds
         the device-side batch.  Raises OutOfPages without side effects.  Entries with
         ``token_src`` take token ids from ``prev_tokens`` (int32, on the device)."""
+        arrays = None
+        if hasattr(self.cache, "reserve_step"):
+            arrays = self._check_and_reserve_native(entries, prev_tokens)
+        else:
+            self._check_and_reserve(entries, prev_tokens)
+        if self._graph_eligible(entries):
+            batch = self._make_static_batch(entries, arrays)
+            if batch.tok_src is not None:
+                self.ops.gather_tokens(batch.token_ids, prev_tokens, batch.tok_src)
+            return batch
+        batch = packed_to_device(*self._pack(entries, arrays), self.device, pinned=self.device.type == "cuda")
+        if batch.tok_src is not None:
+            self.ops.gather_tokens(batch.token_ids, prev_tokens, batch.tok_src)
+        self.last_h2d_bytes = batch.token_ids.numel() * 0 + 4 * (
+            3 * batch.num_tokens + 4 * batch.num_requests + 1 + batch.num_logit_rows
+            + sum(t.numel() for t in batch.block_tables))
+        return batch
+
+    def _check_and_reserve(self, entries, prev_tokens) -> None:
+        """The checks of a step and its pages, all or nothing, entry by entry (the twin of
+        _check_and_reserve_native, used with the Python cache manager)."""
         seen = set()
         for e in entries:
             if not self.cache.is_live(e.req):
@@ -196,18 +217,33 @@ class ModelRunner:
         for e in entries:
             ok = self.cache.reserve(e.req, len(e.tokens))
             assert ok
-        if self._graph_eligible(entries):
-            batch = self._make_static_batch(entries)
-            if batch.tok_src is not None:
-                self.ops.gather_tokens(batch.token_ids, prev_tokens, batch.tok_src)
-            return batch
-        batch = packed_to_device(*self._pack(entries), self.device, pinned=self.device.type == "cuda")
-        if batch.tok_src is not None:
-            self.ops.gather_tokens(batch.token_ids, prev_tokens, batch.tok_src)
-        self.last_h2d_bytes = batch.token_ids.numel() * 0 + 4 * (
-            3 * batch.num_tokens + 4 * batch.num_requests + 1 + batch.num_logit_rows
-            + sum(t.numel() for t in batch.block_tables))
-        return batch
+
+    def _check_and_reserve_native(self, entries, prev_tokens):
+        """The same by the C++ host runtime: the entries are gathered into flat arrays once (they are packed
+        from the same arrays afterwards), token ids are checked on the array, and one call checks the
+        requests and takes the pages of the whole step or none."""
+        arrays = self.cache.gather_step(entries)
+        tok = arrays.tokens if arrays.tok_src is None else arrays.tokens[arrays.tok_src < 0]
+        if tok.size and (int(tok.min()) < 0 or int(tok.max()) >= self.desc.vocab_size):
+            for e in entries:
+                toks = e.tokens if e.token_src is None else [t for t, s in zip(e.tokens, e.token_src) if s < 0]
+                if toks and (min(toks) < 0 or max(toks) >= self.desc.vocab_size):
+                    raise RequestError(f"request {e.req!r}: token id outside [0, {self.desc.vocab_size})")
+        if arrays.has_src and prev_tokens is None:
+            e = next(e for e in entries if e.token_src is not None)
+            raise RequestError(f"request {e.req!r} takes tokens from a previous step, but none was given")
+        status, detail = self.cache.reserve_step(arrays, self.max_model_len)
+        if status == 1:
+            return arrays
+        if status == 0:
+            g, need, free = detail
+            raise OutOfPages(f"step needs {need} pages in cache group {g}, {free} are free")
+        req = entries[detail].req
+        raise RequestError({-2: f"request {req!r} is not live (add_request first)",
+                            -6: f"request {req!r} appears twice in one step",
+                            -1: f"request {req!r} brings no tokens",
+                            -7: f"request {req!r} would exceed the maximum length {self.max_model_len}",
+                            }.get(status, f"request {req!r}: the host runtime refused the step ({status})"))
 
     # ------------------------------------------------------------ CUDA graphs
     def _graph_eligible(self, entries) -> bool:
@@ -215,18 +251,18 @@ class ModelRunner:
                 and len(entries) <= self.graph_buckets[-1]
                 and all(len(e.tokens) == 1 and len(e.want) == 1 for e in entries))
 
-    def _pack(self, entries, **kw):
+    def _pack(self, entries, arrays=None, **kw):
         """The step's integer arrays in one host buffer: by the C++ host runtime, which holds the positions,
         slots and block tables itself, or by its Python twin from lists read out of the cache manager."""
         native = getattr(self.cache, "pack_step", None)
         if native is not None:
-            return native(entries, **kw)
+            return native(entries, arrays=arrays, **kw)
         starts = [self.cache.num_tokens(e.req) for e in entries]
         slots = [self.cache.slot_of(e.req) for e in entries]
         tables = [[self.cache.block_table(e.req, g) for e in entries] for g in range(len(self.groups))]
         return pack_step(entries, starts, slots, tables, **kw)
 
-    def _make_static_batch(self, entries) -> StepBatch:
+    def _make_static_batch(self, entries, arrays=None) -> StepBatch:
         """Decode-only steps use device arrays of fixed address and size, one set per
         batch-size bucket, so that the step can be replayed as a CUDA graph.  A graph fixes the
         geometry of its launches, and how the attention shares out the key range depends on how
@@ -242,7 +278,7 @@ class ModelRunner:
             self._graphs[bucket] = st
         if st.get("copied") is not None:
             st["copied"].synchronize()              # the last copy out of the staging buffer has finished
-        arr, layout, info = self._pack(entries, pad_requests=bucket, widths=st["layout"].widths,
+        arr, layout, info = self._pack(entries, arrays, pad_requests=bucket, widths=st["layout"].widths,
                                        dummy_pages=self.dummy_pages, dummy_slot=self.dummy_slot,
                                        out=st["host"].numpy())
         st["dev"].copy_(st["host"], non_blocking=True)

@@ -57,6 +57,15 @@ class Request:
     def __len__(self) -> int:
         return len(self.prompt) + len(self.generated)
 
+    def token_slice(self, start: int, n: int) -> List[int]:
+        """tokens[start:start + n] without joining the prompt and the generated tokens first."""
+        lp = len(self.prompt)
+        if start >= lp:
+            return self.generated[start - lp:start - lp + n]
+        if start + n <= lp:
+            return self.prompt[start:start + n]
+        return self.prompt[start:] + self.generated[:start + n - lp]
+
 
 @dataclass
 class PlanEntry:
@@ -211,7 +220,7 @@ class Scheduler:
             start = self.cache.num_tokens(r.id)
             got = self.cache.reserve(r.id, n)
             assert got, "pages were counted but could not be taken"
-            toks = r.tokens[start:start + n]
+            toks = r.token_slice(start, n)
             entries.append(PlanEntry(r, start, toks, samples=(start + n == len(r))))
         return StepPlan(entries, preempted, finished)
 
@@ -247,7 +256,7 @@ class Scheduler:
                 self._admissions += 1
                 self.running.append(r)
             else:                                   # EVENT_RUN: a tokens from position b
-                entries.append(PlanEntry(r, b, r.tokens[b:b + a], samples=(b + a == len(r))))
+                entries.append(PlanEntry(r, b, r.token_slice(b, a), samples=(b + a == len(r))))
         return StepPlan(entries, preempted, finished)
 
     # ---------------------------------------------------------------- update
@@ -256,9 +265,9 @@ class Scheduler:
         draws a token gets a PENDING one (the value arrives with :meth:`resolve`); requests that end by
         count end now and give their pages back -- whoever takes those pages runs later on the device."""
         self.counters["steps"] += 1
+        self.cache.commit_step([e.request.id for e in plan.entries], [len(e.tokens) for e in plan.entries])
         for e in plan.entries:
             r = e.request
-            self.cache.commit(r.id, len(e.tokens))
             if len(e.tokens) == 1 and r.generated and e.start >= len(r.prompt):
                 self.counters["decode_tokens"] += 1
             else:
