@@ -21,6 +21,11 @@ class CpuOps:
     def projection_buffer(self, rows, width, device, act_dtype):
         return torch.empty((rows, width), dtype=torch.float32, device=device)
 
+    def reset_state_slots(self, state, slots, pos_start):
+        for slot, p in zip(slots.tolist(), pos_start.tolist()):
+            if p == 0:
+                state[slot].zero_()
+
     def gather_tokens(self, token_ids, drawn, src):
         m = src >= 0
         token_ids[m] = drawn[src[m].long()]

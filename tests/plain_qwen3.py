@@ -4,11 +4,15 @@ config.json itself, reads the weights with the ``safetensors`` library, and work
 one floating type (float64 by default, so that it is an oracle for the 32-bit engine).
 
 It rests on the formulas of NKKdev/TFFinfer, cited at each function by the file's path
-inside that project.  The reference's own model code cannot be compiled or imported
-on a machine without its dependencies (glog, Taskflow, libdivide are fetched from the
-network by its CMakeLists.txt:28-78) and it has no CPU implementation of the model
-(only embedding and IO run on the CPU), so there is no golden output of the
-reference itself under tests/golden/.
+inside that project.  The reference as a whole cannot be built or imported offline (glog,
+Taskflow and libdivide are fetched from the network by its CMakeLists.txt:28-78) and it has no
+CPU implementation of the model, but its device code for the norm, the rotation table, the
+SiLU product and the rotating causal attention of 32 heads on 8 of 128 depends on nothing of
+the project: tests/golden/make_reference_golden.py cut those kernels out of a checkout at run
+time and ran them on a B200, tests/golden/reference_outputs.npz keeps what they computed, and
+tests/test_reference_golden.py holds ``rms_norm``, ``rope_angles``, ``rope_rotate_half``,
+``silu`` and ``causal_attention`` of this file against it.  The embedding, the projections,
+the order of the parts in a layer and the sampling rest on the cited formulas alone.
 """
 from __future__ import annotations
 

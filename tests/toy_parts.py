@@ -32,19 +32,25 @@ class RunningMeanMixer(Mixer):
         self.w = tensors["mix.weight"]
 
     def forward(self, h, ctx, residual):
+        # Everything stays on the device and no shape depends on the batch's values, so that a decode
+        # step with this mixer can be captured in a CUDA graph: the running sum of each request's rows is
+        # the running sum over all rows minus what the rows ahead of the request add up to.
         b = ctx.batch
         H = self.hidden_size
-        q_start = b.q_start.tolist()
-        slots = b.slots.tolist()
-        mean = torch.empty(h.shape, dtype=torch.float32, device=h.device)
-        for i in range(b.num_requests):
-            rows = slice(q_start[i], q_start[i + 1])
-            st = ctx.state[slots[i]]
-            csum = torch.cumsum(h[rows].float(), 0) + st[:H]
-            cnt = st[H] + torch.arange(1, rows.stop - rows.start + 1, device=h.device, dtype=torch.float32)
-            mean[rows] = csum / cnt[:, None]
-            st[:H] = csum[-1]
-            st[H] = cnt[-1]
+        D = torch.float64
+        req = b.tok_req.long()
+        first = b.q_start[:-1].long()                    # first row of each request
+        last = b.q_start[1:].long() - 1                  # last row of each request
+        slots = b.slots.long()
+        st = ctx.state.index_select(0, slots).to(D)      # [B, H + 1]: running sum, count
+        total = torch.cumsum(h.to(D), 0)
+        ahead = total.index_select(0, first) - h.to(D).index_select(0, first)
+        csum = total - ahead.index_select(0, req) + st[:, :H].index_select(0, req)
+        rows = torch.arange(h.shape[0], device=h.device)
+        cnt = st[:, H].index_select(0, req) + (rows - first.index_select(0, req) + 1).to(D)
+        mean = (csum / cnt[:, None]).to(torch.float32)
+        new_state = torch.cat([csum.index_select(0, last), cnt.index_select(0, last)[:, None]], dim=1)
+        ctx.state.index_copy_(0, slots, new_state.to(ctx.state.dtype))
         out = torch.empty_like(residual)
         ctx.ops.gemm(mean.to(h.dtype), self.w, out)
         residual += out
@@ -69,14 +75,13 @@ class Top1Experts(FeedForward):
         self.experts = [tensors[f"experts.{e}.weight"] for e in range(self.num_experts)]
 
     def forward(self, h, ctx, residual):
+        # every expert runs on every row and the router's choice picks one result: wasteful, and free of
+        # shapes that depend on the data (a toy, and a decode step with it can be captured in a CUDA graph)
         choice = (h.float() @ self.router.t()).argmax(-1)
         for e in range(self.num_experts):
-            idx = (choice == e).nonzero().flatten()
-            if idx.numel() == 0:
-                continue
-            out = torch.empty((idx.numel(), self.hidden_size), dtype=torch.float32, device=h.device)
-            ctx.ops.gemm(h[idx].contiguous(), self.experts[e], out)
-            residual[idx] += out
+            out = torch.empty((h.shape[0], self.hidden_size), dtype=torch.float32, device=h.device)
+            ctx.ops.gemm(h, self.experts[e], out)
+            residual += torch.where((choice == e)[:, None], out, torch.zeros_like(out))
         return residual
 
 
