@@ -142,10 +142,36 @@ def trace_mixed(reqs: Dict[str, List[int]], prompt_lens: Sequence[int], max_live
     return steps
 
 
-def run_trace(runner: ModelRunner, reqs: Dict[str, List[int]], steps) -> Dict[str, torch.Tensor]:
+def run_trace(runner: ModelRunner, reqs: Dict[str, List[int]], steps, poison: bool = False,
+              stats: Dict[str, int] = None) -> Dict[str, torch.Tensor]:
     """Feeds the steps through the runner's step function, asking for the logits of every
-    token; returns per request a tensor [len, vocab] (float32, on the CPU)."""
+    token; returns per request a tensor [len, vocab] (float32, on the CPU).
+
+    ``poison``: every page that a step or the end of a request gives back is filled with NaN before the
+    next step runs, so that a read of a page the request no longer holds shows in the logits.
+    ``stats``: receives ``pages_reused``, the number of times a page id was handed to a request after
+    another request had held it."""
     got = {r: [None] * len(t) for r, t in reqs.items()}
+    groups = range(len(runner.kv_caches))
+    held = {}                                   # (request, group) -> pages it holds
+    past_holders = [dict() for _ in groups]     # group -> page -> requests that held it
+    reused = 0
+
+    def account(r, released: bool):
+        nonlocal reused
+        for g in groups:
+            now = set() if released else {p for p in runner.cache.block_table(r, g) if p >= 0}
+            before = held.get((r, g), set())
+            for p in now - before:
+                holders = past_holders[g].setdefault(p, set())
+                if holders - {r}:
+                    reused += 1
+                holders.add(r)
+            gone = sorted(before - now)
+            if poison and gone:
+                runner.kv_caches[g][torch.tensor(gone, device=runner.kv_caches[g].device)] = float("nan")
+            held[(r, g)] = now
+
     for entries, end in steps:
         ents = []
         for r, start, n in entries:
@@ -161,10 +187,22 @@ def run_trace(runner: ModelRunner, reqs: Dict[str, List[int]], steps) -> Dict[st
                 assert got[r][start + i] is None
                 got[r][start + i] = logits[row]
                 row += 1
+            account(r, released=False)
         for r in end:
             runner.finish_request(r)
+            account(r, released=True)
         runner.cache.check()
+    if stats is not None:
+        stats["pages_reused"] = reused
     return {r: torch.stack(v) for r, v in got.items()}
+
+
+def steps_to_jsonl(reqs: Dict[str, List[int]], steps) -> List[str]:
+    """The steps as the lines bin/trace_run reads, the logits of every token wanted."""
+    import json
+    return [json.dumps({"step": i, "entries": [{"id": r, "tokens": reqs[r][start:start + n], "want": list(range(n))}
+                                               for r, start, n in entries], "end": list(end)})
+            for i, (entries, end) in enumerate(steps)]
 
 
 def max_rel_err(got: torch.Tensor, want: torch.Tensor) -> float:

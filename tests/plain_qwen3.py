@@ -181,6 +181,16 @@ def sample_greedy(logits: torch.Tensor) -> int:
     return int((logits == logits.max()).nonzero()[0].item())
 
 
+def repetition_penalty(logits: torch.Tensor, seen: Sequence[int], penalty: float) -> torch.Tensor:
+    """Once for every distinct token of the prompt and the output so far: a positive logit is divided by
+    the penalty, any other multiplied by it (src/core/sampler/LLMSampler.cpp:21-34)."""
+    out = logits.clone()
+    for t in set(int(x) for x in seen):
+        if 0 <= t < out.numel():
+            out[t] = out[t] / penalty if out[t] > 0 else out[t] * penalty
+    return out
+
+
 def sample_temperature(logits: torch.Tensor, temperature: float, u: float, top_k: int = 0,
                        top_p: float = 1.0, min_p: float = 0.0) -> int:
     """logits / T (LLMSampler.cpp:36-41), softmax, optional filters named by SamplingConfig

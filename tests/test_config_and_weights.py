@@ -184,3 +184,66 @@ def test_safetensors_reader_rejects_broken_files(tmp_path):
     write_safetensors(str(p), {"a": torch.arange(6, dtype=torch.int32).view(2, 3)})
     f = SafetensorsFile(str(p))
     assert f.tensor("a").tolist() == [[0, 1, 2], [3, 4, 5]]
+
+
+def _write_sharded(tmp_path, cfg, sd, stored_twice=()):
+    """A model folder whose tensors are spread over three shard files named by model.safetensors.index.json
+    (the layout of checkpoints too large for one file)."""
+    d = str(tmp_path / ("sharded_twice" if stored_twice else "sharded"))
+    os.makedirs(d)
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(cfg.to_json_dict(), f)
+    names = sorted(sd)
+    files = [f"model-0000{i + 1}-of-00003.safetensors" for i in range(3)]
+    parts = [dict(), dict(), dict()]
+    weight_map = {}
+    for i, n in enumerate(names):
+        parts[i % 3][n] = sd[n]
+        weight_map[n] = files[i % 3]
+    for n in stored_twice:
+        other = (files.index(weight_map[n]) + 1) % 3
+        parts[other][n] = sd[n]
+    for fn, part in zip(files, parts):
+        write_safetensors(os.path.join(d, fn), part)
+    with open(os.path.join(d, "model.safetensors.index.json"), "w") as f:
+        json.dump({"metadata": {}, "weight_map": weight_map}, f)
+    return d
+
+
+def test_a_sharded_folder_loads_like_a_single_file_and_a_tensor_stored_twice_is_an_error(tmp_path):
+    cfg = tiny_config("B")
+    sd = random_state_dict(cfg, 3)
+    model = Model(get_architecture(cfg.architecture).describe(cfg))
+    expected = model.expected_tensors()
+    d = _write_sharded(tmp_path, cfg, sd)
+    held = load_model_weights(d, expected, torch.bfloat16, "cpu")
+    assert sorted(held) == sorted(sd)
+    for n, t in sd.items():
+        assert torch.equal(held[n].float(), t.float()), n
+    # the whole engine from the sharded folder gives the single-file folder's logits
+    from cpu_ops import CpuOps
+    from tffinfer_b200.engine import ModelRunner, StepEntry
+    single = make_model_dir(tmp_path, "B", seed=3)
+    logits = []
+    for folder in (d, single):
+        r = ModelRunner(folder, EngineConfig(dtype="float32", page_size=8, max_cache_tokens=64, device="cpu"), ops=CpuOps())
+        r.add_request("x")
+        logits.append(r.step([StepEntry("x", [5, 17, 3, 200, 41], [4])]))
+    assert torch.equal(logits[0], logits[1])
+    # the same tensor in two shards: one error that names it, beside whatever else is wrong
+    twice = ["model.layers.1.mlp.down_proj.weight", "model.norm.weight"]
+    sd2 = dict(sd)
+    del sd2["model.layers.0.input_layernorm.weight"]
+    d2 = _write_sharded(tmp_path, cfg, sd2, stored_twice=twice)
+    with pytest.raises(WeightError) as ei:
+        load_model_weights(d2, expected, torch.bfloat16, "cpu")
+    assert ei.value.duplicates == sorted(twice)
+    assert ei.value.missing == ["model.layers.0.input_layernorm.weight"]
+    assert "more than one file" in str(ei.value)
+    # an index that names no file is refused
+    from tffinfer_b200.weights import SafetensorsError
+    empty = tmp_path / "empty_index"
+    empty.mkdir()
+    (empty / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {}}))
+    with pytest.raises(SafetensorsError):
+        load_model_weights(str(empty), expected, torch.bfloat16, "cpu")

@@ -64,3 +64,23 @@ def test_full_width_layers_match_plain(wide, mode, dtype):
         bad = first_bad(got[r], want[r], TOL[dtype])
         assert bad is None, (f"{mode}/{dtype}/{r}: first wrong position {bad[0]} (rel err {bad[1]:.3e}) "
                              f"of {len(reqs[r])}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_full_width_decode_steps_replayed_as_cuda_graphs_match_plain(wide, dtype):
+    """The decode path the benchmark measures (device arrays of fixed size, CUDA-graph replay, split keys)
+    at the full layer widths: every prompt in one step, then the three requests decode together."""
+    d, reqs, want = wide
+    pool = sum(-(-len(t) // PAGE) * PAGE for t in reqs.values())
+    runner = ModelRunner(d, EngineConfig(dtype=dtype, page_size=PAGE, max_cache_tokens=pool, max_live_requests=4,
+                                         use_cuda_graphs=True))
+    for c in runner.kv_caches:
+        c.fill_(float("nan"))
+    steps = [([(r, 0, n)], []) for r, n in zip(reqs, PROMPTS)]
+    for k in range(DECODED):
+        steps.append(([(r, n + k, 1) for r, n in zip(reqs, PROMPTS)], list(reqs) if k == DECODED - 1 else []))
+    got = run_trace(runner, reqs, steps, poison=True)
+    assert any(st["graphs"] for st in runner._graphs.values())
+    for r in reqs:
+        bad = first_bad(got[r], want[r], TOL[dtype])
+        assert bad is None, f"{dtype}/{r}: first wrong position {bad[0]} (rel err {bad[1]:.3e}) of {len(reqs[r])}"

@@ -515,6 +515,73 @@ def test_window_edge_is_exact(ops):
     assert float(out.max()) <= 3.0 + 1e-4 and float(out.max()) > 2.9
 
 
+WINDOW_EDGE_CASES = [
+    # nq, nkv, d, page, new, old, window, splits
+    (8, 2, 128, 16, 1, 100, 48, 1),      # decode: first key of the window (53) in the middle of a page
+    (8, 2, 128, 16, 1, 100, 48, 4),      # the same with the key range shared out
+    (8, 2, 128, 16, 1, 111, 48, 1),      # first key of the window (64) on a 64-key block boundary
+    (8, 2, 128, 16, 1, 111, 48, 3),
+    (4, 4, 64, 8, 1, 130, 40, 2),        # heads of 64, pages of 8
+    (8, 2, 128, 16, 2, 100, 48, 1),      # a two-token portion: the rows of a tile have different first keys
+    (8, 2, 128, 16, 140, 60, 48, 1),     # a portion of prompt size (the tcgen05 kernel): every row its own edge
+    (4, 2, 64, 16, 150, 37, 40, 1),
+    (16, 2, 128, 16, 3, 200, 100, None),  # eight heads a group, splits chosen by the library
+]
+
+
+@pytest.mark.parametrize("case", WINDOW_EDGE_CASES)
+def test_window_edge_is_exact_in_the_bf16_kernels(ops, case):
+    """Queries and keys are built so that, for EVERY query row at position p, the key at p - w (just outside
+    the window) would take all the weight if it were seen (score 30 against 0), and the key at p - w + 1 (the
+    first one inside) takes most of it (score 8): a kernel that is off by one at either side of the edge
+    returns another key's value, far outside the tolerance.  Pages that the window of the first row has
+    passed are given back (-1 in the block table)."""
+    nq, nkv, d, page, new, old, w, splits = case
+    dt = torch.bfloat16
+    assert w < d
+    entries, tables, cache, qkv = _paged_case(nq, nkv, d, page, [new], [old], w, dt, seed=130, layers=2)
+    scale = 1 / math.sqrt(d)
+    total = old + new
+    cache[:, 1, 0] = 0
+    for j in range(total):                                     # key j: one unit in dimension j mod d
+        cache[tables[0][j // page], 1, 0, :, j % page, j % d] = 1.0
+    q = torch.zeros(new, nq, d)
+    for r in range(new):
+        pos = old + r
+        q[r, :, (pos - w) % d] = 30.0 / scale
+        q[r, :, (pos - w + 1) % d] = 8.0 / scale
+    q = q.to(dt).view(new, nq * d)
+    first_needed = max(0, old - w + 1) // page
+    tables[0] = [-1] * first_needed + tables[0][first_needed:]
+    # what the released pages held is poison now
+    cache = cache.clone()
+    gone = torch.ones(cache.shape[0], dtype=torch.bool)
+    gone[torch.tensor([pg for pg in tables[0] if pg >= 0])] = False
+    cache[gone] = float("nan")
+    bc = build_step_batch(entries, [old], [0], [tables], "cpu")
+    bg = build_step_batch(entries, [old], [0], [tables], DEV)
+    want = torch.empty(new, nq * d, dtype=dt)
+    CpuOps().attention(q, bc, bc.block_tables[0], cache, 1, page, want, nq, nkv, d, scale, w)
+    assert torch.isfinite(want).all()
+    # the plain result is, to 2 %, the value of the first key inside the window: the construction bites
+    for r in (0, new - 1):
+        j = old + r - w + 1
+        if j < 0:
+            continue                                           # the window of this row starts before the sequence
+        v = cache[tables[0][j // page], 1, 1, :, j % page].float()              # [nkv, d]
+        got = want[r].float().view(nq, d)
+        assert float((got - v.repeat_interleave(nq // nkv, 0)).abs().max()) < 0.05 * float(v.abs().max()) + 0.05
+    out = torch.full((new, nq * d), float("nan"), dtype=dt, device=DEV)
+    if splits is None:
+        ops.attention(q.to(DEV), bg, bg.block_tables[0], cache.to(DEV), 1, page, out, nq, nkv, d, scale, w)
+    else:
+        ops.attention_bf16(q.to(DEV), bg, bg.block_tables[0], cache.to(DEV), 1, page, out, nq, nkv, d, scale, w,
+                           num_splits=splits)
+    ops.check_errors()
+    assert torch.isfinite(out).all()
+    assert rel_err(out, want) < 1e-2
+
+
 @pytest.mark.parametrize("R,V", [(1, 100), (5, 311), (3, 151936), (64, 4097)])
 def test_argmax_first_maximum(ops, R, V):
     logits = g((R, V), torch.float32, 60)

@@ -36,11 +36,15 @@ def test_key_split_follows_the_effective_number_of_requests():
     assert effective_requests([2048] * 8) == 8.0
     assert effective_requests([]) == 1.0
     assert abs(effective_requests([4000, 10, 10, 10]) - 1.0075) < 1e-9
-    splits = lambda n: CudaKernels.attention_splits(CudaKernels, n, 1, 32, 8)
+    from types import SimpleNamespace
+    planner = SimpleNamespace(NUM_SMS=148)         # the planner reads the SM count from the device; a B200 has 148
+    splits = lambda n: CudaKernels.attention_splits(planner, n, 1, 32, 8)
     assert [splits(n) for n in (1, 2, 4, 8, 16, 24, 32, 64)] == [16, 16, 9, 4, 2, 1, 1, 1]
     # 26 requests, one of them long: cut as 4 equal ones would be, not as 32
     assert splits(effective_requests([4000] + [500] * 25)) == splits(4.2) == splits(4) == 9
     assert splits(20) == splits(16) and splits(23) == splits(32)
     assert CudaKernels.key_split_class([600, 37, 580, 5, 610, 90]) == 4 and CudaKernels.key_split_class([9] * 24) == 32
     # many tokens a request (portions): never cut
-    assert CudaKernels.attention_splits(CudaKernels, 1, 64, 32, 8) == 1
+    assert CudaKernels.attention_splits(planner, 1, 64, 32, 8) == 1
+    # on a part with fewer SMs the same batch is cut into fewer shares
+    assert CudaKernels.attention_splits(SimpleNamespace(NUM_SMS=74), 4, 1, 32, 8) == 4

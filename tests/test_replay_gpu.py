@@ -50,13 +50,16 @@ def test_cut_modes_match_plain(plain_logits, name, mode, dtype):
     # poison the cache: a read of a slot that was never written shows up as NaN
     for c in runner.kv_caches:
         c.fill_(float("nan"))
-    got = run_trace(runner, reqs, steps)
+    stats = {}
+    got = run_trace(runner, reqs, steps, poison=True, stats=stats)
     for r in reqs:
         bad = first_bad(got[r], want[r], TOL[dtype])
         assert bad is None, (f"{name}/{mode}/{dtype}/{r}: first wrong position {bad[0]} "
                              f"(rel err {bad[1]:.3e}) of {len(reqs[r])}")
         assert torch.isfinite(got[r]).all()
     assert all(p.num_free == p.num_pages for p in runner.cache.pools)
+    if mode == "mixed":
+        assert stats["pages_reused"] > 0, "the pool was meant to be so small that pages are used again"
 
 
 @pytest.mark.parametrize("name", ["B", "D"])
@@ -118,3 +121,71 @@ def test_first_tokens_of_a_sequence(plain_logits, name, dtype):
     for r in names:
         bad = first_bad(got[r], want[r][:len(some[r])], TOL[dtype])
         assert bad is None, f"{name}/{dtype}/{r}: first wrong position {bad[0]} (rel err {bad[1]:.3e})"
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+def test_float32_logits_are_the_same_bits_however_the_requests_are_cut(plain_logits, name):
+    """In the 32-bit mode every output element is summed in an order that depends on its own row alone
+    (products in k order, norms and softmax per row, keys walked in blocks aligned to absolute positions),
+    so the four cuts must agree to the last bit, not merely within rounding."""
+    d, reqs, _ = plain_logits[name]
+    got = {}
+    for mode in ("whole", "tail", "portions", "mixed"):
+        pool, steps = _steps(name, mode, reqs)
+        runner = ModelRunner(d, EngineConfig(dtype="float32", page_size=PAGE_SIZE[name], max_cache_tokens=pool,
+                                             max_live_requests=4, use_cuda_graphs=(mode == "tail")))
+        got[mode] = run_trace(runner, reqs, steps)
+    for mode in ("tail", "portions", "mixed"):
+        for r in reqs:
+            same = (got[mode][r] == got["whole"][r]).all(dim=-1)
+            assert bool(same.all()), (f"{name}/{mode}/{r}: position {int((~same).nonzero()[0])} differs from the whole "
+                                      f"prompt by {float((got[mode][r] - got['whole'][r]).abs().max()):.3e}")
+
+
+def _trace_decode_together(reqs, prompt_lens, stagger: int = 5):
+    """Each prompt in a step of its own, then all requests decode together, one token each a step; request i
+    has ``stagger * i`` more of its tokens in its prompt step, so the requests end at different times and the
+    batch shrinks from all of them to one."""
+    steps, at = [], {}
+    names = list(reqs)
+    for i, (r, n) in enumerate(zip(names, prompt_lens)):
+        first = min(len(reqs[r]) - 1, n + stagger * i)
+        steps.append(([(r, 0, first)], []))
+        at[r] = first
+    while at:
+        entries = [(r, p, 1) for r, p in at.items()]
+        end = [r for r, p in at.items() if p + 1 == len(reqs[r])]
+        steps.append((entries, end))
+        at = {r: p + 1 for r, p in at.items() if r not in end}
+    return steps
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+def test_decode_steps_replayed_as_cuda_graphs_match_plain(plain_logits, name, dtype):
+    """The path generation takes by default: decode-only steps run from device arrays of fixed size (three
+    requests in a bucket of four, the spare row writing to the spare page), captured once per bucket and
+    class of how unequal the contexts are, and replayed.  Logits of every position against the plain
+    implementation, as in the eager cuts."""
+    d, reqs, want = plain_logits[name]
+    ps = PAGE_SIZE[name]
+    pool = sum(-(-len(t) // ps) * ps for t in reqs.values())
+    runner = ModelRunner(d, EngineConfig(dtype=dtype, page_size=ps, max_cache_tokens=pool, max_live_requests=4,
+                                         use_cuda_graphs=True))
+    for c in runner.kv_caches:
+        c.fill_(float("nan"))
+    steps = _trace_decode_together(reqs, PROMPT_LENS[name])
+    got = run_trace(runner, reqs, steps, poison=True)
+    for r in reqs:
+        bad = first_bad(got[r], want[r], TOL[dtype])
+        assert bad is None, f"{name}/{dtype}/{r}: first wrong position {bad[0]} (rel err {bad[1]:.3e})"
+    buckets = {b: sorted(st["graphs"]) for b, st in runner._graphs.items() if st["graphs"]}
+    assert len(buckets) >= 2, f"the batch was meant to shrink through several buckets: {buckets}"
+    assert 4 in buckets and 3 not in buckets, f"three requests run in the bucket of four, one row padded: {buckets}"
+    # the tail cut again, each decoded token a replay of the one-request graph
+    runner2 = ModelRunner(d, EngineConfig(dtype=dtype, page_size=ps, max_cache_tokens=pool, max_live_requests=4,
+                                          use_cuda_graphs=True))
+    got = run_trace(runner2, reqs, trace_tail_decode(reqs))
+    for r in reqs:
+        bad = first_bad(got[r], want[r], TOL[dtype])
+        assert bad is None, f"{name}/{dtype}/{r} (tail): first wrong position {bad[0]} (rel err {bad[1]:.3e})"

@@ -45,10 +45,13 @@ def test_cut_modes_match_plain(plain_logits, name, mode):
         pool = longest
         steps = {"whole": trace_whole, "tail": trace_tail_decode, "portions": trace_portions}[mode](reqs)
     runner = _runner(d, name, pool)
-    got = run_trace(runner, reqs, steps)
+    stats = {}
+    got = run_trace(runner, reqs, steps, poison=True, stats=stats)
     for r in reqs:
         err = max_rel_err(got[r], want[r])
         assert err < TOL, f"{name}/{mode}/{r}: rel err {err:.3e}"
+    if mode == "mixed":
+        assert stats["pages_reused"] > 0, "the pool was meant to be so small that pages are used again"
     assert all(p.num_free == p.num_pages for p in runner.cache.pools)
     assert runner.cache.slots.num_free == 4
     if mode == "mixed":

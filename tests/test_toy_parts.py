@@ -53,3 +53,64 @@ def test_toy_architecture_steps_on_the_gpu(tmp_path):
     runner = ModelRunner(d, EngineConfig(dtype="float32", page_size=4, max_cache_tokens=96, max_live_requests=4,
                                          use_cuda_graphs=False))
     _check(runner, reqs, want, 5e-5)
+
+
+# ------------------------------------------------------------------ generation with state of fixed size
+def _follows_toy_plain(w, cfg, prompt, generated, slack):
+    toks = list(prompt)
+    for t in generated:
+        row = toy_plain_logits(toks, w, cfg)[-1]
+        gap = float(row.max() - row[t]) / float(row.abs().max())
+        if gap > slack:
+            return False
+        toks.append(t)
+    return True
+
+
+def _generate_case(tmp_path):
+    register_toy()
+    cfg = ToyConfig(architecture="ToyStateLM")
+    d = write_random_model(str(tmp_path / "toygen"), cfg, seed=9, store_dtype="float32")
+    from safetensors.torch import load_file
+    w = load_file(os.path.join(d, "model.safetensors"))
+    rng = random.Random(2)
+    prompts = [[rng.randrange(cfg.vocab_size) for _ in range(n)] for n in (5, 23, 17, 9, 14, 3)]
+    return d, cfg, w, prompts
+
+
+def _check_generation(eng, cfg, w, prompts, slack):
+    """Six requests on four state slots and a pool of 48 tokens: slots are handed on from finished
+    requests to new ones, and requests give way and are recomputed from position 0.  Each time the
+    mixer's state must start from zero, although nobody calls ModelRunner.add_request here."""
+    got = eng.generate(prompts, max_new_tokens=12)
+    assert eng.scheduler.counters["preemptions"] > 0
+    for p, g in zip(prompts, got):
+        assert len(g) == 12 and _follows_toy_plain(w, cfg, p, g, slack), (p, g)
+    eng.runner.cache.check()
+    assert eng.runner.cache.slots.num_free == 4
+
+
+@pytest.mark.parametrize("native", [True, False], ids=["native", "python"])
+def test_a_mixer_with_state_generates_through_the_engine_on_cpu_twins(tmp_path, native):
+    from cpu_ops import CpuOps
+    from tffinfer_b200.engine import Engine
+    d, cfg, w, prompts = _generate_case(tmp_path)
+    ecfg = EngineConfig(dtype="float32", page_size=4, max_cache_tokens=48, max_live_requests=4,
+                        max_tokens_per_step=6, device="cpu", native_host=native)
+    _check_generation(Engine(runner=ModelRunner(d, ecfg, ops=CpuOps())), cfg, w, prompts, 1e-5)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("graphs", [True, False], ids=["graphs", "eager"])
+def test_a_mixer_with_state_generates_through_the_engine_on_the_gpu(tmp_path, graphs):
+    """With the engine's defaults: decode-only steps are captured and replayed as CUDA graphs, and the step
+    that is captured must advance the state once, not twice."""
+    from tffinfer_b200.engine import Engine
+    d, cfg, w, prompts = _generate_case(tmp_path)
+    ecfg = EngineConfig(dtype="float32", page_size=4, max_cache_tokens=48, max_live_requests=4,
+                        max_tokens_per_step=6, use_cuda_graphs=graphs)
+    eng = Engine(d, ecfg)
+    _check_generation(eng, cfg, w, prompts, 1e-5)
+    if graphs:
+        assert any(st["graphs"] for st in eng.runner._graphs.values()), "no decode step was replayed as a graph"
+    eng.runner.ops.check_errors()

@@ -505,15 +505,35 @@ float* g_noalloc_ptr[kMaxDevices] = {nullptr};
 std::mutex g_noalloc_mu;
 }  // namespace
 
+// Bytes of the library's scratch array that a call would use, in 64-bit arithmetic throughout (the
+// row count tokens * nq of a large batch does not fit an int): 0 when num_splits == 1, -1 when a count is
+// not positive or the product does not fit 62 bits.  A pure function of its arguments; launches nothing.
+long long tff_attention_bf16_noalloc_bytes(long long num_tokens, long long nq, long long num_splits, long long d) {
+    if (num_tokens <= 0 || nq <= 0 || num_splits < 1 || d <= 0) return -1;
+    if (num_splits == 1) return 0;
+    const long long limit = 1LL << 62;
+    long long v = num_tokens;
+    const long long factors[4] = {nq, num_splits, d + 2, 4};
+    for (long long f : factors) {
+        if (v > limit / f) return -1;
+        v *= f;
+    }
+    return v;
+}
+
 int tff_attention_bf16_noalloc(
     const void* q, const int* q_start, const int* pos_start, const int* block_table, int table_width,
     const void* cache, int cache_layers, int layer, int page_size,
     void* out, int num_tokens, int num_requests, int max_q_len, int num_splits,
     int nq, int nkv, int d, float scale, int window, cudaStream_t stream) {
     if (num_tokens <= 0 || num_requests <= 0) return TFF_OK;
-    if (num_splits < 1 || nq <= 0 || d <= 0) return TFF_ERR_BAD_ARGUMENT;
-    const long long need = tff_attention_bf16_workspace(num_tokens * nq, num_splits, d);
-    if (need > (long long)TFF_ATTENTION_NOALLOC_SCRATCH_BYTES) return TFF_ERR_SCRATCH_TOO_SMALL;
+    // every argument is checked here, before the size of the scratch is looked at and before anything is launched
+    if (!q || !q_start || !pos_start || !block_table || !cache || !out) return TFF_ERR_BAD_ARGUMENT;
+    if (num_splits < 1 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || d <= 0 || page_size <= 0 || table_width <= 0 ||
+        max_q_len <= 0 || cache_layers <= 0 || layer < 0 || layer >= cache_layers || window < 0)
+        return TFF_ERR_BAD_ARGUMENT;
+    const long long need = tff_attention_bf16_noalloc_bytes(num_tokens, nq, num_splits, d);
+    if (need < 0 || need > (long long)TFF_ATTENTION_NOALLOC_SCRATCH_BYTES) return TFF_ERR_SCRATCH_TOO_SMALL;
     float* scratch = nullptr;
     if (num_splits > 1) {
         int dev = -1;

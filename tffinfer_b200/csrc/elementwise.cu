@@ -2,6 +2,10 @@
 // table, and the fused per-head q/k RMSNorm + RoPE + paged K/V write.
 // Every reduction and every rotation is done in float32 whatever the storage type.
 #include "common.cuh"
+#include "tma_host.h"
+
+// grids of the grid-stride kernels: a few CTAs for every SM of the device the call runs on
+static inline long long sm_count() { const int n = tff_num_sms(); return n > 0 ? n : 1; }
 
 // ---------------------------------------------------------------- embedding
 // x[t, :] = float(E[token[t], :]).  Stands where the reference gathers (and
@@ -157,7 +161,8 @@ TFF_API int tff_swiglu(void* gu, int in_dt, void* out, int out_dt, int rows, int
     if (inter <= 0 || block < 0 || (block > 0 && inter % block != 0)) return TFF_ERR_BAD_ARGUMENT;
     const long long total = (long long)rows * inter;
     const int nt = 256;
-    const int blocks = (int)((total + nt - 1) / nt < 148 * 16 ? (total + nt - 1) / nt : 148 * 16);
+    const long long most = sm_count() * 16;
+    const int blocks = (int)((total + nt - 1) / nt < most ? (total + nt - 1) / nt : most);
     if (in_dt == 1 && out_dt == 1) return tff_launch_pdl(swiglu_kernel<bf16, bf16>, blocks, nt, 0, stream, (bf16*)gu, (bf16*)out, total, inter, block, clear);
     if (in_dt == 0 && out_dt == 1) return tff_launch_pdl(swiglu_kernel<float, bf16>, blocks, nt, 0, stream, (float*)gu, (bf16*)out, total, inter, block, clear);
     if (in_dt == 0 && out_dt == 0) return tff_launch_pdl(swiglu_kernel<float, float>, blocks, nt, 0, stream, (float*)gu, (float*)out, total, inter, block, clear);
@@ -404,7 +409,7 @@ TFF_API int tff_zero_f32(float* p, long long n, cudaStream_t stream) {
     const int ntail = (int)(n - n4 * 4);
     long long blocks = (n4 + 255) / 256;
     if (blocks < 1) blocks = 1;
-    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks > sm_count() * 8) blocks = sm_count() * 8;
     return tff_launch_pdl(zero_f32_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, (float4*)p, p + n4 * 4, n4, ntail);
 }
 
@@ -424,4 +429,39 @@ __global__ void gather_tokens_kernel(int* __restrict__ token_ids, const int* __r
 TFF_API int tff_gather_tokens(int* token_ids, const int* drawn, const int* src, int n, int num_drawn, cudaStream_t stream) {
     if (n <= 0) return TFF_OK;
     return tff_launch_pdl(gather_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, token_ids, drawn, src, n, num_drawn);
+}
+
+// ------------------------------------------------------------ state slots
+// Fixed-size per-request state starts from zero: every request of the step whose first token of this
+// step is at position 0 (a new request, or one that is recomputed after it gave way) has its slot
+// cleared before the layers run.  On the device and part of the step, so that it happens wherever a
+// step is launched from (and inside a replayed CUDA graph), not at some host-side admission call.
+// state: [slots, slot_bytes] bytes; one CTA row per request.
+__global__ void reset_state_slots_kernel(unsigned char* __restrict__ state, long long slot_bytes, int num_slots,
+                                         const int* __restrict__ slots, const int* __restrict__ pos_start) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.y;
+    if (pos_start[b] != 0) return;
+    const int slot = slots[b];
+    if (slot < 0 || slot >= num_slots) return;
+    unsigned char* p = state + (long long)slot * slot_bytes;
+    const long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x, step = (long long)gridDim.x * blockDim.x;
+    if (((uintptr_t)p & 15) == 0 && (slot_bytes & 15) == 0) {
+        uint4* p4 = reinterpret_cast<uint4*>(p);
+        for (long long i = i0; i < (slot_bytes >> 4); i += step) p4[i] = make_uint4(0u, 0u, 0u, 0u);
+    } else {
+        for (long long i = i0; i < slot_bytes; i += step) p[i] = 0;
+    }
+}
+
+TFF_API int tff_reset_state_slots(void* state, long long slot_bytes, int num_slots, const int* slots,
+                                  const int* pos_start, int num_requests, cudaStream_t stream) {
+    if (num_requests <= 0 || slot_bytes <= 0) return TFF_OK;
+    if (!state || !slots || !pos_start || num_slots <= 0 || num_requests > 65535) return TFF_ERR_BAD_ARGUMENT;
+    long long chunks = (slot_bytes / 16 + 255) / 256;
+    if (chunks < 1) chunks = 1;
+    if (chunks > 64) chunks = 64;
+    return tff_launch_pdl(reset_state_slots_kernel, dim3((unsigned)chunks, (unsigned)num_requests), dim3(256), 0, stream,
+                          (unsigned char*)state, slot_bytes, num_slots, slots, pos_start);
 }

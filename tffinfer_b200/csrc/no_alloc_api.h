@@ -54,6 +54,12 @@ int tff_attention_bf16_noalloc(
     void* out, int num_tokens, int num_requests, int max_q_len, int num_splits,
     int nq, int nkv, int d, float scale, int window, cudaStream_t stream);
 
+// How many bytes of the array a call with these counts uses (0 when num_splits == 1), computed in 64 bits;
+// -1 when a count is not positive or the product is beyond 62 bits.  The entry point above refuses a call
+// whose answer is -1 or more than TFF_ATTENTION_NOALLOC_SCRATCH_BYTES.  Launches nothing.
+__attribute__((visibility("default")))
+long long tff_attention_bf16_noalloc_bytes(long long num_tokens, long long nq, long long num_splits, long long d);
+
 #ifdef __cplusplus
 }
 #endif

@@ -123,6 +123,10 @@ int tff_num_sms() {
     return n;
 }
 
+// The SM count of the current device, for planners outside this library (they must cut work the way
+// the launchers size their grids).
+TFF_API int tff_sm_count() { return tff_num_sms(); }
+
 // Copies the error word into pinned host memory in stream order (no synchronisation): the host looks at it
 // when it reads the results of the same step.
 TFF_API int tff_error_word_to_host_async(int* pinned_dst, cudaStream_t stream) {

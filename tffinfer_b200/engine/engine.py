@@ -39,6 +39,7 @@ class Engine:
         self._inflight = None        # the step that has been launched and whose drawn tokens have not been read
         self._host_tokens = [None, None]   # pinned buffers the drawn tokens are copied to, used in turn
         self._host_flip = 0
+        self._held_outputs: List[StepOutput] = []   # outputs read outside step() (abort), handed out by the next step()
 
     # --------------------------------------------------------------- requests
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
@@ -57,7 +58,7 @@ class Engine:
         return rid
 
     def has_unfinished(self) -> bool:
-        return self.scheduler.has_work() or self._inflight is not None
+        return self.scheduler.has_work() or self._inflight is not None or bool(self._held_outputs)
 
     # ------------------------------------------------------------------- step
     def step(self) -> List[StepOutput]:
@@ -69,7 +70,8 @@ class Engine:
         late; ``has_unfinished`` stays true until the last ones have been handed out.  Whenever the host
         needs token values first -- a preempted request to recompute, pages about to run out, a
         repetition penalty -- the step in flight is read before planning."""
-        outs: List[StepOutput] = []
+        outs: List[StepOutput] = self._held_outputs
+        self._held_outputs = []
         sched = self.scheduler
         if self._inflight is not None and (not self.ecfg.async_steps or sched.has_pending_outside_running()
                                            or sched.may_run_out_of_pages() or self._needs_token_values()):
@@ -154,8 +156,10 @@ class Engine:
         return self._resolve(record)
 
     def abort(self, request_id: Hashable) -> None:
-        """Ends a request now (reason "abort") and gives back what it holds."""
-        self._resolve_inflight()
+        """Ends a request now (reason "abort") and gives back what it holds.  A step in flight is read
+        first (its pages must not go to another request while it still writes them); what it produced for
+        the other requests is handed out by the next ``step()``, the aborted request's share is dropped."""
+        self._held_outputs += [o for o in self._resolve_inflight() if o.request_id != request_id]
         r = self.requests.pop(request_id, None)
         if r is None or r.status == "finished":
             return

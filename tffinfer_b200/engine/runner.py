@@ -149,13 +149,10 @@ class ModelRunner:
 
     # --------------------------------------------------------------- requests
     def add_request(self, req: Hashable) -> bool:
-        """Make ``req`` live (a state slot, empty block tables).  False if no slot is free."""
-        slot = self.cache.admit(req)
-        if slot is None:
-            return False
-        for s in self.states:
-            s[slot].zero_()
-        return True
+        """Make ``req`` live (a state slot, empty block tables).  False if no slot is free.
+        Fixed-size state is not touched here: the step that brings a request's token at position 0
+        clears its slot on the device (``_forward``), whoever admitted the request."""
+        return self.cache.admit(req) is not None
 
     def finish_request(self, req: Hashable) -> None:
         self.cache.release(req)
@@ -296,7 +293,11 @@ class ModelRunner:
         graphs = self._graphs[batch.graph_bucket]["graphs"]
         st = graphs.get(batch.key_split_class)
         if st is None:
-            self._forward(batch)                    # warm-up outside the capture (same writes, same values)
+            # The first step of a class runs kernel by kernel and its logits are the step's result; the
+            # capture that follows records the same launches without running them, and replays start
+            # with the next step.  (Running the step once more as a replay would write the same keys and
+            # values again, which is harmless, but would advance a mixer's fixed-size state twice.)
+            eager = self._forward(batch)
             torch.cuda.current_stream().synchronize()
             g = torch.cuda.CUDAGraph()
             if self._graph_pool is None:
@@ -304,8 +305,11 @@ class ModelRunner:
             launches = getattr(self.ops, "launches", 0)
             with torch.cuda.graph(g, pool=self._graph_pool):
                 logits = self._forward(batch)
-            st = {"graph": g, "logits": logits, "launches": getattr(self.ops, "launches", 0) - launches}
-            graphs[batch.key_split_class] = st
+            graphs[batch.key_split_class] = {"graph": g, "logits": logits,
+                                             "launches": getattr(self.ops, "launches", 0) - launches}
+            if hasattr(self.ops, "launches"):
+                self.ops.launches = launches        # recorded, not run
+            return eager[:batch.real_logit_rows]
         st["graph"].replay()
         if hasattr(self.ops, "launches"):
             self.ops.launches += st["launches"]
@@ -313,6 +317,8 @@ class ModelRunner:
 
     def _forward(self, batch: StepBatch) -> torch.Tensor:
         try:
+            for state in self.states:       # requests that start (again) at position 0 start from zero state
+                self.ops.reset_state_slots(state, batch.slots, batch.pos_start)
             return self.model.forward(batch, self.ops, self.act_dtype, self.bindings, self.kv_caches,
                                       batch.block_tables, self.ecfg.page_size, self.states)
         except Exception:

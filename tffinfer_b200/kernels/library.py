@@ -84,6 +84,10 @@ class CudaKernels:
         self._accumulators = {}    # (shape, device) -> float32 buffer kept at zero between uses
         self._acc_zero = {}        # data_ptr -> True while the buffer is known to hold zeros
         self._inv_freq_cache = {}
+        # the planners below cut work by the SM count the launchers size their grids with
+        self.NUM_SMS = int(self.lib.tff_sm_count())
+        if self.NUM_SMS <= 0:
+            raise KernelError("cannot read the SM count of the current CUDA device")
 
     # ------------------------------------------------------------- plumbing
     @staticmethod
@@ -178,7 +182,7 @@ class CudaKernels:
 
     SWAP_MAX_M = 256          # up to this many rows the weights are the 128-row operand
     USE_SM_PAIRS = os.environ.get("TFFINFER_SM_PAIRS", "1") != "0"   # prompt-sized products on tcgen05 cta_group::2
-    NUM_SMS = 148
+    NUM_SMS = 0               # SMs of the device, read from it when the library is loaded
 
     def tc_plan(self, M: int, N: int, K: int, out_is_f32: bool, add: bool = False):
         """(swap, bn, stream_k) of the tcgen05 product for a shape.  stream_k: 0 = whole tiles; 1 = the
@@ -244,6 +248,17 @@ class CudaKernels:
     def zero_f32(self, t) -> None:
         assert t.dtype == torch.float32 and t.is_contiguous()
         self._check(self.lib.tff_zero_f32(_ptr(t), ctypes.c_longlong(t.numel()), self._stream()), "zero_f32")
+        self.launches += 1
+
+    def reset_state_slots(self, state, slots, pos_start) -> None:
+        """state[slots[b]] = 0 for every request b of the step whose first token is at position 0.
+        state: [slots, ...] of any element type; slots, pos_start: int32 [B] on the device."""
+        self._need_cuda(state, slots, pos_start)
+        assert slots.dtype == pos_start.dtype == torch.int32 and slots.numel() == pos_start.numel()
+        slot_bytes = state[0].numel() * state.element_size()
+        self._check(self.lib.tff_reset_state_slots(_ptr(state), ctypes.c_longlong(slot_bytes), _c_int(state.shape[0]),
+                                                   _ptr(slots), _ptr(pos_start), _c_int(slots.numel()),
+                                                   self._stream()), "reset_state_slots")
         self.launches += 1
 
     def gather_tokens(self, token_ids, drawn, src) -> None:
