@@ -30,8 +30,14 @@ class CpuOps:
         m = src >= 0
         token_ids[m] = drawn[src[m].long()]
 
-    def embed(self, token_ids, table, out):
-        out.copy_(table[token_ids.long()].to(torch.float32))
+    def embed(self, token_ids, table, out, scale=1.0):
+        out.copy_((table[token_ids.long()].to(F64) * scale).to(torch.float32))
+
+    def logit_transform(self, logits, scale=1.0, softcap=0.0):
+        v = logits.to(F64) * scale
+        if softcap > 0:
+            v = softcap * torch.tanh(v / softcap)
+        logits.copy_(v.to(torch.float32))
 
     def rmsnorm(self, x, weight, eps, out, row_index=None):
         xs = x if row_index is None else x[row_index.long()]

@@ -5,7 +5,8 @@ import random
 
 import pytest
 
-from tffinfer_b200.cache import (CacheManager, NativeCacheManager, GroupSpec, PagePool, SlotPool, CacheAccountingError,
+from host_twin import TwinCacheManager as CacheManager, PagePool, SlotPool
+from tffinfer_b200.cache import (NativeCacheManager, GroupSpec, CacheAccountingError,
                                  NO_PAGE)
 
 

@@ -9,7 +9,8 @@ import pytest
 import torch
 
 from cpu_ops import CpuOps
-from tffinfer_b200.engine.batch import StepEntry, build_step_batch
+from tffinfer_b200.engine.batch import StepEntry
+from host_twin import build_step_batch
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -42,6 +43,47 @@ def test_embed(ops, T, H, V, dt):
     out = torch.empty(T, H, device=DEV)
     ops.embed(tok.to(DEV), table.to(DEV), out)
     assert torch.equal(out.cpu(), want)
+
+
+def test_embed_with_a_scale_and_with_a_token_outside_the_table(ops):
+    table = g((50, 96), torch.bfloat16, 1)
+    tok = torch.tensor([3, 49, 0], dtype=torch.int32)
+    want = torch.empty(3, 96); CpuOps().embed(tok, table, want, 96 ** 0.5)
+    out = torch.empty(3, 96, device=DEV)
+    ops.embed(tok.to(DEV), table.to(DEV), out, 96 ** 0.5)
+    assert rel_err(out, want) < 1e-6
+    bad = torch.tensor([3, 50, -1], dtype=torch.int32)          # never another token's row: poison instead
+    ops.embed(bad.to(DEV), table.to(DEV), out)
+    assert torch.isfinite(out[0]).all() and torch.isnan(out[1]).all() and torch.isnan(out[2]).all()
+
+
+@pytest.mark.parametrize("R,V,scale,cap", [(1, 100, 0.5, 5.0), (7, 311, 1.0, 30.0), (3, 151936, 0.125, 0.0), (64, 4097, 2.0, 1.5)])
+def test_logit_transform(ops, R, V, scale, cap):
+    logits = g((R, V), torch.float32, 5, 20.0)
+    want = logits.clone(); CpuOps().logit_transform(want, scale, cap)
+    out = logits.clone().to(DEV)
+    ops.logit_transform(out, scale, cap)
+    assert rel_err(out, want) < 2e-6
+    if cap > 0:
+        assert float(out.abs().max()) <= cap
+
+
+@pytest.mark.parametrize("shape,dt", [((7,), torch.float32), ((3, 5), torch.bfloat16), ((4096,), torch.float32),
+                                      ((33,), torch.int32), ((1,), torch.bfloat16)])
+def test_reset_state_slots_clears_exactly_the_slots_of_requests_at_position_zero(ops, shape, dt):
+    slots_total = 6
+    if dt == torch.int32:
+        state = torch.arange(1, slots_total * 33 + 1, dtype=dt).view(slots_total, 33).to(DEV)
+    else:
+        state = (g((slots_total,) + shape, torch.float32, 6) + 3).to(dt).to(DEV)
+    before = state.clone()
+    slots = torch.tensor([4, 0, 2, 5], dtype=torch.int32)
+    pos = torch.tensor([0, 17, 0, 1], dtype=torch.int32)
+    want = before.cpu().clone(); CpuOps().reset_state_slots(want, slots, pos)
+    ops.reset_state_slots(state, slots.to(DEV), pos.to(DEV))
+    assert torch.equal(state.cpu(), want)
+    assert float(state[4].float().abs().max()) == 0 and float(state[2].float().abs().max()) == 0
+    assert torch.equal(state[[0, 1, 3, 5]].cpu(), before[[0, 1, 3, 5]].cpu())
 
 
 @pytest.mark.parametrize("rows,dim", [(1, 48), (7, 80), (3, 4096), (2, 5120), (9, 1000)])

@@ -6,7 +6,8 @@ import torch
 
 import plain_qwen3 as P
 from tffinfer_b200 import get_part
-from tffinfer_b200.engine.batch import StepEntry, build_step_batch
+from tffinfer_b200.engine.batch import StepEntry
+from host_twin import build_step_batch
 from tffinfer_b200.parts import LayerContext, PartSpec, build_part
 
 pytestmark = pytest.mark.gpu

@@ -6,7 +6,8 @@ import pytest
 from cpu_ops import CpuOps
 from helpers import make_model_dir, PAGE_SIZE
 from plain_qwen3 import PlainModel, sample_temperature, sample_greedy
-from tffinfer_b200.cache import make_cache_manager, GroupSpec
+from host_twin import TwinCacheManager
+from tffinfer_b200.cache import NativeCacheManager, GroupSpec
 from tffinfer_b200.config import EngineConfig
 from tffinfer_b200.engine import Scheduler, Request, Engine, ModelRunner
 from tffinfer_b200.sampling import SamplingParams, uniform_for
@@ -23,7 +24,7 @@ def _which_manager(request):
 
 
 def _sched(pages=16, page=4, live=4, budget=8, max_len=64):
-    cache = make_cache_manager([GroupSpec(2, 2, 16, 0)], page, [pages], live, native=NATIVE)
+    cache = (NativeCacheManager if NATIVE else TwinCacheManager)([GroupSpec(2, 2, 16, 0)], page, [pages], live)
     return Scheduler(cache, budget, max_len), cache
 
 
@@ -131,8 +132,8 @@ def test_a_request_that_cannot_fit_alone_ends_with_out_of_memory():
 # ------------------------------------------------------------------ through the entry point
 def _engine(tmp_path, name, **kw):
     d = make_model_dir(tmp_path, name)
-    ecfg = EngineConfig(dtype="float32", page_size=PAGE_SIZE[name], device="cpu", native_host=NATIVE, **kw)
-    return d, Engine(runner=ModelRunner(d, ecfg, ops=CpuOps()))
+    ecfg = EngineConfig(dtype="float32", page_size=PAGE_SIZE[name], device="cpu", **kw)
+    return d, Engine(runner=ModelRunner(d, ecfg, ops=CpuOps(), cache_factory=None if NATIVE else TwinCacheManager))
 
 
 def _plain_generate(pm, prompt, n, params=None, key=0):
@@ -191,3 +192,32 @@ def test_infer_runtime_has_the_reference_call_sequence(tmp_path):
     out = []
     rt.infer(4, out)
     assert [len(o) for o in out] == [4, 4]
+
+
+def test_a_windowed_group_serves_requests_longer_than_its_pool():
+    """A group whose mixers keep a window of keys gives the pages behind the window back at every commit, so a
+    request needs the window and one step's tokens at a time, not its whole length: 60 tokens run through a
+    pool of 32.  The same length is refused when a group that keeps all keys shares the model."""
+    page, pages, budget = 4, 8, 8
+    Manager = NativeCacheManager if NATIVE else TwinCacheManager
+    cache = Manager([GroupSpec(2, 2, 16, 8)], page, [pages], 2)
+    s = Scheduler(cache, budget, 128)
+    r = _req(1, 60, new=4)
+    s.add(r)
+    steps, most = 0, 0
+    while s.has_work():
+        p = s.schedule()
+        assert not p.finished, p.finished[0].finish_reason
+        most = max(most, pages - cache.pools[0].num_free)
+        _run(s, p)
+        steps += 1
+        assert steps < 100
+    assert r.finish_reason == "length" and len(r.generated) == 4
+    assert most <= 5                                   # the window's pages and the step's, never the whole length
+    assert cache.pools[0].num_free == pages
+    cache.check()
+    both = Manager([GroupSpec(2, 2, 16, 8), GroupSpec(1, 2, 16, 0)], page, [pages, pages], 2)
+    s = Scheduler(both, budget, 128)
+    s.add(_req(2, 60))
+    p = s.schedule()
+    assert p.finished and p.finished[0].finish_reason == "out_of_memory" and not p.entries

@@ -2,7 +2,8 @@
 the attention launches take the requests, padding of fixed-size batches."""
 import torch
 
-from tffinfer_b200.engine.batch import StepEntry, build_step_batch, pack_step, batch_from_device
+from tffinfer_b200.engine.batch import StepEntry, batch_from_device
+from host_twin import build_step_batch, pack_step
 
 
 def _batch(lens_new, lens_old, page=4):

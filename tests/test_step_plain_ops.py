@@ -66,8 +66,9 @@ def test_a_step_that_cannot_run_is_refused_without_side_effects(tmp_path, native
     from tffinfer_b200.engine import StepEntry, OutOfPages, RequestError
     d = make_model_dir(tmp_path, "A")
     ecfg = EngineConfig(dtype="float32", page_size=4, max_cache_tokens=24, max_live_requests=3, device="cpu",
-                        max_model_len=20, native_host=native)
-    runner = ModelRunner(d, ecfg, ops=CpuOps())
+                        max_model_len=20)
+    from host_twin import TwinCacheManager
+    runner = ModelRunner(d, ecfg, ops=CpuOps(), cache_factory=None if native else TwinCacheManager)
     runner.add_request("a"); runner.add_request("b")
     free = lambda: [p.num_free for p in runner.cache.pools]
     before = free()

@@ -96,8 +96,10 @@ def test_a_mixer_with_state_generates_through_the_engine_on_cpu_twins(tmp_path, 
     from tffinfer_b200.engine import Engine
     d, cfg, w, prompts = _generate_case(tmp_path)
     ecfg = EngineConfig(dtype="float32", page_size=4, max_cache_tokens=48, max_live_requests=4,
-                        max_tokens_per_step=6, device="cpu", native_host=native)
-    _check_generation(Engine(runner=ModelRunner(d, ecfg, ops=CpuOps())), cfg, w, prompts, 1e-5)
+                        max_tokens_per_step=6, device="cpu")
+    from host_twin import TwinCacheManager
+    runner = ModelRunner(d, ecfg, ops=CpuOps(), cache_factory=None if native else TwinCacheManager)
+    _check_generation(Engine(runner=runner), cfg, w, prompts, 1e-5)
 
 
 @pytest.mark.gpu

@@ -1,5 +1,7 @@
 """Toy parts defined outside the framework: a mixer with state of its own, a routed
-feed-forward, an absolute position encoding, and an architecture made of them.  They
+feed-forward, an absolute position encoding, an arrangement with norms after the mixer and
+after the feed-forward as well as before them, a scaled embedding and capped logits, and an
+architecture made of them.  They
 exist to show that parts and architectures can be registered, built and stepped
 without a change to the framework's files.  They are not a model of anyone's."""
 from __future__ import annotations
@@ -11,8 +13,10 @@ import torch
 
 from tffinfer_b200 import register_part, register_architecture
 from tffinfer_b200.config import ModelConfig
-from tffinfer_b200.parts import (Mixer, FeedForward, PositionEncoding, WeightSpec, MATRIX, VECTOR, StateNeed,
+from tffinfer_b200.parts import (Mixer, FeedForward, PositionEncoding, Block, WeightSpec, MATRIX, VECTOR, StateNeed,
                                  ModelDescription, LayerSpec, PartSpec, ScheduleEntry)
+
+LOGIT_SCALE, LOGIT_SOFTCAP = 0.5, 5.0
 
 
 @register_part("mixer", "toy_running_mean", replace=True)
@@ -102,6 +106,19 @@ class LearnedAbsolute(PositionEncoding):
         return x + self.table[batch.positions.long()]
 
 
+@register_part("block", "toy_sandwich", replace=True)
+class SandwichBlock(Block):
+    """x + norm(mixer(norm(x))), then x + norm(ffn(norm(x))): the two norms behind the parts come from the
+    layer's ``extra_norms``."""
+    def forward(self, x, ctx, act_dtype):
+        h = self.mixer_norm.forward(x, ctx.ops, act_dtype)
+        m = self.mixer.forward(h, ctx, residual=torch.zeros_like(x))
+        x = x + self.extra_norms["post_mixer"].forward(m, ctx.ops, torch.float32)
+        h = self.ffn_norm.forward(x, ctx.ops, act_dtype)
+        f = self.feed_forward.forward(h, ctx, residual=torch.zeros_like(x))
+        return x + self.extra_norms["post_ffn"].forward(f, ctx.ops, torch.float32)
+
+
 @dataclass(frozen=True)
 class ToyConfig(ModelConfig):
     hidden_size: int = 48
@@ -135,9 +152,10 @@ def describe_toy(cfg: ToyConfig) -> ModelDescription:
                                                    qk_norm=False, window=0), prefix=f"{p}.mixer")
         ffn = (PartSpec("toy_top1_experts", dict(hidden_size=H, num_experts=cfg.num_experts), prefix=f"{p}.ffn")
                if i % 2 == 0 else PartSpec("swiglu", dict(hidden_size=H, intermediate_size=2 * H), prefix=f"{p}.ffn"))
-        layers.append(LayerSpec(mixer=mixer, feed_forward=ffn,
-                                mixer_norm=PartSpec("rms_norm", dict(dim=H, eps=cfg.eps), prefix=f"{p}.norm1"),
-                                ffn_norm=PartSpec("rms_norm", dict(dim=H, eps=cfg.eps), prefix=f"{p}.norm2"),
+        norm = lambda name: PartSpec("rms_norm", dict(dim=H, eps=cfg.eps), prefix=f"{p}.{name}")
+        layers.append(LayerSpec(mixer=mixer, feed_forward=ffn, mixer_norm=norm("norm1"), ffn_norm=norm("norm2"),
+                                block="pre_norm" if i % 2 == 0 else "toy_sandwich",
+                                extra_norms={} if i % 2 == 0 else {"post_mixer": norm("norm3"), "post_ffn": norm("norm4")},
                                 position=None))
     # layer 0 runs twice (each run with a state of its own); the last run of the attention
     # layer reads the cache of its first run instead of keeping one
@@ -148,7 +166,8 @@ def describe_toy(cfg: ToyConfig) -> ModelDescription:
         final_norm=PartSpec("rms_norm", dict(dim=H, eps=cfg.eps), prefix="final_norm"),
         layers=layers, schedule=schedule,
         positions={"abs": PartSpec("toy_learned_absolute", dict(hidden_size=H, max_position=cfg.max_position),
-                                   prefix="positions")})
+                                   prefix="positions")},
+        embed_scale=float(H) ** 0.5, logit_scale=LOGIT_SCALE, logit_softcap=LOGIT_SOFTCAP)
 
 
 def register_toy():
@@ -166,7 +185,7 @@ def toy_plain_logits(tokens, w: Dict[str, torch.Tensor], cfg: ToyConfig) -> torc
     def norm(x, name):
         return (x * torch.rsqrt((x * x).mean(-1, keepdim=True) + cfg.eps)) * w[name]
 
-    x = w["embed.weight"][torch.tensor(tokens)] + w["positions.weight"][:T]
+    x = w["embed.weight"][torch.tensor(tokens)] * float(H) ** 0.5 + w["positions.weight"][:T]
     kv_of_layer1 = None
     for e, li in enumerate([0, 1, 2, 0, 1]):
         p = f"blocks.{li}"
@@ -187,7 +206,7 @@ def toy_plain_logits(tokens, w: Dict[str, torch.Tensor], cfg: ToyConfig) -> torc
             for hh in range(3):
                 s = (q[:, hh] @ k[:, 0].t()) / math.sqrt(16)
                 o[:, hh] = torch.softmax(s.masked_fill(~mask, float("-inf")), -1) @ v[:, 0]
-            x = x + o.reshape(T, 48) @ w[f"{p}.mixer.o_proj.weight"].t()
+            x = x + norm(o.reshape(T, 48) @ w[f"{p}.mixer.o_proj.weight"].t(), f"{p}.norm3.weight")
         h = norm(x, f"{p}.norm2.weight")
         if li % 2 == 0:
             choice = (h @ w[f"{p}.ffn.router.weight"].t()).argmax(-1)
@@ -199,5 +218,6 @@ def toy_plain_logits(tokens, w: Dict[str, torch.Tensor], cfg: ToyConfig) -> torc
         else:
             g = h @ w[f"{p}.ffn.gate_proj.weight"].t()
             u = h @ w[f"{p}.ffn.up_proj.weight"].t()
-            x = x + ((g / (1 + torch.exp(-g))) * u) @ w[f"{p}.ffn.down_proj.weight"].t()
-    return norm(x, "final_norm.weight") @ w["head.weight"].t()
+            x = x + norm(((g / (1 + torch.exp(-g))) * u) @ w[f"{p}.ffn.down_proj.weight"].t(), f"{p}.norm4.weight")
+    logits = norm(x, "final_norm.weight") @ w["head.weight"].t()
+    return LOGIT_SOFTCAP * torch.tanh(logits * LOGIT_SCALE / LOGIT_SOFTCAP)

@@ -1,9 +1,9 @@
-from .pages import PagePool, SlotPool, CacheAccountingError
-from .manager import CacheManager, GroupSpec, RequestCache, NO_PAGE
+from .spec import GroupSpec, CacheAccountingError, NO_PAGE
 from .native import NativeCacheManager
 
+CacheManager = NativeCacheManager
 
-def make_cache_manager(groups, page_size, pages_per_group, max_live_requests, native: bool = True):
-    """The cache manager of the C++ host runtime, or its Python twin (same interface, same decisions)."""
-    cls = NativeCacheManager if native else CacheManager
-    return cls(groups, page_size, pages_per_group, max_live_requests)
+
+def make_cache_manager(groups, page_size, pages_per_group, max_live_requests):
+    """The cache manager of the C++ host runtime (csrc/host/host_runtime.cpp)."""
+    return NativeCacheManager(groups, page_size, pages_per_group, max_live_requests)

@@ -1,8 +1,10 @@
-"""The cache manager and the step packer of the C++ host runtime (csrc/host/host_runtime.cpp) behind the
-interface of the Python classes in manager.py and of engine.batch.pack_step.
+"""The cache manager, the planner of a scheduler pass and the step packer: the C++ host runtime
+(csrc/host/host_runtime.cpp) behind a Python class.  Keys and values live in pages with a block table per
+request, one page pool per group of layers with the same need, and slots for fixed-size state.
 
-The Python classes stay as the plain twin: same decisions, same page ids in the same order; the tests drive
-both with the same random orders of requests and compare every answer.  The engine uses this one.
+This is the one host runtime of the engine.  A plain Python twin with the same interface lives with the
+tests (tests/host_twin.py); they drive both with the same random orders of requests and compare every
+answer.
 """
 from __future__ import annotations
 
@@ -12,8 +14,7 @@ from typing import Dict, Hashable, List, Optional, Sequence
 import numpy as np
 
 from ..csrc import build as _build
-from .manager import GroupSpec
-from .pages import CacheAccountingError
+from .spec import GroupSpec, CacheAccountingError
 
 _i32p = ctypes.POINTER(ctypes.c_int)
 _i64p = ctypes.POINTER(ctypes.c_int64)
@@ -98,7 +99,7 @@ class _SlotView:
 
 
 class NativeCacheManager:
-    """Same interface as cache.manager.CacheManager; the state lives in the C++ object."""
+    """Page pools, slots and block tables of the live requests; the state lives in the C++ object."""
 
     def __init__(self, groups: Sequence[GroupSpec], page_size: int, pages_per_group: Sequence[int],
                  max_live_requests: int):
@@ -330,8 +331,11 @@ class NativeCacheManager:
     def pack_step(self, entries, *, pad_requests: int = 0, widths: Optional[Sequence[int]] = None,
                   dummy_pages: Optional[Sequence[int]] = None, dummy_slot: int = 0,
                   out: Optional[np.ndarray] = None, arrays: Optional["StepArrays"] = None):
-        """engine.batch.pack_step with positions, slots and block tables taken from this manager: returns
-        (array, layout, info) of the same meaning.  ``arrays``: what gather_step made of the entries."""
+        """The step's integer arrays in one int32 buffer (layout: engine.batch.BatchLayout), with positions,
+        slots and block tables taken from this manager.  Returns (array, layout, info); ``info`` holds the
+        host-side figures launch decisions need.  ``pad_requests`` fills the batch up with padding requests
+        (one token at position 0 writing to ``dummy_pages`` / ``dummy_slot``), ``widths`` fixes the block-table
+        widths, ``out`` is a buffer to pack into, ``arrays`` what gather_step made of the entries."""
         from ..engine.batch import BatchLayout
         if arrays is None:
             arrays = self.gather_step(entries)

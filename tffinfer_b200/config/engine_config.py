@@ -26,8 +26,6 @@ class EngineConfig:
     max_model_len: Optional[int] = None      # cap on a request's length; None = config.max_position
     use_cuda_graphs: bool = True       # capture decode-only steps per batch-size bucket
     async_steps: bool = True           # launch the next step before the drawn tokens of the last one are read
-    native_host: bool = True           # page pools, block tables and step packing in the C++ host library
-                                       # (False: their Python twins, same decisions)
     seed: int = 0
     device: str = "cuda"
     memory_fraction: float = 0.85      # share of free device memory the cache may take when sized automatically

@@ -10,9 +10,11 @@ static inline long long sm_count() { const int n = tff_num_sms(); return n > 0 ?
 // ---------------------------------------------------------------- embedding
 // x[t, :] = float(E[token[t], :]).  Stands where the reference gathers (and
 // de-quantises) embedding rows on the CPU: src/kernel/cpu/embedding.cpp:35-49.
+// ``scale`` multiplies every element (1 for this architecture, whose embedding is not scaled: the product
+// with 1.0f is exact; architectures that scale by sqrt(hidden) or another constant say so in their description).
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
-                             float* __restrict__ out, int hidden, int vocab) {
+                             float* __restrict__ out, int hidden, int vocab, float scale) {
     pdl_launch_dependents();          // the next kernel may become resident (it waits before it reads or writes)
     pdl_wait();
     const int t = blockIdx.x;
@@ -23,16 +25,16 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restric
         return;
     }
     const TW* row = table + (size_t)tok * hidden;
-    for (int h = threadIdx.x; h < hidden; h += blockDim.x) o[h] = to_f32<TW>(row[h]);
+    for (int h = threadIdx.x; h < hidden; h += blockDim.x) o[h] = to_f32<TW>(row[h]) * scale;
 }
 
 TFF_API int tff_embed(const int* tokens, const void* table, int table_is_bf16, float* out,
-                      int num_tokens, int hidden, int vocab, cudaStream_t stream) {
+                      int num_tokens, int hidden, int vocab, float scale, cudaStream_t stream) {
     if (num_tokens <= 0) return TFF_OK;
     if (hidden <= 0 || vocab <= 0) return TFF_ERR_BAD_ARGUMENT;
     const int nt = hidden >= 1024 ? 256 : 128;
-    if (table_is_bf16) return tff_launch_pdl(embed_kernel<bf16>, num_tokens, nt, 0, stream, tokens, (const bf16*)table, out, hidden, vocab);
-    return tff_launch_pdl(embed_kernel<float>, num_tokens, nt, 0, stream, tokens, (const float*)table, out, hidden, vocab);
+    if (table_is_bf16) return tff_launch_pdl(embed_kernel<bf16>, num_tokens, nt, 0, stream, tokens, (const bf16*)table, out, hidden, vocab, scale);
+    return tff_launch_pdl(embed_kernel<float>, num_tokens, nt, 0, stream, tokens, (const float*)table, out, hidden, vocab, scale);
 }
 
 // four consecutive outputs in one store
@@ -464,4 +466,27 @@ TFF_API int tff_reset_state_slots(void* state, long long slot_bytes, int num_slo
     if (chunks > 64) chunks = 64;
     return tff_launch_pdl(reset_state_slots_kernel, dim3((unsigned)chunks, (unsigned)num_requests), dim3(256), 0, stream,
                           (unsigned char*)state, slot_bytes, num_slots, slots, pos_start);
+}
+
+// ------------------------------------------------------------ logit transform
+// logits = softcap > 0 ? softcap * tanh(logits * scale / softcap) : logits * scale, in place, float32.
+// Not launched for this architecture (scale 1, no cap); a description that sets either gets it after the
+// output projection.
+__global__ void logit_transform_kernel(float* __restrict__ logits, long long n, float scale, float softcap) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const float inv = softcap > 0.f ? 1.f / softcap : 0.f;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        float v = logits[i] * scale;
+        if (softcap > 0.f) v = softcap * tanhf(v * inv);
+        logits[i] = v;
+    }
+}
+
+TFF_API int tff_logit_transform(float* logits, long long n, float scale, float softcap, cudaStream_t stream) {
+    if (n <= 0) return TFF_OK;
+    if (!logits || softcap < 0.f) return TFF_ERR_BAD_ARGUMENT;
+    long long blocks = (n + 255) / 256;
+    if (blocks > sm_count() * 8) blocks = sm_count() * 8;
+    return tff_launch_pdl(logit_transform_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, logits, n, scale, softcap);
 }

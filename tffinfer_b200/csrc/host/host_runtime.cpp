@@ -407,8 +407,18 @@ TFFH_API int tffh_plan_step(void* cache, int budget_tokens, int max_model_len,
         return true;
     };
     const char* too_many = "more events than the buffer given holds";
-    int capacity_tokens = INT32_MAX;
-    for (const Pool& p : c->pools) capacity_tokens = std::min<int64_t>(capacity_tokens, (int64_t)p.total * c->page_size);
+    // Whether a request of ``len`` tokens can ever run, alone: in a group that keeps all keys it holds pages for
+    // all of them; in a group that keeps a window, for the window and one step's tokens (whose pages are taken
+    // before those behind the window go back), with a page of slack at either ragged end.
+    auto fits_alone = [&](int len) -> bool {
+        for (int g = 0; g < G; ++g) {
+            const int w = c->windows[g];
+            int64_t most = len;
+            if (w > 0) most = std::min<int64_t>(most, (int64_t)w + budget_tokens + 2 * (int64_t)c->page_size);
+            if (most > (int64_t)c->pools[g].total * c->page_size) return false;
+        }
+        return true;
+    };
 
     std::vector<std::pair<int, int>> chosen;        // (position in run, tokens)
     std::vector<int> free_pages(G), need(G);
@@ -455,7 +465,7 @@ TFFH_API int tffh_plan_step(void* cache, int budget_tokens, int max_model_len,
                 ++w;
                 continue;
             }
-            if (r.len > capacity_tokens) {
+            if (!fits_alone(r.len)) {
                 if (!emit(TFFH_EVENT_FINISH, r.uid, TFFH_REASON_OUT_OF_MEMORY, 0)) return c->fail(TFFH_ERR_TOO_SMALL, too_many);
                 ++w;
                 continue;

@@ -1,4 +1,4 @@
-from .batch import StepEntry, StepBatch, build_step_batch
+from .batch import StepEntry, StepBatch
 from .runner import ModelRunner, OutOfPages, RequestError
 from .scheduler import Scheduler, Request, StepPlan, PlanEntry, StepOutput
 from .engine import Engine, InferRuntime

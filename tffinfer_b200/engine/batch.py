@@ -6,7 +6,8 @@ The reference's ``LLMBatch{_tokens, _pos, _token_seq_ids, _logits}``
 one contiguous run of one sequence at a time (InferRuntime.cu:429;
 QWen3Creator.cpp:267-268).  Here any mix runs as one batch.
 
-All integer arrays are packed into one host buffer and reach the device in one copy.
+All integer arrays are packed into one host buffer (by the host runtime, which holds the positions, slots and
+block tables: cache/native.py ``pack_step``) and reach the device in one copy.
 A batch may be padded to a fixed number of requests and a fixed block-table width,
 so that its device arrays have fixed addresses and sizes (for CUDA graphs); padding
 requests bring one token at position 0 whose keys go to a page nobody reads.
@@ -101,89 +102,6 @@ def batch_views(dev: torch.Tensor, layout: BatchLayout):
     return v, bts
 
 
-def pack_step(entries: Sequence[StepEntry], starts: Sequence[int], slots: Sequence[int],
-              tables: Sequence[Sequence[Sequence[int]]], *, pad_requests: int = 0,
-              widths: Optional[Sequence[int]] = None, dummy_pages: Optional[Sequence[int]] = None, dummy_slot: int = 0,
-              out: Optional[np.ndarray] = None):
-    """Packs the step into one int32 array.  Returns (array, layout, info).
-
-    entries[i] starts at position starts[i]; tables[g][i] is request i's block table in
-    group g (page ids, -1 for pages that were given back).  With ``pad_requests`` > len(entries)
-    the batch is filled up with padding requests (one token 0 at position 0, logits asked)."""
-    nreal = len(entries)
-    q_lens = np.array([len(e.tokens) for e in entries], dtype=np.int32)
-    if nreal == 0 or (q_lens <= 0).any():
-        raise ValueError("a step needs at least one request and every request at least one token")
-    npad = max(0, pad_requests - nreal)
-    B = nreal + npad
-    if npad:
-        q_lens = np.concatenate([q_lens, np.ones(npad, dtype=np.int32)])
-    T = int(q_lens.sum())
-    q_start = np.zeros(B + 1, dtype=np.int32)
-    np.cumsum(q_lens, out=q_start[1:])
-    pos_start = np.zeros(B, dtype=np.int32)
-    pos_start[:nreal] = np.asarray(starts, dtype=np.int32)
-    kv_len = pos_start + q_lens
-    token_ids = np.zeros(T, dtype=np.int32)
-    if T - npad == nreal:           # every real request brings one token
-        token_ids[:nreal] = [e.tokens[0] for e in entries]
-    else:
-        token_ids[:T - npad] = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
-    tok_req = np.repeat(np.arange(B, dtype=np.int32), q_lens)
-    positions = (np.arange(T, dtype=np.int32) - np.repeat(q_start[:-1], q_lens) + np.repeat(pos_start, q_lens)).astype(np.int32)
-    rows = []
-    for i, e in enumerate(entries):
-        for w in e.want:
-            if not (0 <= int(w) < int(q_lens[i])):
-                raise ValueError(f"request {e.req!r}: wanted place {w} is outside its {int(q_lens[i])} tokens")
-            rows.append(int(q_start[i]) + int(w))
-    real_rows = len(rows)
-    rows.extend(int(q_start[nreal + j]) for j in range(npad))
-    G = len(tables)
-    if widths is None:
-        widths = [max(1, max((len(t) for t in tables[g]), default=0)) for g in range(G)]
-    layout = BatchLayout(T, B, len(rows), tuple(int(w) for w in widths))
-    if out is None:
-        out = np.empty(layout.total, dtype=np.int32)
-    elif out.shape[0] != layout.total:
-        raise ValueError("the given buffer does not fit the batch layout")
-    offs = layout.offsets()
-    slot_arr = np.full(B, dummy_slot, dtype=np.int32)
-    slot_arr[:nreal] = np.asarray(slots, dtype=np.int32)
-    # requests ordered by the number of tokens they bring (shortest first): kernels that treat
-    # single decoded tokens and long portions differently take a prefix or a suffix of this order
-    # by the number of new tokens, and among equals the longest context first: the attention launches take
-    # their requests in this order, and work items that start first should be the long ones
-    req_order = np.lexsort((-kv_len, q_lens)).astype(np.int32)
-    tok_src = np.full(T, -1, dtype=np.int32)
-    has_src = False
-    for i, e in enumerate(entries):
-        if e.token_src is not None:
-            tok_src[q_start[i]:q_start[i] + len(e.tokens)] = np.asarray(e.token_src, dtype=np.int32)
-            has_src = True
-    if has_src:
-        token_ids[tok_src >= 0] = 0
-    for o, arr in zip(offs[:NUM_FLAT], (token_ids, positions, tok_req, q_start, pos_start, kv_len, slot_arr,
-                                        np.asarray(rows, dtype=np.int32), req_order, tok_src)):
-        out[o:o + arr.shape[0]] = arr
-    for g in range(G):
-        w = layout.widths[g]
-        bt = out[offs[NUM_FLAT + g]:offs[NUM_FLAT + g] + B * w].reshape(B, w)
-        bt[:nreal] = -1
-        bt[nreal:] = dummy_pages[g] if dummy_pages is not None else -1
-        for i, t in enumerate(tables[g]):
-            n = len(t)
-            if n > w:
-                raise ValueError("a block table is wider than the batch layout allows")
-            if n:
-                bt[i, :n] = t
-    info = dict(max_q_len=int(q_lens.max()), max_kv_len=int(kv_len.max()), q_lens=q_lens, pos_start=pos_start,
-                sorted_q_lens=q_lens[req_order], sorted_kv_lens=np.where(req_order < nreal, kv_len[req_order], 0),
-                has_token_src=has_src,
-                all_decode=bool((q_lens == 1).all()), real_requests=nreal, real_logit_rows=real_rows)
-    return out, layout, info
-
-
 def batch_from_device(dev: torch.Tensor, layout: BatchLayout, info) -> StepBatch:
     v, bts = batch_views(dev, layout)
     return StepBatch(
@@ -206,10 +124,3 @@ def packed_to_device(arr: np.ndarray, layout: BatchLayout, info, device, pinned:
     else:
         dev = host.to(device)
     return batch_from_device(dev, layout, info)
-
-
-def build_step_batch(entries: Sequence[StepEntry], starts: Sequence[int], slots: Sequence[int],
-                     tables: Sequence[Sequence[Sequence[int]]], device, pinned: bool = False) -> StepBatch:
-    """Packs the step and copies it to ``device`` in one transfer."""
-    arr, layout, info = pack_step(entries, starts, slots, tables)
-    return packed_to_device(arr, layout, info, device, pinned)

@@ -19,7 +19,7 @@ from ..config import EngineConfig, read_config_json
 from ..parts import Model, CacheBinding, KVNeed, StateNeed
 from ..registry import get_architecture
 from ..weights import load_model_weights
-from .batch import StepEntry, StepBatch, pack_step, packed_to_device, batch_from_device, BatchLayout
+from .batch import StepEntry, StepBatch, packed_to_device, batch_from_device, BatchLayout
 
 _TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 _STATE_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": torch.int32}
@@ -42,9 +42,12 @@ def _make_ops(device: str):
 
 class ModelRunner:
     def __init__(self, model_dir: Optional[str] = None, engine_config: Optional[EngineConfig] = None, *,
-                 config=None, tensors: Optional[Dict[str, torch.Tensor]] = None, ops=None):
+                 config=None, tensors: Optional[Dict[str, torch.Tensor]] = None, ops=None, cache_factory=None):
         """Either ``model_dir`` (config.json + safetensors) or ``config`` with ``tensors``
-        (name -> tensor, checked like a file).  ``ops`` overrides the kernel library."""
+        (name -> tensor, checked like a file).  ``ops`` overrides the kernel library and
+        ``cache_factory(groups, page_size, pages_per_group, max_live_requests)`` the host runtime (tests
+        hand in plain twins of either; the engine itself has one of each)."""
+        self._cache_factory = cache_factory or make_cache_manager
         import tffinfer_b200.parts  # noqa: F401  registers the built-in parts
         import tffinfer_b200.models  # noqa: F401  registers the architectures
         self.ecfg = (engine_config or EngineConfig()).normalized()
@@ -143,8 +146,7 @@ class ModelRunner:
         if self.graph_buckets[-1] < min(self.ecfg.max_live_requests, 256):
             self.graph_buckets.append(min(self.ecfg.max_live_requests, 256))
         self.table_width = max(1, -(-self.max_model_len // ps))
-        self.cache = make_cache_manager(groups, ps, n_pages, self.ecfg.max_live_requests,
-                                        native=self.ecfg.native_host)
+        self.cache = self._cache_factory(groups, ps, n_pages, self.ecfg.max_live_requests)
         self.groups = groups
 
     # --------------------------------------------------------------- requests
@@ -165,11 +167,7 @@ class ModelRunner:
         """Checks the entries, takes the pages they need (all or nothing) and builds
         the device-side batch.  Raises OutOfPages without side effects.  Entries with
         ``token_src`` take token ids from ``prev_tokens`` (int32, on the device)."""
-        arrays = None
-        if hasattr(self.cache, "reserve_step"):
-            arrays = self._check_and_reserve_native(entries, prev_tokens)
-        else:
-            self._check_and_reserve(entries, prev_tokens)
+        arrays = self._check_and_reserve(entries, prev_tokens)
         if self._graph_eligible(entries):
             batch = self._make_static_batch(entries, arrays)
             if batch.tok_src is not None:
@@ -183,42 +181,10 @@ class ModelRunner:
             + sum(t.numel() for t in batch.block_tables))
         return batch
 
-    def _check_and_reserve(self, entries, prev_tokens) -> None:
-        """The checks of a step and its pages, all or nothing, entry by entry (the twin of
-        _check_and_reserve_native, used with the Python cache manager)."""
-        seen = set()
-        for e in entries:
-            if not self.cache.is_live(e.req):
-                raise RequestError(f"request {e.req!r} is not live (add_request first)")
-            if e.req in seen:
-                raise RequestError(f"request {e.req!r} appears twice in one step")
-            seen.add(e.req)
-            n = len(e.tokens)
-            if n == 0:
-                raise RequestError(f"request {e.req!r} brings no tokens")
-            if self.cache.num_tokens(e.req) + n > self.max_model_len:
-                raise RequestError(f"request {e.req!r} would exceed the maximum length {self.max_model_len}")
-            toks = e.tokens if e.token_src is None else [t for t, s in zip(e.tokens, e.token_src) if s < 0]
-            if toks and (min(toks) < 0 or max(toks) >= self.desc.vocab_size):
-                raise RequestError(f"request {e.req!r}: token id outside [0, {self.desc.vocab_size})")
-            if e.token_src is not None and prev_tokens is None:
-                raise RequestError(f"request {e.req!r} takes tokens from a previous step, but none was given")
-        # all-or-nothing over the whole step: check first, then take
-        need = [0] * len(self.groups)
-        for e in entries:
-            for g, n in enumerate(self.cache.pages_needed(e.req, len(e.tokens))):
-                need[g] += n
-        for g, n in enumerate(need):
-            if n > self.cache.pools[g].num_free:
-                raise OutOfPages(f"step needs {n} pages in cache group {g}, {self.cache.pools[g].num_free} are free")
-        for e in entries:
-            ok = self.cache.reserve(e.req, len(e.tokens))
-            assert ok
-
-    def _check_and_reserve_native(self, entries, prev_tokens):
-        """The same by the C++ host runtime: the entries are gathered into flat arrays once (they are packed
-        from the same arrays afterwards), token ids are checked on the array, and one call checks the
-        requests and takes the pages of the whole step or none."""
+    def _check_and_reserve(self, entries, prev_tokens):
+        """The checks of a step and its pages, all or nothing, by the host runtime: the entries are gathered
+        into flat arrays once (they are packed from the same arrays afterwards), token ids are checked on the
+        array, and one call checks the requests and takes the pages of the whole step or none."""
         arrays = self.cache.gather_step(entries)
         tok = arrays.tokens if arrays.tok_src is None else arrays.tokens[arrays.tok_src < 0]
         if tok.size and (int(tok.min()) < 0 or int(tok.max()) >= self.desc.vocab_size):
@@ -249,15 +215,9 @@ class ModelRunner:
                 and all(len(e.tokens) == 1 and len(e.want) == 1 for e in entries))
 
     def _pack(self, entries, arrays=None, **kw):
-        """The step's integer arrays in one host buffer: by the C++ host runtime, which holds the positions,
-        slots and block tables itself, or by its Python twin from lists read out of the cache manager."""
-        native = getattr(self.cache, "pack_step", None)
-        if native is not None:
-            return native(entries, arrays=arrays, **kw)
-        starts = [self.cache.num_tokens(e.req) for e in entries]
-        slots = [self.cache.slot_of(e.req) for e in entries]
-        tables = [[self.cache.block_table(e.req, g) for e in entries] for g in range(len(self.groups))]
-        return pack_step(entries, starts, slots, tables, **kw)
+        """The step's integer arrays in one host buffer, packed by the host runtime, which holds the
+        positions, slots and block tables itself."""
+        return self.cache.pack_step(entries, arrays=arrays, **kw)
 
     def _make_static_batch(self, entries, arrays=None) -> StepBatch:
         """Decode-only steps use device arrays of fixed address and size, one set per

@@ -22,8 +22,10 @@ Policy
     a prompt longer than the model allows is refused with reason "too_long"
     (the reference truncates with a warning, InferRuntime.cu:399-403).
 
-The scheduler touches only the cache manager's host-side accounting, so its
-decisions can be tested without a GPU.
+The decisions of a pass are taken by the host runtime (``plan_step`` of the cache
+manager: tffh_plan_step in csrc/host/host_runtime.cpp), which holds the pools and the
+block tables, and come back as a list of events that are applied to the request
+objects here.  Nothing of it touches the device, so it is tested without a GPU.
 """
 from __future__ import annotations
 
@@ -97,13 +99,8 @@ class StepOutput:
 
 
 class Scheduler:
-    def __init__(self, cache: CacheManager, max_tokens_per_step: int, max_model_len: int,
-                 native_plan: Optional[bool] = None):
+    def __init__(self, cache: CacheManager, max_tokens_per_step: int, max_model_len: int):
         self.cache = cache
-        # decisions by the C++ host runtime when the cache manager is its (None: whenever it is)
-        self.native_plan = hasattr(cache, "plan_step") if native_plan is None else bool(native_plan)
-        if self.native_plan and not hasattr(cache, "plan_step"):
-            raise ValueError("native planning needs the cache manager of the C++ host runtime")
         self.max_tokens_per_step = int(max_tokens_per_step)
         self.max_model_len = int(max_model_len)
         self.waiting: Deque[Request] = deque()
@@ -120,23 +117,6 @@ class Scheduler:
         return bool(self.waiting or self.running)
 
     # -------------------------------------------------------------- planning
-    def _capacity_tokens(self) -> int:
-        return min(p.num_pages for p in self.cache.pools) * self.cache.page_size if self.cache.pools else 1 << 60
-
-    def _free_pages(self) -> List[int]:
-        return [p.num_free for p in self.cache.pools]
-
-    def _fits(self, free: List[int], need: Sequence[int]) -> bool:
-        return all(n <= f for n, f in zip(need, free))
-
-    def _preempt(self, req: Request) -> None:
-        self.cache.release(req.id)
-        self.running.remove(req)
-        req.status = WAITING
-        req.num_preemptions += 1
-        self.counters["preemptions"] += 1
-        self.waiting.appendleft(req)
-
     def _finish(self, req: Request, reason: str, release: bool) -> None:
         if release:
             self.cache.release(req.id)
@@ -146,85 +126,9 @@ class Scheduler:
         req.finish_reason = reason
 
     def schedule(self) -> StepPlan:
-        """Decides the next step and takes its pages.  The plan's entries are ready to be
-        run; after the step, call :meth:`update` with the drawn tokens.  With the cache manager of the
-        C++ host runtime the decisions are taken there (tffh_plan_step in csrc/host/host_runtime.cpp) and
-        applied to the requests here; the loop below is their Python twin, and the tests run both in
-        lockstep."""
-        if self.native_plan:
-            return self._schedule_native()
-        preempted: List[Request] = []
-        finished: List[Request] = []
-        while True:
-            budget = self.max_tokens_per_step
-            free = self._free_pages()
-            chosen: List[Tuple[Request, int]] = []       # (request, number of tokens)
-            ok = True
-            # running requests, oldest admission first: decodes (one token), then prompt portions
-            order = sorted(self.running, key=lambda r: r.admitted_at)
-            decodes = [r for r in order if len(r) - self.cache.num_tokens(r.id) == 1]
-            prefills = [r for r in order if len(r) - self.cache.num_tokens(r.id) > 1]
-            for r in decodes + prefills:
-                if budget <= 0:
-                    break
-                n = min(len(r) - self.cache.num_tokens(r.id), budget)
-                need = self.cache.pages_needed(r.id, n)
-                if not self._fits(free, need):
-                    ok = False
-                    break
-                free = [f - x for f, x in zip(free, need)]
-                budget -= n
-                chosen.append((r, n))
-            if not ok:
-                victim = max(self.running, key=lambda r: r.admitted_at)
-                if len(self.running) == 1:
-                    # alone and still too large for the pool
-                    self._finish(victim, "out_of_memory", release=True)
-                    finished.append(victim)
-                else:
-                    self._preempt(victim)
-                    preempted.append(victim)
-                continue
-            # admissions
-            while self.waiting and budget > 0:
-                r = self.waiting[0]
-                if len(r.prompt) == 0 or len(r) > self.max_model_len:
-                    self.waiting.popleft()
-                    self._finish(r, "too_long" if len(r.prompt) else "empty_prompt", release=False)
-                    finished.append(r)
-                    continue
-                if len(r) > self._capacity_tokens():
-                    self.waiting.popleft()
-                    self._finish(r, "out_of_memory", release=False)
-                    finished.append(r)
-                    continue
-                if self.cache.slots.num_free == 0:
-                    break
-                n = min(len(r), budget)
-                blocks = -(-n // self.cache.page_size)
-                if not self._fits(free, [blocks] * len(free)):
-                    break
-                self.waiting.popleft()
-                slot = self.cache.admit(r.id)
-                assert slot is not None
-                r.status = RUNNING
-                r.admitted_at = self._admissions
-                self._admissions += 1
-                self.running.append(r)
-                free = [f - blocks for f in free]
-                budget -= n
-                chosen.append((r, n))
-            break
-        entries = []
-        for r, n in chosen:
-            start = self.cache.num_tokens(r.id)
-            got = self.cache.reserve(r.id, n)
-            assert got, "pages were counted but could not be taken"
-            toks = r.token_slice(start, n)
-            entries.append(PlanEntry(r, start, toks, samples=(start + n == len(r))))
-        return StepPlan(entries, preempted, finished)
-
-    def _schedule_native(self) -> StepPlan:
+        """Decides the next step and takes its pages.  The plan's entries are ready to be run; after the
+        step, call :meth:`update` with the drawn tokens (or :meth:`commit_launch` and, later,
+        :meth:`resolve`)."""
         cache = self.cache
         order = sorted(self.running, key=lambda r: r.admitted_at)
         waiting = list(self.waiting)

@@ -132,12 +132,20 @@ class CudaKernels:
         raise KernelError("the cache is neither contiguous nor a view of layer-major storage")
 
     # -------------------------------------------------------------- kernels
-    def embed(self, token_ids, table, out) -> None:
+    def embed(self, token_ids, table, out, scale: float = 1.0) -> None:
         self._need_cuda(token_ids, table, out)
         T, H = out.shape
         assert token_ids.dtype == torch.int32 and out.dtype == torch.float32 and table.shape[1] == H
         self._check(self.lib.tff_embed(_ptr(token_ids), _ptr(table), _c_int(_dt(table)), _ptr(out),
-                                       _c_int(T), _c_int(H), _c_int(table.shape[0]), self._stream()), "embed")
+                                       _c_int(T), _c_int(H), _c_int(table.shape[0]), _c_float(scale), self._stream()), "embed")
+        self.launches += 1
+
+    def logit_transform(self, logits, scale: float = 1.0, softcap: float = 0.0) -> None:
+        """In place: logits * scale, then softcap * tanh(. / softcap) when softcap > 0."""
+        self._need_cuda(logits)
+        assert logits.dtype == torch.float32
+        self._check(self.lib.tff_logit_transform(_ptr(logits), ctypes.c_longlong(logits.numel()), _c_float(scale),
+                                                 _c_float(softcap), self._stream()), "logit_transform")
         self.launches += 1
 
     def rmsnorm(self, x, weight, eps: float, out, row_index=None) -> None:

@@ -130,18 +130,23 @@ class FeedForward(Part):
 
 
 class Block:
-    """An arrangement of (norm, mixer, norm, feed-forward) around the residual stream."""
+    """An arrangement of a mixer, a feed-forward and norms around the residual stream.  Which norms there
+    are is the arrangement's business: the two of the pre-norm arrangement have names of their own, any
+    others come in ``extra_norms`` under the names the layer's description gave them."""
     family = "block"
     kind = ""
 
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, ffn_norm: Norm):
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Optional[Norm] = None,
+                 ffn_norm: Optional[Norm] = None, extra_norms: Optional[Dict[str, Norm]] = None):
         self.mixer = mixer
         self.feed_forward = feed_forward
         self.mixer_norm = mixer_norm
         self.ffn_norm = ffn_norm
+        self.extra_norms = dict(extra_norms or {})
 
     def parts(self):
-        return [self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward]
+        named = [self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward] + list(self.extra_norms.values())
+        return [p for p in named if p is not None]
 
     def forward(self, x: torch.Tensor, ctx: LayerContext, act_dtype: torch.dtype) -> torch.Tensor:
         raise NotImplementedError

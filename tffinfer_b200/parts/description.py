@@ -23,14 +23,18 @@ class PartSpec:
 
 @dataclass
 class LayerSpec:
-    """One layer's parts.  ``block`` names the arrangement (registry family "block").
-    ``position`` names an entry of ``ModelDescription.positions`` (or None)."""
+    """One layer's parts.  ``block`` names the arrangement (registry family "block") that decides how they
+    are wired around the residual stream; ``mixer_norm`` and ``ffn_norm`` are the norms the pre-norm
+    arrangement uses, ``extra_norms`` any further norms another arrangement names (after the mixer, after the
+    feed-forward, ...), by a name of the arrangement's choosing.  ``position`` names an entry of
+    ``ModelDescription.positions`` (or None)."""
     mixer: PartSpec
     feed_forward: PartSpec
-    mixer_norm: PartSpec
-    ffn_norm: PartSpec
+    mixer_norm: Optional[PartSpec] = None
+    ffn_norm: Optional[PartSpec] = None
     block: str = "pre_norm"
     position: Optional[str] = None
+    extra_norms: Dict[str, PartSpec] = field(default_factory=dict)
 
 
 @dataclass
@@ -55,6 +59,9 @@ class ModelDescription:
     schedule: List[ScheduleEntry]
     positions: Dict[str, PartSpec] = field(default_factory=dict)
     init_std: float = 0.02                # random-weights mode: std of matrices
+    embed_scale: float = 1.0              # the embedding rows are multiplied by this (1: as they are)
+    logit_scale: float = 1.0              # the logits are multiplied by this ...
+    logit_softcap: float = 0.0            # ... and then, if > 0, squashed: softcap * tanh(logit / softcap)
 
     def validate(self) -> "ModelDescription":
         for i, e in enumerate(self.schedule):

@@ -41,8 +41,9 @@ class Model:
             self.blocks.append(block_cls(
                 mixer=build_part("mixer", ls.mixer),
                 feed_forward=build_part("feed_forward", ls.feed_forward),
-                mixer_norm=build_part("norm", ls.mixer_norm),
-                ffn_norm=build_part("norm", ls.ffn_norm)))
+                mixer_norm=build_part("norm", ls.mixer_norm) if ls.mixer_norm is not None else None,
+                ffn_norm=build_part("norm", ls.ffn_norm) if ls.ffn_norm is not None else None,
+                extra_norms={name: build_part("norm", ps) for name, ps in ls.extra_norms.items()}))
         self.layer_position = [self.positions[ls.position] if ls.position else None for ls in desc.layers]
         self.final_norm = build_part("norm", desc.final_norm)
         self.embed: Optional[torch.Tensor] = None
@@ -97,7 +98,7 @@ class Model:
         d = self.desc
         T = batch.num_tokens
         x = torch.empty((T, d.hidden_size), dtype=torch.float32, device=self.embed.device)
-        ops.embed(batch.token_ids, self.embed, x)
+        ops.embed(batch.token_ids, self.embed, x, d.embed_scale)
         for pos in self.positions.values():
             x = pos.embed(x, batch, ops)
         for e, entry in enumerate(d.schedule):
@@ -117,4 +118,6 @@ class Model:
         hn = self.final_norm.forward(x, ops, act_dtype, row_index=batch.logit_rows)
         logits = torch.empty((R, d.vocab_size), dtype=torch.float32, device=x.device)
         ops.gemm(hn, self.lm_head, logits)
+        if d.logit_scale != 1.0 or d.logit_softcap > 0.0:
+            ops.logit_transform(logits, d.logit_scale, d.logit_softcap)
         return logits
