@@ -1,4 +1,5 @@
 """tffinfer_b200: a small, whole LLM inference engine for one B200 (sm_100a)."""
+from . import log
 from . import parts as _parts    # noqa: F401  registers the built-in parts
 from . import models as _models  # noqa: F401  registers the architectures
 from .config import EngineConfig, Qwen3Config, ConfigError

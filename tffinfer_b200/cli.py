@@ -51,6 +51,11 @@ def build_parser() -> argparse.ArgumentParser:
     e.add_argument("--max-live", type=int, default=64)
     e.add_argument("--max-tokens-per-step", type=int, default=2048)
     e.add_argument("--no-cuda-graphs", action="store_true")
+    e.add_argument("--log-level", default=None, choices=["error", "warning", "info", "debug"],
+                   help="threshold of the log lines on stderr (default: TFFINFER_LOG, else warning)")
+    e.add_argument("--kernel-trace", metavar="FILE",
+                   help="time every kernel call of the run (CUDA graphs off) and write a Chrome trace to FILE; "
+                        "the totals per kind of call go to stderr")
     r = ap.add_argument_group("random weights")
     r.add_argument("--random-config", help="config.json to make random weights for")
     r.add_argument("--random-seed", type=int, default=0)
@@ -87,10 +92,13 @@ def main(argv=None) -> int:
         print("a model folder is needed (or --random-config with --save-model)", file=sys.stderr)
         return 2
 
+    if args.log_level:
+        tff.log.set_level(args.log_level)
     dtype = args.dtype or ("bfloat16" if args.use_f16 else "float32")
     ecfg = EngineConfig(dtype=dtype, page_size=args.page_size, max_cache_tokens=args.max_cache_tokens,
                         max_live_requests=args.max_live, max_tokens_per_step=args.max_tokens_per_step,
-                        max_model_len=args.n_ctx, use_cuda_graphs=not args.no_cuda_graphs, seed=args.seed)
+                        max_model_len=args.n_ctx, use_cuda_graphs=not (args.no_cuda_graphs or args.kernel_trace),
+                        seed=args.seed)
     t0 = time.time()
     engine = tff.Engine(args.model, ecfg)
     t_load = time.time() - t0
@@ -117,7 +125,15 @@ def main(argv=None) -> int:
                              repetition_penalty=args.repetition_penalty, seed=args.seed,
                              max_new_tokens=args.n_predict, eos_token_ids=tuple(args.eos))
     t0 = time.time()
-    reqs = engine.generate(prompts, sp, return_requests=True)
+    if args.kernel_trace:
+        from tffinfer_b200.kernels.trace import KernelTrace
+        with KernelTrace(engine.runner.ops) as trace:
+            reqs = engine.generate(prompts, sp, return_requests=True)
+        trace.write_chrome_trace(args.kernel_trace)
+        for name, calls, ms in trace.summary():
+            print(f"  {name:28s} {calls:7d} calls {ms:10.3f} ms", file=sys.stderr)
+    else:
+        reqs = engine.generate(prompts, sp, return_requests=True)
     dt = time.time() - t0
     n_new = sum(len(r.generated) for r in reqs)
     if args.json:

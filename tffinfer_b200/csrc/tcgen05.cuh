@@ -34,9 +34,11 @@ static __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t 
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok;
 }
-// Bounded wait.  Returns false when it gave up or when another role already had.
-static __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+// Bounded wait: at most ``limit`` polls.  Returns false when it gave up (the flag is then raised) or when
+// another role already had.
+static __device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                       uint32_t limit) {
+    for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if (i >= 64) {
             __nanosleep(32);
@@ -45,6 +47,9 @@ static __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, 
     }
     *abort_flag = 1;
     return false;
+}
+static __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    return mbar_wait_limit(bar, parity, abort_flag, WAIT_LIMIT);
 }
 static __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int x, int y) {
     asm volatile(

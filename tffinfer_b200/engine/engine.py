@@ -14,6 +14,7 @@ from typing import Dict, Hashable, List, Optional, Sequence, Union
 
 import torch
 
+from .. import log
 from ..config import EngineConfig
 from ..sampling import Sampler, SamplingParams
 from .batch import StepEntry
@@ -142,6 +143,8 @@ class Engine:
             if record["event"] is not None:
                 record["event"].synchronize()
                 if record.get("error_word") and int(record["host"][-1]) != 0:
+                    log.error("a bounded wait inside a kernel ran out during the step of %d requests whose tokens "
+                              "were being read", len(record["samplers"]))
                     self.runner.ops.check_errors()             # raises
                 host = record["host"][:len(record["samplers"])].tolist()
             else:

@@ -14,6 +14,7 @@ from typing import Dict, Hashable, List, Optional, Sequence
 
 import torch
 
+from .. import log
 from ..cache import make_cache_manager, GroupSpec
 from ..config import EngineConfig, read_config_json
 from ..parts import Model, CacheBinding, KVNeed, StateNeed
@@ -77,8 +78,13 @@ class ModelRunner:
             held = check_tensors(tensors, expected, self.act_dtype, self.device)
         self.model.load(held, self.ops, self.act_dtype, self.device)
         del held
+        log.info("model %s: %d layers in %d runs, width %d, vocabulary %d, %s", self.desc_name(), len(self.desc.layers),
+                 len(self.desc.schedule), self.desc.hidden_size, self.desc.vocab_size, self.ecfg.dtype)
         self.max_model_len = min(self.ecfg.max_model_len or self.desc.max_position, self.desc.max_position)
         self._build_cache()
+
+    def desc_name(self) -> str:
+        return getattr(self.config, "architecture", type(self.config).__name__)
 
     # ------------------------------------------------------------------ cache
     def _build_cache(self) -> None:
@@ -148,6 +154,13 @@ class ModelRunner:
         self.table_width = max(1, -(-self.max_model_len // ps))
         self.cache = self._cache_factory(groups, ps, n_pages, self.ecfg.max_live_requests)
         self.groups = groups
+        for g, (spec, n, pb) in enumerate(zip(groups, n_pages, page_bytes)):
+            # the reference logs the size of its cache the same way (src/core/runtime/InferRuntime.cu:109-140)
+            log.info("cache group %d: %d layers, %d kv heads of %d, %s: %d pages of %d tokens (%.1f MiB), %s",
+                     g, spec.num_layers, spec.num_kv_heads, spec.head_dim,
+                     f"window {spec.window}" if spec.window else "all keys", n, ps, n * pb / 2 ** 20, self.ecfg.dtype)
+        if self.states:
+            log.info("%d state tensors of %d slots", len(self.states), self.ecfg.max_live_requests)
 
     # --------------------------------------------------------------- requests
     def add_request(self, req: Hashable) -> bool:

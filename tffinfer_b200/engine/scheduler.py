@@ -33,6 +33,7 @@ from collections import deque
 from dataclasses import dataclass, field
 from typing import Deque, Dict, Hashable, List, Optional, Sequence, Tuple
 
+from .. import log
 from ..cache import CacheManager
 from ..sampling.params import SamplingParams
 
@@ -148,11 +149,13 @@ class Scheduler:
                 self.counters["preemptions"] += 1
                 self.waiting.appendleft(r)
                 preempted.append(r)
+                log.debug("request %r gives way (pages ran out); it will be recomputed from its %d tokens", r.id, len(r))
             elif kind == cache.EVENT_FINISH:
                 (self.running if b else self.waiting).remove(r)
                 r.status = FINISHED
                 r.finish_reason = a
                 finished.append(r)
+                log.warning("request %r of %d tokens ends without running further: %s", r.id, len(r), a)
             elif kind == cache.EVENT_ADMIT:
                 self.waiting.remove(r)
                 r.status = RUNNING

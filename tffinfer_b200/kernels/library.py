@@ -284,6 +284,15 @@ class CudaKernels:
         self._check(self.lib.tff_error_word_to_host_async(_vp(pinned.data_ptr() + 4 * index), self._stream()),
                     "error_word_to_host")
 
+    def selftest_bounded_wait(self, arrive: bool, max_polls: int = 4096) -> None:
+        """Launches a kernel that waits, bounded, on a barrier at which one thread arrives (``arrive``) or
+        nobody does: in the second case the wait runs out after ``max_polls`` polls and raises the error
+        word, as a stalled pipeline inside a tcgen05 kernel would.  For testing the way from the word to
+        the caller (error_word_async, check_errors)."""
+        self._check(self.lib.tff_selftest_bounded_wait(_c_int(1 if arrive else 0), _c_int(max_polls), self._stream()),
+                    "selftest_bounded_wait")
+        self.launches += 1
+
     def check_errors(self) -> None:
         """Synchronises and raises if a bounded wait inside a kernel ran out since the last check."""
         v = self.lib.tff_kernel_error()
