@@ -160,7 +160,8 @@ def decode_run(engine, batch: int, steps: int, warmup: int, seed: int, sampler=N
     if sampler is not None:
         sampler.stop()
     engine.step_events = None
-    dev_ms = sum(a.elapsed_time(b) for a, b in ev)
+    per_step = sorted(a.elapsed_time(b) for a, b in ev)
+    dev_ms = sum(per_step)
     ctx1 = sum(len(engine.requests[i]) for i in ids) / batch
     launches = ops.launches - launches0
     ops.check_errors()
@@ -169,7 +170,9 @@ def decode_run(engine, batch: int, steps: int, warmup: int, seed: int, sampler=N
         engine.abort(i)
     return {"tok_s": batch * steps / (dev_ms / 1e3), "ms_per_step": dev_ms / steps,
             "e2e_tok_s": batch * steps / wall, "launches": launches, "mean_context": (ctx0 + ctx1) / 2,
-            "h2d_bytes": h2d, "d2h_bytes": 4 * batch + 4}      # drawn tokens and the kernels' error word
+            "h2d_bytes": h2d, "d2h_bytes": 4 * batch + 4,      # drawn tokens and the kernels' error word
+            "p50_ms": per_step[len(per_step) // 2], "p99_ms": per_step[min(len(per_step) - 1, int(0.99 * len(per_step)))],
+            "max_ms": per_step[-1]}
 
 
 def prefill_run(engine, iters: int, warmup: int, seed: int):
@@ -245,11 +248,15 @@ def run_workload(name: str, layers: int = 0) -> int:
     ids = [engine.add_request(p, sp, key=i) for i, p in enumerate(prompts)]
     steps = 0
     first_token_at = {}
+    step_s = []
     while engine.has_unfinished():
+        t_step = time.perf_counter()
         for o in engine.step():
             if o.token is not None and o.request_id not in first_token_at:
                 first_token_at[o.request_id] = time.perf_counter() - t0
-        steps += 1
+        step_s.append(time.perf_counter() - t_step)       # host time of a step: with steps launched ahead, the
+        steps += 1                                        # device time of the step before
+    step_s.sort()
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
     engine.runner.ops.check_errors()
@@ -258,6 +265,8 @@ def run_workload(name: str, layers: int = 0) -> int:
     print(json.dumps({"workload": name, "layers": cfg.num_layers, "requests": len(ids), "prompt_tokens": sum(lens),
                       "generated_tokens": gen, "seconds": round(dt, 3), "steps": steps,
                       "total_tok_s": round((sum(lens) + gen) / dt, 1), "generated_tok_s": round(gen / dt, 1),
+                      "step_ms_p50": round(1e3 * step_s[len(step_s) // 2], 3),
+                      "step_ms_p99": round(1e3 * step_s[min(len(step_s) - 1, int(0.99 * len(step_s)))], 3),
                       "mean_time_to_first_token_s": round(sum(first_token_at.values()) / max(1, len(first_token_at)), 3),
                       "pages_high_water": st["pages_high_water"], "pages_total": st["pages_total"],
                       "preemptions": st["preemptions"], "dtype": "bf16" if dtype == "bfloat16" else "fp32",
@@ -306,11 +315,21 @@ def main() -> int:
     clocks = ClockSampler()
     main_run = decode_run(engine, args.batch, args.steps, warmup, seed=1, sampler=clocks)
     points = {}
+    points_roofline = {}
     prefill = None
+
+    def hbm_fraction(run, batch):
+        """bytes the step has to read (every weight once, the cache of the live requests) / its time / the peak"""
+        b = mb["weights_read_per_step"] + batch * run["mean_context"] * mb["kv_bytes_per_token"]
+        return b / (run["ms_per_step"] / 1e3) / 1e9 / peaks["hbm_gbs"]
+
     if not args.skip_points:
         small_steps = min(args.steps, 32)
-        points["decode_b1"] = round(decode_run(engine, 1, small_steps, warmup, seed=2)["tok_s"], 1)
-        points["decode_b64"] = round(decode_run(engine, 64, small_steps, warmup, seed=3)["tok_s"], 1)
+        for name, b, seed in (("decode_b1", 1, 2), ("decode_b64", 64, 3)):
+            run = decode_run(engine, b, small_steps, warmup, seed=seed)
+            points[name] = round(run["tok_s"], 1)
+            points_roofline[name] = {"ms_per_step": round(run["ms_per_step"], 4), "hbm_frac": round(hbm_fraction(run, b), 4),
+                                     "p50_ms": round(run["p50_ms"], 4), "p99_ms": round(run["p99_ms"], 4)}
         pms = prefill_run(engine, iters=5, warmup=3, seed=4)
         T = PROMPT_LEN
         flops = 2 * T * mb["layer_params"] * cfg.num_layers \
@@ -337,6 +356,8 @@ def main() -> int:
         "e2e": {"value": round(main_run["e2e_tok_s"], 1), "unit": "tok/s",
                 "h2d_bytes_per_step": main_run["h2d_bytes"], "d2h_bytes_per_step": main_run["d2h_bytes"]},
         "gpu_launches": main_run["launches"],
+        "latency_ms": {"p50": round(main_run["p50_ms"], 4), "p99": round(main_run["p99_ms"], 4),
+                       "max": round(main_run["max_ms"], 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peaks["hbm_gbs"], 4), "peaks": peaks["source"]},
         "clocks": clocks.summary(),
@@ -344,6 +365,7 @@ def main() -> int:
     if prefill is not None:
         out["prefill"] = prefill
         out["points"] = points
+        out["points_roofline"] = points_roofline
     print(json.dumps(out))
     return 0
 

@@ -133,6 +133,11 @@ class CpuOps:
                 pr = torch.softmax(s, 0)
                 out[t, h * d:(h + 1) * d] = (pr @ V[:, h // G, :]).to(out.dtype)
 
+    def gated_mlp(self, h, w_gate_up, w_down, residual, inter):
+        act = torch.empty((h.shape[0], inter), dtype=h.dtype, device=h.device)
+        self.gemm_swiglu(h, w_gate_up, act)
+        self.gemm(act, w_down, residual, residual=residual)
+
     def gemm_swiglu(self, a, w_gate_up, out):
         gu = a.to(F64) @ w_gate_up.to(F64).t()
         I = out.shape[1]

@@ -228,6 +228,31 @@ def test_gemm_tc_explicit_plans(ops, M, N, K, swap, bn, splits):
     ops.check_errors()
 
 
+@pytest.mark.parametrize("M,H,I", [(1, 4096, 12288), (8, 4096, 12288), (16, 520, 192), (7, 264, 64), (4, 5120, 17408),
+                                   (3, 64, 128)])
+def test_norm_gate_up_product_and_swiglu_as_one_kernel(ops, M, H, I):
+    """act = silu(gate) * up of RMSNorm(x) W^T for a decode step of at most 16 tokens: one kernel in which the
+    CTAs of a cluster share a tile's K range and meet in the first one's shared memory; against the plain twins
+    of the norm, the product and the SwiGLU kernel.  Then the whole feed-forward in two launches."""
+    cpu = CpuOps()
+    from tffinfer_b200.kernels.library import DeferredNorm
+    x = g((M, H), torch.float32, 153, 2.0)
+    nw = 1 + 0.1 * g((H,), torch.float32, 154)
+    wg, wu = g((I, H), torch.bfloat16, 155, 0.05), g((I, H), torch.bfloat16, 156, 0.05)
+    wd = g((H, I), torch.bfloat16, 151, 0.05)
+    h = torch.empty(M, H, dtype=torch.bfloat16); cpu.rmsnorm(x, nw, 1e-5, h)
+    want = x.clone(); cpu.gated_mlp(h, cpu.merge_gate_up(wg, wu), wd, want, I)
+    xd = x.clone().to(DEV)
+    assert ops.can_fold_norm(xd, nw.to(DEV), torch.bfloat16)
+    launches = ops.launches
+    ops.gated_mlp(DeferredNorm(xd, nw.to(DEV), 1e-5, torch.bfloat16, ops), ops.merge_gate_up(wg.to(DEV), wu.to(DEV)),
+                  wd.to(DEV), xd, I)
+    assert ops.launches == launches + 2
+    ops.check_errors()
+    # x * w is rounded to bfloat16 where the separate kernel rounds (x * r) * w: a bfloat16 rounding apart
+    assert rel_err(xd - x.to(DEV), want - x) < 2e-2
+
+
 def _paged_case(nq, nkv, d, page, lens_new, lens_old, window, dt, seed, layers=2, layer=1, rot=None):
     """Builds a batch of requests with ``lens_old`` tokens already cached and ``lens_new`` new ones,
     scattered pages, and returns everything both implementations need."""

@@ -29,6 +29,12 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 
 
+def extra_flags_from_env() -> List[str]:
+    """More flags for nvcc from TFFINFER_NVCC_FLAGS (for instance -DTFF_DEC_STAGES=2 to try another depth of
+    the decode attention's ring); they enter the stamp, so changing them rebuilds the library."""
+    return os.environ.get("TFFINFER_NVCC_FLAGS", "").split()
+
+
 def sources() -> List[str]:
     return sorted(f for f in os.listdir(CSRC_DIR) if f.endswith(".cu"))
 
@@ -59,7 +65,7 @@ def _source_hash() -> str:
         h.update(f.encode())
         with open(os.path.join(CSRC_DIR, f), "rb") as fh:
             h.update(fh.read())
-    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
+    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS + extra_flags_from_env()).encode())
     return h.hexdigest()
 
 
@@ -121,7 +127,7 @@ def compile_all(bdir: str, verbose: bool = True, extra_flags: Optional[List[str]
     srcs = sources()
     t0 = time.time()
     _say(f"compiling {len(srcs)} CUDA sources for sm_100a with {nvcc} into {bdir}", verbose)
-    flags = ARCH_FLAGS + NVCC_FLAGS + (extra_flags or [])
+    flags = ARCH_FLAGS + NVCC_FLAGS + extra_flags_from_env() + (extra_flags or [])
     stop = threading.Event()
     hb = threading.Thread(target=_heartbeat, args=(stop, t0, verbose, "kernels"), daemon=True)
     hb.start()

@@ -291,6 +291,17 @@ int launch_tc(const CUtensorMap& tl, const CUtensorMap& tc, const CUtensorMap& t
     const long long n_tiles = (long long)((rows_lane + BM - 1) / BM) * ((rows_col + BN - 1) / BN);
     const long long units = stream_k ? n_tiles * ((K + BK - 1) / BK) : n_tiles;
     long long ctas = (long long)tff_num_sms() * Cfg::kCtasPerSm;
+    // Products of a decode layer follow one another with a small kernel in between, and a CTA of the product
+    // after next can only become resident -- and ask for its first ring of weight tiles before it waits for its
+    // predecessor -- where an SM has room.  A grid that fills every CTA slot leaves none: the next product then
+    // starts from empty rings when this one has drained.  The 16-column configuration therefore leaves about a
+    // twelfth of its slots free (measured at the Qwen3-8B shape, 8 requests: 3.66 ms a step with 2.75 CTAs an SM,
+    // 3.72 with 2.6, 3.85 with all 3).  The output projection alone is one long kernel and takes every slot.
+    if (SWAP && BN == 16 && rows_lane < 65536) {
+        static int x100 = -1;
+        if (x100 < 0) { const char* v = getenv("TFFINFER_GEMM_CTAS_X100"); x100 = v ? atoi(v) : 275; if (x100 < 100 || x100 > 300) x100 = 275; }
+        ctas = (long long)tff_num_sms() * x100 / 100;
+    }
     if (ctas <= 0) return TFF_ERR_LAUNCH;
     if (ctas > units) ctas = units;
     return tff_launch_pdl(kern, dim3((unsigned)ctas), dim3(NUM_THREADS), (size_t)Cfg::kSmemBytes, stream, tl, tc, to,

@@ -68,6 +68,24 @@ def nearest_power_of_two(x: float) -> int:
     return b
 
 
+class DeferredNorm:
+    """A norm that has not been run yet: the float32 rows ``x``, the weight and eps of an RMSNorm whose
+    output only feeds a product of the kernel library.  ``CudaKernels.gated_mlp`` takes it in place of the
+    activation rows and runs norm, product and SwiGLU as one kernel when the shape allows (decode steps of at
+    most 16 tokens in bfloat16: csrc/gemm_tc_cluster.cu); otherwise, and in ``qkv_project``, the norm kernel
+    runs first (``materialize``)."""
+    def __init__(self, x, weight, eps, out_dtype, ops):
+        self.x, self.weight, self.eps, self.out_dtype, self.ops = x, weight, float(eps), out_dtype, ops
+        self.shape = x.shape
+        self.dtype = out_dtype
+        self.device = x.device
+
+    def materialize(self):
+        out = torch.empty(self.x.shape, dtype=self.out_dtype, device=self.x.device)
+        self.ops.rmsnorm(self.x, self.weight, self.eps, out)
+        return out
+
+
 class CudaKernels:
     """Loads (building first if needed) the sm_100a kernel library."""
 
@@ -188,6 +206,8 @@ class CudaKernels:
                                            self._stream()), "gemm_simt")
         self.launches += 1
 
+    FOLD_MAX_M = 16           # up to this many rows the norm and the SwiGLU kernel are folded into the products
+    FOLD_DECODE = os.environ.get("TFFINFER_FOLD_DECODE", "1") != "0"
     SWAP_MAX_M = 256          # up to this many rows the weights are the 128-row operand
     USE_SM_PAIRS = os.environ.get("TFFINFER_SM_PAIRS", "1") != "0"   # prompt-sized products on tcgen05 cta_group::2
     NUM_SMS = 0               # SMs of the device, read from it when the library is loaded
@@ -335,6 +355,39 @@ class CudaKernels:
             buf.zero_()
             self._acc_zero[buf.data_ptr()] = True
 
+    # ------------------------------------------------------- folded decode products
+    def can_fold_norm(self, x, weight, out_dtype) -> bool:
+        """Whether an RMSNorm of these rows may be handed to the products as a DeferredNorm."""
+        return (self.FOLD_DECODE and x.is_cuda and out_dtype == torch.bfloat16 and x.dtype == torch.float32
+                and x.dim() == 2 and x.shape[0] <= self.FOLD_MAX_M and x.shape[1] % 8 == 0 and x.is_contiguous()
+                and weight.dtype == torch.float32 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+    def _foldable_weight(self, w) -> bool:
+        return w.dtype == torch.bfloat16 and w.is_contiguous() and w.data_ptr() % 16 == 0 and w.shape[1] % 8 == 0
+
+    def gated_mlp(self, h, w_gate_up, w_down, residual, inter: int) -> None:
+        """residual += down(silu(gate(h)) * up(h)); ``h`` the activation rows or a DeferredNorm of them.
+        A decode step of at most FOLD_MAX_M tokens in bfloat16 whose norm has been deferred runs two kernels:
+        norm, gate/up product and SwiGLU as one (clusters of CTAs share a tile's K range), then the down
+        product.  Everything else runs the products and kernels one by one."""
+        T = h.shape[0]
+        if isinstance(h, DeferredNorm):
+            if (self.gate_up_block(inter) == 64 and self._foldable_weight(w_gate_up)
+                    and residual.is_cuda and residual.dtype == torch.float32):
+                act = torch.empty((T, inter), dtype=torch.bfloat16, device=residual.device)
+                self._need_cuda(h.x, h.weight, w_gate_up, act)
+                assert tuple(w_gate_up.shape) == (2 * inter, h.x.shape[1])
+                self._check(self.lib.tff_gemm_tc_cluster_swiglu(
+                    _ptr(h.x), _ptr(h.weight), _c_float(h.eps), _ptr(w_gate_up), _c_int(T), _c_int(h.x.shape[1]),
+                    _ptr(act), _c_int(inter), self._stream()), "gemm_tc_cluster_swiglu")
+                self.launches += 1
+                self.gemm(act, w_down, residual, residual=residual)
+                return
+            h = h.materialize()
+        act = torch.empty((T, inter), dtype=h.dtype, device=h.device)
+        self.gemm_swiglu(h, w_gate_up, act)
+        self.gemm(act, w_down, residual, residual=residual)
+
     def swiglu(self, gate_up, out, block: int = 0) -> None:
         """out[t, i] = silu(gate[t, i]) * up[t, i]; gate_up float32 or of out's type, [gate | up] (block = 0) or
         alternating in blocks of ``block`` columns."""
@@ -396,6 +449,8 @@ class CudaKernels:
         of it in the epilogue of the product on pairs of SMs; everything else is the product into a float32 buffer
         followed by qk_norm_rope_kv_write."""
         T, K = h.shape
+        if isinstance(h, DeferredNorm):
+            h = h.materialize()
         fused = (self.USE_SM_PAIRS and T > self.SWAP_MAX_M and d == 128 and h.dtype == torch.bfloat16
                  and w_qkv.dtype == torch.bfloat16 and q_out.dtype == torch.bfloat16 and K % 8 == 0
                  and (table is None or rot_dim == d) and (kv_cache is None or kv_cache.dtype == torch.bfloat16)
@@ -448,7 +503,11 @@ class CudaKernels:
         if max_q_len * (nq // nkv) > 16:
             return 1                                   # portions: enough tiles already
         b = nearest_power_of_two(num_requests)
-        return max(1, min(16, 2 * self.NUM_SMS // (b * nkv)))     # one wave of two CTAs per SM
+        # One wave of two CTAs per SM.  With more work items than that the grid runs in rounds and the last one is
+        # seldom full (64 requests of 8 heads on 296 slots: two rounds for 1.73 rounds' worth of work); cutting
+        # the items so that the rounds fill was measured and lost (4 shares: 7.36 against 6.76 ms a step at 64
+        # requests): every share pays its own ramp, and the partial results another pass.
+        return max(1, min(16, 2 * self.NUM_SMS // (b * nkv)))
 
     @staticmethod
     def key_split_class(kv_lens) -> int:

@@ -15,6 +15,8 @@ from .base import FeedForward, WeightSpec, MATRIX
 
 @register_part("feed_forward", "swiglu")
 class SwiGLU(FeedForward):
+    takes_deferred_norm = True        # the input only feeds the gate/up product
+
     def __init__(self, hidden_size: int, intermediate_size: int, prefix: str = ""):
         super().__init__(prefix)
         self.hidden_size = int(hidden_size)
@@ -36,8 +38,5 @@ class SwiGLU(FeedForward):
         self.w_down = tensors["down_proj.weight"]
 
     def forward(self, h, ctx, residual):
-        ops = ctx.ops
-        act = torch.empty((h.shape[0], self.intermediate_size), dtype=h.dtype, device=h.device)
-        ops.gemm_swiglu(h, self.w_gate_up, act)
-        ops.gemm(act, self.w_down, residual, residual=residual)
+        ctx.ops.gated_mlp(h, self.w_gate_up, self.w_down, residual, self.intermediate_size)
         return residual

@@ -26,6 +26,15 @@ class RMSNorm(Norm):
     def load(self, tensors, ops, act_dtype) -> None:
         self.weight = tensors["weight"]
 
+    def deferred(self, x, ops, out_dtype):
+        """The norm of ``x`` as an object that the kernel library's products can fold in, or None when the
+        library cannot (then ``forward`` runs the norm kernel)."""
+        can = getattr(ops, "can_fold_norm", None)
+        if can is None or not can(x, self.weight, out_dtype):
+            return None
+        from ..kernels.library import DeferredNorm
+        return DeferredNorm(x, self.weight, self.eps, out_dtype, ops)
+
     def forward(self, x, ops, out_dtype, row_index=None):
         rows = x.shape[0] if row_index is None else row_index.shape[0]
         out = torch.empty((rows, self.dim), dtype=out_dtype, device=x.device)
