@@ -16,11 +16,19 @@
 // memory, because a page's unused slots, and shared memory that was not written, may hold
 // anything.
 // Every mbarrier wait is bounded; when one runs out the CTA raises the library's error word.
-#include "common.cuh"
-#include "tma_host.h"
+#include "tcgen05.cuh"
 #include "attention_common.h"
 
 namespace {
+
+// mbarrier, TMA and tensor-memory wrappers shared with the product kernels
+using tc5::smem_u32;
+using tc5::mbar_init;
+using tc5::mbar_expect_tx;
+using tc5::mbar_arrive;
+using tc5::mbar_try_wait;
+using tc5::mbar_wait;
+
 
 constexpr int BLOCK_N = 64;
 #ifndef TFF_DEC_STAGES
@@ -31,38 +39,7 @@ constexpr int BLOCK_N = 64;
 #endif
 constexpr int NSTAGES = TFF_DEC_STAGES;
 constexpr int NTHREADS = 160;
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok;
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (i >= 64) {
-            __nanosleep(32);
-            if (*abort_flag) return false;
-        }
-    }
-    *abort_flag = 1;
-    return false;
-}
 __device__ __forceinline__ void compute_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
