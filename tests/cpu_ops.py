@@ -72,6 +72,13 @@ class CpuOps:
         table[..., 0] = torch.cos(ang).to(torch.float32)
         table[..., 1] = torch.sin(ang).to(torch.float32)
 
+    def attend(self, h, w_qkv, q_w, k_w, eps, table, rot_dim, batch, block_table, kv_cache, kv_layer, page_size, out,
+               nq, nkv, d, scale, window, write_cache):
+        q = torch.empty((h.shape[0], nq * d), dtype=out.dtype, device=out.device)
+        self.qkv_project(h, w_qkv, q, q_w, k_w, eps, table, rot_dim, batch, block_table, kv_cache, kv_layer, page_size,
+                         nq, nkv, d, write_cache)
+        self.attention(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, scale, window)
+
     def qkv_project(self, h, w_qkv, q_out, q_w, k_w, eps, table, rot_dim, batch, block_table, kv_cache,
                     kv_layer, page_size, nq, nkv, d, write_cache):
         qkv = self.projection_buffer(h.shape[0], (nq + 2 * nkv) * d, h.device, h.dtype)

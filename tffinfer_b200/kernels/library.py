@@ -477,6 +477,22 @@ class CudaKernels:
             _c_int(nq), _c_int(nkv), self._stream()), "gemm_tc_qkv_rope")
         self.launches += 1
 
+    def attend(self, h, w_qkv, q_w, k_w, eps, table, rot_dim, batch, block_table, kv_cache, kv_layer, page_size, out,
+               nq, nkv, d, scale, window, write_cache) -> None:
+        """The whole mixer between its input rows and its output projection: q/k/v projection of ``h``, per-head
+        RMSNorm of q and k, rotation, cache write, attention over the paged cache -> out [T, nq*d].  How many
+        kernels that is, is decided here: prompt portions with heads of 128 do everything up to the cache write in
+        the projection's epilogue (qkv_project); a decode step runs projection, q/k-norm + rotation + write, and
+        attention (with the merge of its key shares).  A decode attention that took the projection's float32
+        accumulators and finished queries, new keys and new values itself was built and measured: one launch
+        fewer and 0.05 ms a step slower at the Qwen3-8B shape (under programmatic dependent launch the small
+        kernel's time already hid behind the attention's first loads of old keys), so it was not kept."""
+        T = h.shape[0]
+        q = torch.empty((T, nq * d), dtype=out.dtype, device=out.device)
+        self.qkv_project(h, w_qkv, q, q_w, k_w, eps, table, rot_dim, batch, block_table, kv_cache, kv_layer, page_size,
+                         nq, nkv, d, write_cache)
+        self.attention(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, scale, window)
+
     def attention(self, q, batch, block_table, kv_cache, kv_layer, page_size, out,
                   nq, nkv, d, scale, window) -> None:
         """q [T, nq*d] (normed, rotated) against the paged cache -> out [T, nq*d]."""

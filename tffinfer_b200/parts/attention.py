@@ -72,17 +72,13 @@ class GQAttention(Mixer):
     def forward(self, h, ctx: LayerContext, residual):
         ops, batch = ctx.ops, ctx.batch
         T = h.shape[0]
-        # projection, q/k norm, rotation and cache write: the kernel library may do them in one kernel; the
-        # projection's accumulators stay in float32 until q and k have been normalised
-        q = torch.empty((T, self.q_width), dtype=h.dtype, device=h.device)
+        # projection, q/k norm, rotation, cache write and attention: how many kernels that is, is the kernel
+        # library's business; the projection's accumulators stay in float32 until q and k have been normalised
         rot = ctx.position.rotary() if ctx.position is not None else None
-        ops.qkv_project(
-            h, self.w_qkv, q, self.q_norm_w, self.k_norm_w, self.qk_norm_eps,
-            rot[0] if rot else None, rot[1] if rot else 0,
-            batch, ctx.block_table, ctx.kv_cache, ctx.kv_layer, ctx.page_size,
-            self.num_heads, self.num_kv_heads, self.head_dim, ctx.write_cache)
         attn = torch.empty((T, self.q_width), dtype=h.dtype, device=h.device)
-        ops.attention(q, batch, ctx.block_table, ctx.kv_cache, ctx.kv_layer, ctx.page_size,
-                      attn, self.num_heads, self.num_kv_heads, self.head_dim, self.scale, self.window)
+        ops.attend(h, self.w_qkv, self.q_norm_w, self.k_norm_w, self.qk_norm_eps,
+                   rot[0] if rot else None, rot[1] if rot else 0,
+                   batch, ctx.block_table, ctx.kv_cache, ctx.kv_layer, ctx.page_size, attn,
+                   self.num_heads, self.num_kv_heads, self.head_dim, self.scale, self.window, ctx.write_cache)
         ops.gemm(attn, self.w_o, residual, residual=residual)
         return residual
