@@ -297,11 +297,10 @@ int launch_tc(const CUtensorMap& tl, const CUtensorMap& tc, const CUtensorMap& t
     // starts from empty rings when this one has drained.  The 16-column configuration therefore leaves about a
     // twelfth of its slots free (measured at the Qwen3-8B shape, 8 requests: 3.66 ms a step with 2.75 CTAs an SM,
     // 3.72 with 2.6, 3.85 with all 3).  The output projection alone is one long kernel and takes every slot.
-    if (SWAP && BN == 16 && rows_lane < 65536) {
-        static int x100 = -1;
-        if (x100 < 0) { const char* v = getenv("TFFINFER_GEMM_CTAS_X100"); x100 = v ? atoi(v) : 275; if (x100 < 100 || x100 > 300) x100 = 275; }
-        ctas = (long long)tff_num_sms() * x100 / 100;
-    }
+    // (Asking the L2 for the successor's first weight tiles from this product's producers, once they have asked
+    // for their own last tile, was measured too: 0.17 ms a step slower -- the prefetches delay the tail they
+    // were meant to use.)
+    if (SWAP && BN == 16 && rows_lane < 65536) ctas = tff_decode_gemm_ctas(units);
     if (ctas <= 0) return TFF_ERR_LAUNCH;
     if (ctas > units) ctas = units;
     return tff_launch_pdl(kern, dim3((unsigned)ctas), dim3(NUM_THREADS), (size_t)Cfg::kSmemBytes, stream, tl, tc, to,

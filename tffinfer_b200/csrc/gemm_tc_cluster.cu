@@ -323,7 +323,7 @@ int launch_cluster_gemm(const CUtensorMap& tw, const ClusterGemmParams& p, cudaS
     // most one per K block
     static int cs_max = -1;
     if (cs_max < 0) { const char* e = getenv("TFFINFER_CLUSTER_MAX"); cs_max = e ? atoi(e) : 8; if (cs_max < 1 || cs_max > 8) cs_max = 8; }
-    int cs = (int)((long long)tff_num_sms() * 275 / 100 / tiles);     // as in gemm_tc.cu: not every CTA slot is taken
+    int cs = (int)(tff_decode_gemm_ctas(1ll << 40) / tiles);         // as in gemm_tc.cu: not every CTA slot is taken
     cs = cs < 1 ? 1 : (cs > cs_max ? cs_max : cs);
     if (cs > kbt) cs = kbt;
     cudaLaunchConfig_t cfg = {};

@@ -123,6 +123,13 @@ int tff_num_sms() {
     return n;
 }
 
+long long tff_decode_gemm_ctas(long long units) {
+    static int x100 = -1;
+    if (x100 < 0) { const char* v = getenv("TFFINFER_GEMM_CTAS_X100"); x100 = v ? atoi(v) : 275; if (x100 < 100 || x100 > 300) x100 = 275; }
+    long long ctas = (long long)tff_num_sms() * x100 / 100;
+    return ctas > units ? units : ctas;
+}
+
 // The SM count of the current device, for planners outside this library (they must cut work the way
 // the launchers size their grids).
 TFF_API int tff_sm_count() { return tff_num_sms(); }

@@ -23,3 +23,7 @@ int* tff_device_error_flag();
 
 // Number of SMs of the current device (0 on failure).
 int tff_num_sms();
+
+// CTAs of a decode-sized product (16 token columns) over ``units`` (tile, K block) units: about a twelfth of the
+// SMs' three-a-piece CTA slots stay free, so that a CTA of the product after next can become resident early.
+long long tff_decode_gemm_ctas(long long units);
