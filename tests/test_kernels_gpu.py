@@ -316,6 +316,24 @@ def test_qk_norm_rope_write_then_attention(ops, case, dt):
     assert rel_err(out_g, out_c) < (3e-6 if dt == torch.float32 else 1e-2)
 
 
+@pytest.mark.parametrize("M,H,I", [(16, 4096, 12288), (5, 4096, 12288), (11, 520, 192), (16, 264, 64), (1, 64, 128)])
+def test_gate_up_product_with_swiglu_in_the_cluster_for_normalised_rows(ops, M, H, I):
+    """Decode steps whose norm was not deferred (another block arrangement): the rows come normalised in bfloat16,
+    the clustered product applies SwiGLU itself; the feed-forward is two launches."""
+    cpu = CpuOps()
+    h = g((M, H), torch.bfloat16, 180)
+    wg, wu = g((I, H), torch.bfloat16, 181, 0.05), g((I, H), torch.bfloat16, 182, 0.05)
+    wd = g((H, I), torch.bfloat16, 183, 0.05)
+    x = g((M, H), torch.float32, 184)
+    want = x.clone(); cpu.gated_mlp(h, cpu.merge_gate_up(wg, wu), wd, want, I)
+    xd = x.clone().to(DEV)
+    launches = ops.launches
+    ops.gated_mlp(h.to(DEV), ops.merge_gate_up(wg.to(DEV), wu.to(DEV)), wd.to(DEV), xd, I)
+    assert ops.launches == launches + 2
+    ops.check_errors()
+    assert rel_err(xd - x.to(DEV), want - x) < 1.2e-2
+
+
 @pytest.mark.parametrize("nq,nkv,page,new,old,K,norm,rope", [
     (32, 8, 16, [300, 450], [17, 0], 1024, True, True),      # two requests, the first with tokens cached
     (40, 8, 16, [777], [100], 512, True, True),              # 56 heads: 28 tiles of two heads

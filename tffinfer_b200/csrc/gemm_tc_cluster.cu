@@ -1,5 +1,5 @@
-// The gate/up projection of a decode step (at most 16 tokens) as ONE kernel with the RMSNorm ahead of it and
-// the SwiGLU behind it:
+// The gate/up projection of a decode step as ONE kernel with the SwiGLU behind it and, for steps of at most 16
+// tokens, the RMSNorm ahead of it:
 //
 //   y[m, n] = r[m] * sum_k bf16(x[m, k] * w_norm[k]) * W[n, k],   r[m] = rsqrt(mean_k x[m, k]^2 + eps)
 //   act[m, i] = bf16(silu(y_gate[m, i]) * y_up[m, i])
@@ -29,6 +29,10 @@
 //   warp 1      TMEM allocation, MMA issue (one lane)
 //   warps 2-5   activation tiles; then partial sums out of tensor memory, the cluster reduction, the tail
 // A stage is full when its weight tile has landed and its activation tile has been written.
+// Rows that come normalised already (FOLD_NORM = false: a block arrangement that did not defer its norm) arrive as
+// bfloat16 by TMA.  The kernel is a template on the number of token columns; 32 and 64 columns (steps of 17 to 64
+// tokens, rows by TMA) were measured and are not instantiated: 7.05 against 6.85 ms a step at 64 requests, even at
+// 32, although they save the SwiGLU kernel and the accumulators' float32 round trip.
 // Every mbarrier wait is bounded; the two cluster barriers are reached by every thread whatever happened.
 #include "tcgen05.cuh"
 
@@ -36,21 +40,24 @@ namespace {
 
 using namespace tc5;
 
-constexpr int CBN = 16;                                   // token columns
-constexpr int C_STAGES = 4;
 constexpr int C_THREADS = 192;
 constexpr int C_CTAS_PER_SM = 3;
 constexpr int C_W_BYTES = BM * BK * 2;                    // 16 KB weight tile
-constexpr int C_B_BYTES = CBN * BK * 2;                   // 2 KB bfloat16 activation tile
-constexpr int C_STAGE_BYTES = C_W_BYTES + C_B_BYTES;      // 18 KB, a multiple of 1024
-constexpr int C_SMEM_BYTES = C_STAGES * C_STAGE_BYTES + 1024 + 256;
-static_assert(C_STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte alignment of swizzled tiles");
-static_assert(C_CTAS_PER_SM * (C_SMEM_BYTES + 1024) <= 228 * 1024, "the CTAs meant to share an SM do not fit");
-static_assert(BM * CBN * 4 + 5 * CBN * 4 <= C_STAGES * C_STAGE_BYTES, "the reduction buffer reuses the ring");
+
+template <int BN> struct ClusterCfg {
+    static constexpr int kStages = BN == 16 ? 4 : 3;
+    static constexpr int kBBytes = BN * BK * 2;            // bfloat16 activation tile: 2, 4 or 8 KB
+    static constexpr int kStageBytes = C_W_BYTES + kBBytes;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+    static constexpr int kTmemCols = BN < 32 ? 32 : BN;
+    static_assert(kStageBytes % 1024 == 0, "stages must keep the 1024-byte alignment of swizzled tiles");
+    static_assert(C_CTAS_PER_SM * (kSmemBytes + 1024) <= 228 * 1024, "the CTAs meant to share an SM do not fit");
+    static_assert(BM * BN * 4 + 5 * 16 * 4 <= kStages * kStageBytes, "the reduction buffer reuses the ring");
+};
 
 struct ClusterGemmParams {
-    const float* x;                       // [M, K] float32
-    const float* norm_w; float eps;       // input RMSNorm
+    const float* x;                       // FOLD_NORM: [M, K] float32
+    const float* norm_w; float eps;       // FOLD_NORM: input RMSNorm
     int M, N, K;
     bf16* act; int inter;                 // [M, inter] bfloat16 out
     int* error_flag;
@@ -81,23 +88,28 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+template <int BN, bool FOLD_NORM>
 __global__ void __launch_bounds__(C_THREADS, C_CTAS_PER_SM)
-gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const ClusterGemmParams p) {
+gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_h,
+                       const ClusterGemmParams p) {
+    static_assert(!FOLD_NORM || BN == 16, "the activation tile is made in the kernel for 16 token columns only");
+    using Cfg = ClusterCfg<BN>;
+    constexpr int STAGES = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
-    const uint32_t bars = base + C_STAGES * C_STAGE_BYTES;
-    auto full_bar = [&](int s) { return bars + 8u * s; };                    // weights landed and activations written
-    auto empty_bar = [&](int s) { return bars + 8u * (C_STAGES + s); };      // the MMAs have read the stage
-    const uint32_t tfull_bar = bars + 8u * (2 * C_STAGES);
-    uint8_t* tail = gen_base + C_STAGES * C_STAGE_BYTES + 8 * (2 * C_STAGES + 1);
+    const uint32_t bars = base + STAGES * Cfg::kStageBytes;
+    auto full_bar = [&](int s) { return bars + 8u * s; };                    // weights landed and activations there
+    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };        // the MMAs have read the stage
+    const uint32_t tfull_bar = bars + 8u * (2 * STAGES);
+    uint8_t* tail = gen_base + STAGES * Cfg::kStageBytes + 8 * (2 * STAGES + 1);
     volatile uint32_t* tmem_slot = (volatile uint32_t*)tail;
     volatile int* abort_flag = (volatile int*)(tail + 4);
-    // after the main loop the ring is free: the first CTA's holds the sums of the whole cluster
-    float* red = reinterpret_cast<float*>(gen_base);                  // [128 features][16 tokens]
-    float* sumsq = red + BM * CBN;                                    // [16 tokens]
-    float* ss_part = sumsq + CBN;                                     // [4 warps][16 tokens]
-    const uint32_t red_addr = base, sumsq_addr = base + BM * CBN * 4;
+    // after the main loop the ring is free: each CTA's holds its share, the first CTA's then the sums of the cluster
+    float* red = reinterpret_cast<float*>(gen_base);                  // [128 features][BN tokens]
+    float* sumsq = red + BM * BN;                                     // [16 tokens]          (FOLD_NORM)
+    float* ss_part = sumsq + 16;                                      // [4 warps][16 tokens] (FOLD_NORM)
+    const uint32_t red_addr = base, sumsq_addr = base + BM * BN * 4;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank(), csize = cluster_nctarank();
@@ -106,13 +118,14 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const ClusterGe
     const int kb0 = (int)((long long)kbt * rank / csize), kb1 = (int)((long long)kbt * (rank + 1) / csize);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < C_STAGES; ++s) { mbar_init(full_bar(s), 2); mbar_init(empty_bar(s), 1); }
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), FOLD_NORM ? 2 : 1); mbar_init(empty_bar(s), 1); }
         mbar_init(tfull_bar, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_w) : "memory");
+        if (!FOLD_NORM) asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_h) : "memory");
     }
-    if (warp == 1) tmem_alloc(smem_u32((const void*)tmem_slot), 32);
+    if (warp == 1) tmem_alloc(smem_u32((const void*)tmem_slot), Cfg::kTmemCols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -123,25 +136,45 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const ClusterGe
     if (warp == 0) {
         if (lane == 0) {
             // ---------------------------------------------- TMA producer (the weights are older than the kernel ahead)
-            for (int kb = kb0; kb < kb1; ++kb) {
-                const uint32_t n = kb - kb0;
-                const int s = n % C_STAGES;
-                if (n >= C_STAGES && !mbar_wait(empty_bar(s), (n / C_STAGES - 1) & 1, abort_flag)) break;
-                mbar_expect_tx(full_bar(s), C_W_BYTES);
-                tma_load_2d(base + s * C_STAGE_BYTES, &tm_w, full_bar(s), kb * BK, tile * BM);
+            if constexpr (FOLD_NORM) {
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    const uint32_t n = kb - kb0;
+                    const int s = n % STAGES;
+                    if (n >= STAGES && !mbar_wait(empty_bar(s), (n / STAGES - 1) & 1, abort_flag)) break;
+                    mbar_expect_tx(full_bar(s), C_W_BYTES);
+                    tma_load_2d(base + s * Cfg::kStageBytes, &tm_w, full_bar(s), kb * BK, tile * BM);
+                }
+            } else {
+                // weight tiles of the first ring before the wait for the kernel ahead, its activation rows after
+                const int pre = min(STAGES, kb1 - kb0);
+                for (int i = 0; i < pre; ++i) {
+                    mbar_expect_tx(full_bar(i), Cfg::kStageBytes);
+                    tma_load_2d(base + i * Cfg::kStageBytes, &tm_w, full_bar(i), (kb0 + i) * BK, tile * BM);
+                }
+                pdl_wait();
+                for (int i = 0; i < pre; ++i)
+                    tma_load_2d(base + i * Cfg::kStageBytes + C_W_BYTES, &tm_h, full_bar(i), (kb0 + i) * BK, 0);
+                for (int kb = kb0 + pre; kb < kb1; ++kb) {
+                    const uint32_t n = kb - kb0;
+                    const int s = n % STAGES;
+                    if (!mbar_wait(empty_bar(s), (n / STAGES - 1) & 1, abort_flag)) break;
+                    mbar_expect_tx(full_bar(s), Cfg::kStageBytes);
+                    tma_load_2d(base + s * Cfg::kStageBytes, &tm_w, full_bar(s), kb * BK, tile * BM);
+                    tma_load_2d(base + s * Cfg::kStageBytes + C_W_BYTES, &tm_h, full_bar(s), kb * BK, 0);
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             // -------------------------------------------------------- MMA issuer
-            constexpr uint32_t idesc = make_idesc(BM, CBN);
+            constexpr uint32_t idesc = make_idesc(BM, BN);
             bool ok = true;
             for (int kb = kb0; kb < kb1 && ok; ++kb) {
                 const uint32_t n = kb - kb0;
-                const int s = n % C_STAGES;
-                if (!mbar_wait(full_bar(s), (n / C_STAGES) & 1, abort_flag)) { ok = false; break; }
+                const int s = n % STAGES;
+                if (!mbar_wait(full_bar(s), (n / STAGES) & 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t a_addr = base + s * C_STAGE_BYTES;
+                const uint32_t a_addr = base + s * Cfg::kStageBytes;
                 const uint64_t adesc = make_smem_desc(a_addr);
                 const uint64_t bdesc = make_smem_desc(a_addr + C_W_BYTES);
 #pragma unroll
@@ -152,7 +185,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const ClusterGe
             }
             if (ok) umma_commit(tfull_bar);
         }
-    } else {
+    } else if constexpr (FOLD_NORM) {
         // ------------------------------------------------------------ activation tiles (warps 2-5)
         // Lane (row, half): 32 consecutive K elements of token ``row``; out go four 16-byte chunks of the row's
         // 128-byte line of the bfloat16 tile, at ((half * 4 + c) XOR row % 8).
@@ -174,7 +207,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const ClusterGe
         bool ok = true;
         for (int kb = kb0 + cw; kb < kb1 && ok; kb += 4) {
             const uint32_t n = kb - kb0;
-            const int s = n % C_STAGES;
+            const int s = n % STAGES;
             const int k0 = kb * BK + half * 32;
             uint32_t packed[16];
 #pragma unroll
@@ -187,13 +220,13 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const ClusterGe
                 packed[2 * i + 1] = pack2(a.z * w.z, a.w * w.w);
             }
             fetch(kb + 4);                                 // the next block of this warp, in flight while this one is written
-            if (n >= C_STAGES) {
+            if (n >= STAGES) {
                 bool free_now = true;
-                if (lane == 0) free_now = mbar_wait(empty_bar(s), (n / C_STAGES - 1) & 1, abort_flag);
+                if (lane == 0) free_now = mbar_wait(empty_bar(s), (n / STAGES - 1) & 1, abort_flag);
                 free_now = __shfl_sync(0xffffffffu, free_now, 0);
                 if (!free_now) { ok = false; break; }
             }
-            const uint32_t btile = base + s * C_STAGE_BYTES + C_W_BYTES + (uint32_t)row * 128u;
+            const uint32_t btile = base + s * Cfg::kStageBytes + C_W_BYTES + (uint32_t)row * 128u;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const uint32_t dst = btile + (uint32_t)((((half * 4 + c) ^ (row & 7)) & 7) << 4);
@@ -210,49 +243,52 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const ClusterGe
     // ---------------------------------------------------------------- partial sums out of tensor memory
     const bool epi = warp >= 2;
     const int q = warp & 3;
-    uint32_t v[16];
+    float acc[BN];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) v[j] = 0u;
+    for (int j = 0; j < BN; ++j) acc[j] = 0.f;
     if (epi && kb1 > kb0) {
         if (mbar_wait(tfull_bar, 0, abort_flag)) {
             tc_fence_after();
-            tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16), v);
-            tmem_ld_wait();
+#pragma unroll
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                uint32_t v[16];
+                tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) acc[c0 + j] = __uint_as_float(v[j]);
+            }
         }
         tc_fence_before();
     }
     // ---------------------------------------------------------------- cluster reduction in the first CTA
     // Every CTA puts its share into its own shared memory (its ring is free by now); after the cluster barrier
-    // the first CTA's epilogue threads fetch the others' shares over distributed shared memory, four 16-byte
-    // loads a share and thread, and add them to what they hold in registers.  The others may not leave (their
-    // shared memory would go) before that is done: they wait at the second barrier, at which the first CTA's
-    // threads arrive as soon as they have read.
+    // the first CTA's epilogue threads fetch the others' shares over distributed shared memory, 16-byte loads,
+    // and add them to what they hold in registers.  The others may not leave (their shared memory would go)
+    // before that is done: they wait at the second barrier, at which the first CTA's threads arrive as soon as
+    // they have read.
     __syncthreads();                                       // this CTA's ring is no longer read or written
     const int f = q * 32 + lane;                           // feature row of an epilogue thread
-    if (epi && (lane & 1) == 0) ss_part[(warp - 2) * CBN + (lane >> 1)] = my_ss;
-    __syncthreads();
-    if (warp == 2 && lane < CBN) my_ss = ss_part[lane] + ss_part[CBN + lane] + ss_part[2 * CBN + lane] + ss_part[3 * CBN + lane];
+    if constexpr (FOLD_NORM) {
+        if (epi && (lane & 1) == 0) ss_part[(warp - 2) * 16 + (lane >> 1)] = my_ss;
+        __syncthreads();
+        if (warp == 2 && lane < 16) my_ss = ss_part[lane] + ss_part[16 + lane] + ss_part[32 + lane] + ss_part[48 + lane];
+    }
     if (rank != 0) {
         if (epi) {
-            float4* mine = reinterpret_cast<float4*>(red + f * CBN);
+            float4* mine = reinterpret_cast<float4*>(red + f * BN);
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
-                mine[c] = make_float4(__uint_as_float(v[4 * c]), __uint_as_float(v[4 * c + 1]), __uint_as_float(v[4 * c + 2]),
-                                      __uint_as_float(v[4 * c + 3]));
+            for (int c = 0; c < BN / 4; ++c) mine[c] = make_float4(acc[4 * c], acc[4 * c + 1], acc[4 * c + 2], acc[4 * c + 3]);
         }
-        if (warp == 2 && lane < CBN) sumsq[lane] = my_ss;
+        if (FOLD_NORM && warp == 2 && lane < 16) sumsq[lane] = my_ss;
     }
     __syncwarp();
     cluster_sync_all();                                    // every share is in its CTA's shared memory
     if (rank == 0) {
         if (epi) {
-            float acc[CBN];
-#pragma unroll
-            for (int j = 0; j < CBN; ++j) acc[j] = __uint_as_float(v[j]);
             for (uint32_t r = 1; r < csize; ++r) {
-                const uint32_t src = map_to_cta(red_addr + (uint32_t)(f * CBN) * 4u, r);
+                const uint32_t src = map_to_cta(red_addr + (uint32_t)(f * BN) * 4u, r);
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
+                for (int c = 0; c < BN / 4; ++c) {
                     float4 t;
                     asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
                                  : "=f"(t.x), "=f"(t.y), "=f"(t.z), "=f"(t.w) : "r"(src + 16u * c) : "memory");
@@ -260,9 +296,9 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const ClusterGe
                 }
             }
 #pragma unroll
-            for (int j = 0; j < CBN; ++j) red[f * CBN + j] = acc[j];
+            for (int j = 0; j < BN; ++j) red[f * BN + j] = acc[j];
         }
-        if (warp == 2 && lane < CBN) {
+        if (FOLD_NORM && warp == 2 && lane < 16) {
             // the rows' sums of squares: lane ``row`` of the first epilogue warp holds this CTA's share
             float ss = my_ss;
             for (uint32_t r = 1; r < csize; ++r) {
@@ -282,17 +318,15 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const ClusterGe
     // ---------------------------------------------------------------- the tail, in the first CTA
     if (rank == 0 && epi && !*abort_flag) {
         pdl_wait();                                        // nothing is written before the kernel ahead has finished
-        {
-            // features 0..63 of the tile are the gate, 64..127 the up projection of the same 64 channels
-            const int et = threadIdx.x - 64;
-            for (int idx = et; idx < p.M * 64; idx += 128) {
-                const int j = idx >> 6, c = idx & 63;
-                const int channel = tile * 64 + c;
-                if (channel >= p.inter) continue;
-                const float r = rsqrtf(sumsq[j] / (float)p.K + p.eps);
-                const float g = red[c * CBN + j] * r, u = red[(64 + c) * CBN + j] * r;
-                p.act[(size_t)j * p.inter + channel] = __float2bfloat16_rn((g / (1.0f + expf(-g))) * u);
-            }
+        // features 0..63 of the tile are the gate, 64..127 the up projection of the same 64 channels
+        const int et = threadIdx.x - 64;
+        for (int idx = et; idx < p.M * 64; idx += 128) {
+            const int j = idx >> 6, c = idx & 63;
+            const int channel = tile * 64 + c;
+            if (channel >= p.inter) continue;
+            const float r = FOLD_NORM ? rsqrtf(sumsq[j] / (float)p.K + p.eps) : 1.0f;
+            const float g = red[c * BN + j] * r, u = red[(64 + c) * BN + j] * r;
+            p.act[(size_t)j * p.inter + channel] = __float2bfloat16_rn((g / (1.0f + expf(-g))) * u);
         }
     }
     // ------------------------------------------------------------------ teardown
@@ -306,29 +340,31 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const ClusterGe
     if (warp == 1) {
         __syncwarp();
         tc_fence_after();
-        tmem_dealloc(tmem_base, 32);
+        tmem_dealloc(tmem_base, Cfg::kTmemCols);
     }
 }
 
-int launch_cluster_gemm(const CUtensorMap& tw, const ClusterGemmParams& p, cudaStream_t stream) {
-    auto kern = gemm_tc_cluster_kernel;
+template <int BN, bool FOLD_NORM>
+int launch_cluster_gemm(const CUtensorMap& tw, const CUtensorMap& th, const ClusterGemmParams& p, cudaStream_t stream) {
+    using Cfg = ClusterCfg<BN>;
+    auto kern = gemm_tc_cluster_kernel<BN, FOLD_NORM>;
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C_SMEM_BYTES) != cudaSuccess)
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess)
             return TFF_ERR_LAUNCH;
         configured = true;
     }
     const int tiles = (p.N + BM - 1) / BM, kbt = (p.K + BK - 1) / BK;
-    // CTAs of a tile: as many as fill the SMs' CTA slots once, at most 8 (the portable cluster size) and at
-    // most one per K block
+    // CTAs of a tile: as many as fill the SMs' CTA slots once (as in gemm_tc.cu, not every slot is taken), at most
+    // 8 (the portable cluster size) and at most one per K block
     static int cs_max = -1;
     if (cs_max < 0) { const char* e = getenv("TFFINFER_CLUSTER_MAX"); cs_max = e ? atoi(e) : 8; if (cs_max < 1 || cs_max > 8) cs_max = 8; }
-    int cs = (int)(tff_decode_gemm_ctas(1ll << 40) / tiles);         // as in gemm_tc.cu: not every CTA slot is taken
+    int cs = (int)(tff_decode_gemm_ctas(1ll << 40) / tiles);
     cs = cs < 1 ? 1 : (cs > cs_max ? cs_max : cs);
     if (cs > kbt) cs = kbt;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(tiles * cs)); cfg.blockDim = dim3(C_THREADS);
-    cfg.dynamicSmemBytes = C_SMEM_BYTES; cfg.stream = stream;
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes; cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = (unsigned)cs; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
@@ -336,34 +372,44 @@ int launch_cluster_gemm(const CUtensorMap& tw, const ClusterGemmParams& p, cudaS
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = tff_pdl_enabled() ? 2 : 1;
-    return cudaLaunchKernelEx(&cfg, kern, tw, p) == cudaSuccess ? TFF_OK : TFF_ERR_LAUNCH;
-}
-
-int fill_common(ClusterGemmParams& p, const float* x, const float* norm_w, float eps, const void* W, int M, int N, int K,
-                CUtensorMap* tw) {
-    if (K <= 0 || !x || !norm_w || !W) return TFF_ERR_BAD_ARGUMENT;
-    if (M > CBN || K % 8 != 0) return TFF_ERR_UNSUPPORTED;
-    if (((uintptr_t)W & 15) || ((uintptr_t)x & 15) || ((uintptr_t)norm_w & 15)) return TFF_ERR_UNSUPPORTED;
-    p.x = x; p.norm_w = norm_w; p.eps = eps; p.M = M; p.N = N; p.K = K;
-    p.error_flag = tff_device_error_flag();
-    if (p.error_flag == nullptr) return TFF_ERR_LAUNCH;
-    if (!tff_tensor_map_2d(W, N, K, BM, BK, 2, tw)) return TFF_ERR_DRIVER;
-    return TFF_OK;
+    return cudaLaunchKernelEx(&cfg, kern, tw, th, p) == cudaSuccess ? TFF_OK : TFF_ERR_LAUNCH;
 }
 
 }  // namespace
 
-// gate/up projection of a decode step with its activation: act [M, I] bfloat16 = silu(gate) * up of
-// RMSNorm(x) W^T, W [2 I, K] with gate and up rows alternating in blocks of 64 (I a multiple of 64).
+// gate/up projection of a decode step of at most 16 tokens with the norm ahead of it and its activation:
+// act [M, I] bfloat16 = silu(gate) * up of RMSNorm(x) W^T; x [M, K] float32, W [2 I, K] bfloat16 with gate and up
+// rows alternating in blocks of 64 (I a multiple of 64).  TFF_ERR_UNSUPPORTED for shapes it does not take.
 TFF_API int tff_gemm_tc_cluster_swiglu(const float* x, const float* norm_w, float eps, const void* W, int M, int K,
                                        void* act, int inter, cudaStream_t stream) {
     if (M <= 0) return TFF_OK;
-    if (inter <= 0 || !act) return TFF_ERR_BAD_ARGUMENT;
-    if (inter % 64 != 0) return TFF_ERR_UNSUPPORTED;
+    if (inter <= 0 || !act || K <= 0 || !x || !norm_w || !W) return TFF_ERR_BAD_ARGUMENT;
+    if (inter % 64 != 0 || M > 16 || K % 8 != 0) return TFF_ERR_UNSUPPORTED;
+    if (((uintptr_t)W & 15) || ((uintptr_t)x & 15) || ((uintptr_t)norm_w & 15)) return TFF_ERR_UNSUPPORTED;
     ClusterGemmParams p = {};
-    CUtensorMap tw;
-    const int st = fill_common(p, x, norm_w, eps, W, M, 2 * inter, K, &tw);
-    if (st != TFF_OK) return st;
+    p.x = x; p.norm_w = norm_w; p.eps = eps; p.M = M; p.N = 2 * inter; p.K = K;
     p.act = (bf16*)act; p.inter = inter;
-    return launch_cluster_gemm(tw, p, stream);
+    p.error_flag = tff_device_error_flag();
+    if (p.error_flag == nullptr) return TFF_ERR_LAUNCH;
+    CUtensorMap tw;
+    if (!tff_tensor_map_2d(W, p.N, K, BM, BK, 2, &tw)) return TFF_ERR_DRIVER;
+    return launch_cluster_gemm<16, true>(tw, tw, p, stream);
+}
+
+// The same for activation rows that have been normalised already: h [M <= 16, K] bfloat16.
+TFF_API int tff_gemm_tc_cluster_swiglu_bf16(const void* h, const void* W, int M, int K, void* act, int inter,
+                                            cudaStream_t stream) {
+    if (M <= 0) return TFF_OK;
+    if (inter <= 0 || !act || K <= 0 || !h || !W) return TFF_ERR_BAD_ARGUMENT;
+    if (inter % 64 != 0 || M > 16 || K % 8 != 0) return TFF_ERR_UNSUPPORTED;
+    if (((uintptr_t)W & 15) || ((uintptr_t)h & 15)) return TFF_ERR_UNSUPPORTED;
+    ClusterGemmParams p = {};
+    p.M = M; p.N = 2 * inter; p.K = K;
+    p.act = (bf16*)act; p.inter = inter;
+    p.error_flag = tff_device_error_flag();
+    if (p.error_flag == nullptr) return TFF_ERR_LAUNCH;
+    CUtensorMap tw, th;
+    if (!tff_tensor_map_2d(W, p.N, K, BM, BK, 2, &tw)) return TFF_ERR_DRIVER;
+    if (!tff_tensor_map_2d(h, M, K, 16, BK, 2, &th)) return TFF_ERR_DRIVER;     // rows beyond M arrive as zeros
+    return launch_cluster_gemm<16, false>(tw, th, p, stream);
 }

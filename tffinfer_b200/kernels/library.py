@@ -206,7 +206,8 @@ class CudaKernels:
                                            self._stream()), "gemm_simt")
         self.launches += 1
 
-    FOLD_MAX_M = 16           # up to this many rows the norm and the SwiGLU kernel are folded into the products
+    FOLD_MAX_M = 16           # up to this many rows the norm is folded into the gate/up product (with SwiGLU)
+    CLUSTER_MAX_M = 16        # up to this many rows the gate/up product applies SwiGLU itself (clusters share a tile's K range)
     FOLD_DECODE = os.environ.get("TFFINFER_FOLD_DECODE", "1") != "0"
     SWAP_MAX_M = 256          # up to this many rows the weights are the 128-row operand
     USE_SM_PAIRS = os.environ.get("TFFINFER_SM_PAIRS", "1") != "0"   # prompt-sized products on tcgen05 cta_group::2
@@ -385,7 +386,17 @@ class CudaKernels:
                 return
             h = h.materialize()
         act = torch.empty((T, inter), dtype=h.dtype, device=h.device)
-        self.gemm_swiglu(h, w_gate_up, act)
+        if (self.FOLD_DECODE and T <= self.CLUSTER_MAX_M and h.dtype == torch.bfloat16 and h.is_cuda and h.is_contiguous()
+                and self.gate_up_block(inter) == 64 and self._foldable_weight(w_gate_up) and h.data_ptr() % 16 == 0):
+            # the product with SwiGLU in the first CTA of each cluster: no float32 accumulators, no SwiGLU kernel
+            self._need_cuda(h, w_gate_up, act)
+            assert tuple(w_gate_up.shape) == (2 * inter, h.shape[1])
+            self._check(self.lib.tff_gemm_tc_cluster_swiglu_bf16(_ptr(h), _ptr(w_gate_up), _c_int(T), _c_int(h.shape[1]),
+                                                                 _ptr(act), _c_int(inter), self._stream()),
+                        "gemm_tc_cluster_swiglu_bf16")
+            self.launches += 1
+        else:
+            self.gemm_swiglu(h, w_gate_up, act)
         self.gemm(act, w_down, residual, residual=residual)
 
     def swiglu(self, gate_up, out, block: int = 0) -> None:
