@@ -16,15 +16,23 @@ from tffinfer_b200.weights import random_tensors_on_device
 
 pytestmark = pytest.mark.gpu
 
-# Largest |difference| over the row's largest |logit|.  bfloat16: as everywhere in these tests.  float32: the
-# tiny and the two-layer tests use 2e-5; here the sums are long and the layers many, and the bar follows from the
-# arithmetic.  A float32 sum of K products added one after the other (the 32-bit product keeps one order of
+# Largest |difference| over the row's largest |logit|.  The tiny and the two-layer tests use 2e-5 in float32 and
+# 4e-2 in bfloat16; here the sums are long and the layers many, and the bars follow from the arithmetic.  A float32 sum of K products added one after the other (the 32-bit product keeps one order of
 # summation per output element, whatever the batch) carries a rounding error of about sqrt(K) * 2^-24 of its
 # size; the two products of each layer that feed the residual stream (output projection, down projection) add
 # errors that are independent from layer to layer, so after L layers the stream, and with it the logits, is off
 # by about sqrt(2 L) * sqrt(K) * 2^-24 of its size: K = 12288, L = 36 give 5.6e-5.
+#
+# bfloat16: every layer rounds the rows it hands from kernel to kernel (normalised rows, queries, keys, values, the
+# attention's output, the activation) to 8 bits of mantissa, 2^-9 of their size each; these errors are independent
+# from layer to layer, so the logits are off by c * sqrt(L) * 2^-9 of their size.  Measured on this model with
+# random weights: c = 2.7 for the mean over positions (0.0105 at 4 layers, 0.0275 at 36) and 2.9 to 4.3 for the
+# largest of about 130 positions.  The bars are set at 1.3 times these: the mean over a request's positions may
+# reach 3.5 * sqrt(L) * 2^-9 = 4.1e-2 and one position 5.4 * sqrt(L) * 2^-9 = 6.3e-2.  A fault of the cache or the
+# batch (a wrong key, a missing page) moves a logit row by its own size, ten times these bars.
 K_LONGEST, LAYERS = 12288, 36
-TOL = {"float32": (2 * LAYERS) ** 0.5 * K_LONGEST ** 0.5 * 2.0 ** -24, "bfloat16": 4e-2}
+TOL = {"float32": (2 * LAYERS) ** 0.5 * K_LONGEST ** 0.5 * 2.0 ** -24, "bfloat16": 5.4 * LAYERS ** 0.5 * 2.0 ** -9}
+MEAN_TOL = {"float32": TOL["float32"], "bfloat16": 3.5 * LAYERS ** 0.5 * 2.0 ** -9}
 PAGE = 16
 LENGTHS = [64, 23, 41]
 PROMPTS = [56, 15, 33]          # the rest of each sequence is fed as decoded tokens
@@ -72,6 +80,9 @@ def test_the_whole_8b_shape_matches_plain_in_three_cuts(whole_8b, dtype):
             bad = first_bad(got[r], want[r], TOL[dtype])
             assert bad is None, (f"{mode}/{dtype}/{r}: first wrong position {bad[0]} (rel err {bad[1]:.3e}) "
                                  f"of {len(reqs[r])}")
+            scale = want[r].abs().amax(dim=-1, keepdim=True)
+            mean = float(((got[r].double() - want[r].double()).abs() / scale).amax(dim=-1).mean())
+            assert mean <= MEAN_TOL[dtype], f"{mode}/{dtype}/{r}: mean rel err over positions {mean:.3e}"
         if mode == "mixed":
             assert stats["pages_reused"] > 0
     runner.ops.check_errors()
