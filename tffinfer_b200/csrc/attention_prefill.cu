@@ -29,6 +29,9 @@
 // CTAs are handed out longest walk first over all kv heads.
 // Same contract as the rows mode of attention_bf16.cu, which it replaces when the page size
 // is 8/16/32/64.  Every mbarrier wait is bounded; a timeout raises the library's error word.
+// Every wait lets the hardware suspend the warp: the waiting warps share their schedulers with the softmax warps
+// of the other tile, and polled they took issue slots from those (5 % of the kernel's time).
+#define TFF_SUSPENDED_WAITS
 #include "tcgen05.cuh"
 #include "attention_common.h"
 

@@ -48,8 +48,38 @@ static __device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t pa
     *abort_flag = 1;
     return false;
 }
+// The same for warps that wait beside warps that compute: try_wait is given a time hint, so that the hardware
+// suspends the waiting warp instead of letting it poll (a failed try_wait without a hint returns after 8 cycles,
+// with a hint of 1 us after 1400; a suspended warp runs again 120 cycles after the arrival).  Polling warps take
+// issue slots from the others on their scheduler: the softmax warps of the prompt attention ran 5 % slower
+// beside them.  Bounded by time: about a second of SM clock.
+constexpr long long WAIT_LIMIT_CYCLES = 1ll << 31;
+static __device__ __forceinline__ uint32_t mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(hint_ns) : "memory");
+    return ok;
+}
+static __device__ __forceinline__ bool mbar_wait_suspended(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+        if (mbar_try_wait_hint(bar, parity, 2000u)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) break;
+    }
+    *abort_flag = 1;
+    return false;
+}
 static __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+#ifdef TFF_SUSPENDED_WAITS
+    return mbar_wait_suspended(bar, parity, abort_flag);
+#else
     return mbar_wait_limit(bar, parity, abort_flag, WAIT_LIMIT);
+#endif
 }
 static __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int x, int y) {
     asm volatile(
