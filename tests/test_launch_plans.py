@@ -48,3 +48,30 @@ def test_key_split_follows_the_effective_number_of_requests():
     assert CudaKernels.attention_splits(planner, 1, 64, 32, 8) == 1
     # on a part with fewer SMs the same batch is cut into fewer shares
     assert CudaKernels.attention_splits(SimpleNamespace(NUM_SMS=74), 4, 1, 32, 8) == 4
+
+
+def test_prompt_sized_products_take_the_configuration_with_the_fewest_waves():
+    """Above the row count of the swapped orientation the product is planned by what its waves of tiles cost in
+    each configuration (256 x 256 on pairs of SMs, 128 x 256, 128 x 128)."""
+    from types import SimpleNamespace
+    p = SimpleNamespace(NUM_SMS=148, USE_SM_PAIRS=True, TILE_COST=CudaKernels.TILE_COST, tail_slices=CudaKernels.tail_slices)
+    plan = lambda M, N, K, added, **kw: CudaKernels.prompt_plan(p, M, N, K, added, **kw)
+    # 2048 rows of the 8B shape: pairs of SMs throughout; the added products cut their last wave in four
+    assert plan(2048, 6144, 4096, False) == (0, 512, 0)
+    assert plan(2048, 4096, 4096, True) == (0, 512, 4)
+    assert plan(2048, 24576, 4096, False)[1] == 512
+    # 544 rows of the 14B shape's q/k/v: 84 pair tiles are two waves on 74 pairs, 140 single tiles one wave on 148 SMs
+    assert plan(544, 7168, 5120, False) == (0, 256, 0)
+    # few rows and a narrow output: the small tile, whose wave is the cheapest
+    assert plan(300, 6144, 4096, False) == (0, 128, 0)
+    # a product that is stored is never cut along K; one that is added may be
+    for M in (257, 300, 544, 1000, 4096):
+        for N, K in ((6144, 4096), (4096, 12288), (34816, 5120)):
+            assert plan(M, N, K, False)[2] == 0
+            assert plan(M, N, K, True)[2] in (0, 2, 3, 4, 5, 6, 7, 8)
+    # without pairs of SMs, or asked for one configuration, it plans within what it is given
+    q = SimpleNamespace(NUM_SMS=148, USE_SM_PAIRS=False, TILE_COST=CudaKernels.TILE_COST, tail_slices=CudaKernels.tail_slices)
+    assert CudaKernels.prompt_plan(q, 2048, 6144, 4096, False)[1] in (256, 128)
+    assert plan(2048, 6144, 4096, False, kinds=(256,)) == (0, 256, 0)
+    # a narrow output has no pair tile
+    assert plan(2048, 128, 4096, False)[1] in (256, 128)

@@ -224,17 +224,39 @@ class CudaKernels:
             tiles = -(-N // 128)
             stream_k = 1 if (out_is_f32 and tiles < 4 * self.NUM_SMS) else 0
             return 1, bn, stream_k
-        if N <= 128:
-            bn, tiles, ctas = 128, -(-M // 128), self.NUM_SMS
-        elif self.USE_SM_PAIRS:
-            # 256 x 256 tiles on pairs of SMs (bn = 512 stands for that)
-            bn, tiles, ctas = 512, -(-M // 256) * -(-N // 256), self.NUM_SMS // 2
-        else:
-            bn, tiles, ctas = 256, -(-M // 128) * -(-N // 256), self.NUM_SMS
-        if not (add and out_is_f32):
-            return 0, bn, 0
-        # added to a float32 buffer, shares of a tile can meet there: the last wave may be cut along K
-        return 0, bn, self.tail_slices(tiles, -(-K // 64), ctas)
+        return self.prompt_plan(M, N, K, add and out_is_f32)
+
+    # What a wave of tiles costs in each of the three prompt-sized configurations, in us per K block of 64 at the
+    # clocks of a B200 under load, and what a launch costs on top: fitted to the measured times of the q/k/v, o,
+    # gate/up and down products of the 8B and 14B shapes at 160 to 544 rows (within 10 %; only the ratios matter).
+    # A tile of the last wave costs as much as one of a full wave, so the plan with the fewest waves wins unless
+    # its tiles are the dearer ones: 544 rows of the 14B shape's q/k/v are 84 pair tiles on 74 pairs of SMs (two
+    # waves, 63 us) and 140 single tiles on 148 SMs (one wave, 38 us).
+    #          bn: (us a K block and wave, us a launch, tile rows, tile columns, SMs a tile)
+    TILE_COST = {512: (0.385, 3.0, 256, 256, 2), 256: (0.450, 1.0, 128, 256, 1), 128: (0.340, 1.5, 128, 128, 1)}
+
+    def prompt_costs(self, M: int, N: int, K: int, added: bool, kinds=(512, 256, 128)):
+        """{bn: (estimated us, slices)} of the normal-orientation configurations for a prompt-sized product; the
+        last wave's tiles are cut along K only where the result is added to a float32 buffer."""
+        kb = -(-K // 64)
+        costs = {}
+        for bn in kinds:
+            if bn == 512 and (not self.USE_SM_PAIRS or N <= 128):
+                continue
+            c, launch, tm, tn, sms = self.TILE_COST[bn]
+            tiles, slots = -(-M // tm) * -(-N // tn), max(1, self.NUM_SMS // sms)
+            waves, tail = divmod(tiles, slots)
+            slices = self.tail_slices(tiles, kb, slots) if added else 0
+            if tail:
+                waves += (-(-tail * slices // slots) / slices + 0.02 * slices) if slices else 1
+            costs[bn] = (waves * kb * c + launch, slices)
+        return costs
+
+    def prompt_plan(self, M: int, N: int, K: int, added: bool, kinds=(512, 256, 128)):
+        """(0, bn, slices) of the cheapest of them."""
+        costs = self.prompt_costs(M, N, K, added, kinds)
+        bn = min(costs, key=lambda b: costs[b][0])
+        return 0, bn, costs[bn][1]
 
     @staticmethod
     def tail_slices(tiles: int, k_blocks: int, ctas: int) -> int:
@@ -462,7 +484,15 @@ class CudaKernels:
         T, K = h.shape
         if isinstance(h, DeferredNorm):
             h = h.materialize()
-        fused = (self.USE_SM_PAIRS and T > self.SWAP_MAX_M and d == 128 and h.dtype == torch.bfloat16
+        # The fused form runs on pairs of SMs only.  Where another configuration saves more waves than the separate
+        # kernel costs (a pass over the float32 projection at about 5 TB/s and a launch), the projection is not fused.
+        if self.USE_SM_PAIRS and T > self.SWAP_MAX_M:
+            costs = self.prompt_costs(T, (nq + 2 * nkv) * d, K, False)
+            apart = min(v[0] for v in costs.values()) + T * (nq + 2 * nkv) * d * 6 / 5e6 + 3.0
+            pairs_pay = 512 in costs and costs[512][0] <= apart
+        else:
+            pairs_pay = False
+        fused = (pairs_pay and d == 128 and h.dtype == torch.bfloat16
                  and w_qkv.dtype == torch.bfloat16 and q_out.dtype == torch.bfloat16 and K % 8 == 0
                  and (table is None or rot_dim == d) and (kv_cache is None or kv_cache.dtype == torch.bfloat16)
                  and (not write_cache or kv_cache is not None)
@@ -639,8 +669,9 @@ class CudaKernels:
               and a.data_ptr() % 16 == 0 and w_gate_up.data_ptr() % 16 == 0)
         if tc and T > self.SWAP_MAX_M and block == 64 and out.dtype == torch.bfloat16 and out.data_ptr() % 16 == 0:
             # prompt-sized: the activation is applied in the product's epilogue
+            bn = self.prompt_plan(T, 2 * I, K, False)[1]
             self._check(self.lib.tff_gemm_tc_swiglu(_ptr(a), _ptr(w_gate_up), _ptr(out), _c_int(T), _c_int(I),
-                                                    _c_int(K), _c_int(512 if self.USE_SM_PAIRS else 256), self._stream()),
+                                                    _c_int(K), _c_int(bn), self._stream()),
                         "gemm_tc_swiglu")
             self.launches += 1
             return
