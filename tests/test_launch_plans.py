@@ -53,9 +53,9 @@ def test_key_split_follows_the_effective_number_of_requests():
 def test_prompt_sized_products_take_the_configuration_with_the_fewest_waves():
     """Above the row count of the swapped orientation the product is planned by what its waves of tiles cost in
     each configuration (256 x 256 on pairs of SMs, 128 x 256, 128 x 128)."""
-    from types import SimpleNamespace
-    p = SimpleNamespace(NUM_SMS=148, USE_SM_PAIRS=True, TILE_COST=CudaKernels.TILE_COST, tail_slices=CudaKernels.tail_slices)
-    plan = lambda M, N, K, added, **kw: CudaKernels.prompt_plan(p, M, N, K, added, **kw)
+    p = CudaKernels.__new__(CudaKernels)               # the planner alone: no library is loaded
+    p.NUM_SMS, p.USE_SM_PAIRS = 148, True
+    plan = p.prompt_plan
     # 2048 rows of the 8B shape: pairs of SMs throughout; the added products cut their last wave in four
     assert plan(2048, 6144, 4096, False) == (0, 512, 0)
     assert plan(2048, 4096, 4096, True) == (0, 512, 4)
@@ -70,8 +70,9 @@ def test_prompt_sized_products_take_the_configuration_with_the_fewest_waves():
             assert plan(M, N, K, False)[2] == 0
             assert plan(M, N, K, True)[2] in (0, 2, 3, 4, 5, 6, 7, 8)
     # without pairs of SMs, or asked for one configuration, it plans within what it is given
-    q = SimpleNamespace(NUM_SMS=148, USE_SM_PAIRS=False, TILE_COST=CudaKernels.TILE_COST, tail_slices=CudaKernels.tail_slices)
-    assert CudaKernels.prompt_plan(q, 2048, 6144, 4096, False)[1] in (256, 128)
+    q = CudaKernels.__new__(CudaKernels)
+    q.NUM_SMS, q.USE_SM_PAIRS = 148, False
+    assert q.prompt_plan(2048, 6144, 4096, False)[1] in (256, 128)
     assert plan(2048, 6144, 4096, False, kinds=(256,)) == (0, 256, 0)
     # a narrow output has no pair tile
     assert plan(2048, 128, 4096, False)[1] in (256, 128)
