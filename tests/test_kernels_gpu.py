@@ -376,6 +376,33 @@ def test_qkv_projection_with_norm_rope_and_cache_write_in_the_epilogue(ops, nq, 
     assert rel_err(q_g, q_c) < 1e-2
 
 
+def test_qkv_projection_is_not_fused_where_another_plan_saves_a_wave(ops):
+    """544 rows of a 7168-wide projection are 84 pair tiles on 74 pairs of SMs (two waves) and 140 single tiles on
+    148 SMs (one): the projection then runs as the planned product and the separate kernel, with the same result."""
+    nq, nkv, d, page, K, dt = 40, 8, 128, 16, 5120, torch.bfloat16
+    new, old = [500, 44], [30, 0]
+    assert ops.NUM_SMS == 148 and ops.prompt_plan(sum(new), (nq + 2 * nkv) * d, K, False)[1] != 512
+    entries, tables, cache, _ = _paged_case(nq, nkv, d, page, new, old, 0, dt, seed=60)
+    T = sum(new)
+    cpu = CpuOps()
+    table = torch.empty(2048, d // 2, 2); cpu.rope_table(table, 1e6, d)
+    qw, kw = 1 + 0.1 * g((d,), torch.float32, 61), 1 + 0.1 * g((d,), torch.float32, 62)
+    h = g((T, K), dt, 63)
+    w = g(((nq + 2 * nkv) * d, K), dt, 64, 0.02)
+    bc = build_step_batch(entries, old, list(range(len(new))), [tables], "cpu")
+    bg = build_step_batch(entries, old, list(range(len(new))), [tables], DEV)
+    q_c, cache_c = torch.empty(T, nq * d, dtype=dt), cache.clone()
+    cpu.qkv_project(h, w, q_c, qw, kw, 1e-6, table, d, bc, bc.block_tables[0], cache_c, 1, page, nq, nkv, d, True)
+    q_g, cache_g = torch.full((T, nq * d), float("nan"), dtype=dt, device=DEV), cache.clone().to(DEV)
+    launches = ops.launches
+    ops.qkv_project(h.to(DEV), w.to(DEV), q_g, qw.to(DEV), kw.to(DEV), 1e-6, table.to(DEV), d, bg, bg.block_tables[0],
+                    cache_g, 1, page, nq, nkv, d, True)
+    assert ops.launches - launches == 2, "expected the product and the separate kernel"
+    ops.check_errors()
+    assert rel_err(q_g, q_c) < 1e-2
+    assert rel_err(cache_g, cache_c) < 1e-2
+
+
 FLASH_CASES = [
     # nq, nkv, d, page, new, old, window, splits
     (32, 8, 128, 16, [1, 1, 1], [300, 17, 2049], 0, 1),        # decode, keys mode
