@@ -667,8 +667,10 @@ class CudaKernels:
         block = self.gate_up_block(I)
         tc = (a.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and K % 8 == 0
               and a.data_ptr() % 16 == 0 and w_gate_up.data_ptr() % 16 == 0)
-        if tc and T > self.SWAP_MAX_M and block == 64 and out.dtype == torch.bfloat16 and out.data_ptr() % 16 == 0:
-            # prompt-sized: the activation is applied in the product's epilogue
+        if tc and T > self.CLUSTER_MAX_M and block == 64 and out.dtype == torch.bfloat16 and out.data_ptr() % 16 == 0:
+            # the activation is applied in the product's epilogue, in the normal orientation from 17 rows on: the
+            # swapped product and the SwiGLU kernel behind it took 45 us at 72 rows of the 8B shape against 39, 78
+            # against 59 at 256
             bn = self.prompt_plan(T, 2 * I, K, False)[1]
             self._check(self.lib.tff_gemm_tc_swiglu(_ptr(a), _ptr(w_gate_up), _ptr(out), _c_int(T), _c_int(I),
                                                     _c_int(K), _c_int(bn), self._stream()),
