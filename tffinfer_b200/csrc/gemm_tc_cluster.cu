@@ -320,13 +320,14 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
         pdl_wait();                                        // nothing is written before the kernel ahead has finished
         // features 0..63 of the tile are the gate, 64..127 the up projection of the same 64 channels
         const int et = threadIdx.x - 64;
+        const float inv_k = 1.0f / (float)p.K;
         for (int idx = et; idx < p.M * 64; idx += 128) {
             const int j = idx >> 6, c = idx & 63;
             const int channel = tile * 64 + c;
             if (channel >= p.inter) continue;
-            const float r = FOLD_NORM ? rsqrtf(sumsq[j] / (float)p.K + p.eps) : 1.0f;
+            const float r = FOLD_NORM ? rsqrtf(sumsq[j] * inv_k + p.eps) : 1.0f;
             const float g = red[c * BN + j] * r, u = red[(64 + c) * BN + j] * r;
-            p.act[(size_t)j * p.inter + channel] = __float2bfloat16_rn((g / (1.0f + expf(-g))) * u);
+            p.act[(size_t)j * p.inter + channel] = __float2bfloat16_rn(__fdividef(g, 1.0f + __expf(-g)) * u);   // rounded to bfloat16 anyway
         }
     }
     // ------------------------------------------------------------------ teardown
