@@ -147,6 +147,7 @@ class ModelRunner:
         self._graphs = {}
         self.last_h2d_bytes = 0
         self._graph_pool = None
+        self._capture_stream = None
         self.graph_buckets = [b for b in (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
                               if b <= self.ecfg.max_live_requests] or [self.ecfg.max_live_requests]
         if self.graph_buckets[-1] < min(self.ecfg.max_live_requests, 256):
@@ -276,8 +277,21 @@ class ModelRunner:
             if self._graph_pool is None:
                 self._graph_pool = torch.cuda.graph_pool_handle()
             launches = getattr(self.ops, "launches", 0)
-            with torch.cuda.graph(g, pool=self._graph_pool):
-                logits = self._forward(batch)
+            # Captured on a stream of its own, as torch.cuda.graph does it, but without that context's
+            # gc.collect() and empty_cache(): giving the allocator's cached blocks back to the driver in the
+            # middle of serving cost the steps around a capture tens of milliseconds (and now and then
+            # hundreds) in frees and fresh allocations.
+            if self._capture_stream is None:
+                self._capture_stream = torch.cuda.Stream()
+            main = torch.cuda.current_stream()
+            self._capture_stream.wait_stream(main)
+            with torch.cuda.stream(self._capture_stream):
+                g.capture_begin(pool=self._graph_pool)
+                try:
+                    logits = self._forward(batch)
+                finally:
+                    g.capture_end()
+            main.wait_stream(self._capture_stream)
             graphs[batch.key_split_class] = {"graph": g, "logits": logits,
                                              "launches": getattr(self.ops, "launches", 0) - launches}
             if hasattr(self.ops, "launches"):
