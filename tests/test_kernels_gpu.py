@@ -457,7 +457,12 @@ def test_flash_attention_bf16(ops, case):
 
 
 @pytest.mark.parametrize("nq,nkv,d,page,new,old", [(32, 8, 128, 16, [700], [300]), (8, 2, 64, 32, [333, 40], [0, 1000]),
-                                                   (8, 8, 128, 8, [129, 2], [65, 3])])
+                                                   (8, 8, 128, 8, [129, 2], [65, 3]),
+                                                   # CTAs of two tiles whose tiles take turns at the exponentials: an odd
+                                                   # number of tiles (the last CTA has one, and that one partial), heads
+                                                   # of 64, and two requests of which the shorter leaves CTAs without rows
+                                                   (32, 8, 128, 16, [650], [100]), (16, 4, 64, 16, [1300], [0]),
+                                                   (32, 8, 128, 16, [300, 420], [0, 64])])
 def test_prompt_attention_when_the_running_maximum_jumps_late(ops, nq, nkv, d, page, new, old):
     """Keys whose scores tower over everything before them, planted deep into the sequence: the
     running maximum grows by far more than the lazy-rescale threshold, so the output accumulated
