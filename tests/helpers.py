@@ -214,5 +214,6 @@ def max_rel_err(got: torch.Tensor, want: torch.Tensor) -> float:
 def first_bad(got: torch.Tensor, want: torch.Tensor, tol: float):
     scale = want.abs().amax(dim=-1, keepdim=True).clamp_min(1e-30)
     err = ((got.double() - want.double()).abs() / scale).amax(dim=-1)
+    err = torch.nan_to_num(err, nan=float("inf"))          # a row with a NaN in it is wrong, not within the bar
     bad = (err > tol).nonzero()
     return None if bad.numel() == 0 else (int(bad[0]), float(err[int(bad[0])]))

@@ -84,3 +84,22 @@ def test_full_width_decode_steps_replayed_as_cuda_graphs_match_plain(wide, dtype
     for r in reqs:
         bad = first_bad(got[r], want[r], TOL[dtype])
         assert bad is None, f"{dtype}/{r}: first wrong position {bad[0]} (rel err {bad[1]:.3e}) of {len(reqs[r])}"
+
+
+def test_full_width_prompt_step_run_again_in_a_warm_process_matches_plain(wide):
+    """The same prompts through fresh runners three times in one process.  From the second time on the kernels
+    follow each other without the pauses of first launches, and a prompt attention whose warps could overtake
+    one another (a product issued before a slower warp's probabilities were written) gave the last tokens
+    of the 300-token prompt wrong logits from then on, never the first time."""
+    d, reqs, want = wide
+    most = max(-(-len(t) // PAGE) * PAGE for t in reqs.values())
+    steps = trace_tail_decode(reqs, tail=DECODED)
+    for again in range(3):
+        runner = ModelRunner(d, EngineConfig(dtype="bfloat16", page_size=PAGE, max_cache_tokens=most,
+                                             max_live_requests=4, use_cuda_graphs=False))
+        got = run_trace(runner, reqs, steps)
+        for r in reqs:
+            bad = first_bad(got[r], want[r], TOL["bfloat16"])
+            assert bad is None, (f"run {again}: {r}: first wrong position {bad[0]} (rel err {bad[1]:.3e}) "
+                                 f"of {len(reqs[r])}")
+        del runner

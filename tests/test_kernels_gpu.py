@@ -490,6 +490,35 @@ def test_prompt_attention_when_the_running_maximum_jumps_late(ops, nq, nkv, d, p
     ops.check_errors()
 
 
+@pytest.mark.parametrize("nq,nkv,new,old", [(40, 8, [300], [0]), (40, 8, [277], [0]), (40, 8, [300], [1500]),
+                                            (24, 8, [150, 43], [700, 0]), (32, 8, [301], [900])])
+def test_prompt_attention_with_a_warp_on_the_masked_path_beside_warps_on_the_short_one(ops, nq, nkv, new, old):
+    """The last tile of packed rows ends inside a warp (5 or 3 query heads a key/value head, or a token count
+    that leaves a remainder): that warp masks every key block, its neighbours take the short path and run
+    ahead.  Launched several times back to back, as a model's layers are, and compared row by row: a
+    product issued before the slow warp's probabilities were written shows in that warp's rows only."""
+    dt, d, page = torch.bfloat16, 128, 16
+    entries, tables, cache, qkv = _paged_case(nq, nkv, d, page, new, old, 0, dt, seed=91, layers=1)
+    q = qkv[:, :nq * d].contiguous()
+    T = q.shape[0]
+    bc = build_step_batch(entries, old, list(range(len(new))), [tables], "cpu")
+    bg = build_step_batch(entries, old, list(range(len(new))), [tables], DEV)
+    want = torch.empty(T, nq * d, dtype=dt)
+    CpuOps().attention(q, bc, bc.block_tables[0], cache, 0, page, want, nq, nkv, d, 1 / math.sqrt(d), 0)
+    qg, cg = q.to(DEV), cache.to(DEV)
+    outs = [torch.full((T, nq * d), float("nan"), dtype=dt, device=DEV) for _ in range(8)]
+    for out in outs:
+        ops.attention_bf16(qg, bg, bg.block_tables[0], cg, 0, page, out, nq, nkv, d, 1 / math.sqrt(d), 0)
+    ops.check_errors()
+    w = want.double().view(T * nq, d)
+    scale = w.abs().amax(dim=-1).clamp_min(1e-3)
+    for k, out in enumerate(outs):
+        assert torch.isfinite(out).all()
+        err = (out.cpu().double().view(T * nq, d) - w).abs().amax(dim=-1) / scale
+        worst = int(err.argmax())
+        assert float(err[worst]) < 3e-2, f"launch {k}: token {worst // nq} head {worst % nq} off by {float(err[worst]):.3f}"
+
+
 def test_accumulator_buffers_are_left_at_zero_by_their_readers(ops):
     """Decode-sized bfloat16 projections add their split shares into a persistent float32 buffer; the kernel
     that reads the buffer clears it, so that no clearing kernel runs.  Two rounds through the same buffers."""

@@ -76,6 +76,7 @@ constexpr int NSTAGES = 5;
 #ifndef TURN_AFTER
 #define TURN_AFTER 8          // of the 8 chunks of a block's exponentials, after which the other tile may begin its own
 #endif
+constexpr int BARS_PER_TILE = 7;
 constexpr float RESCALE_THRESHOLD = 8.0f;       // in log2 units
 
 // the same for a whole warp: every lane gets the same answer
@@ -178,26 +179,30 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const Prefi
     constexpr int STAGE_BYTES = 2 * KV_BYTES;
     constexpr int P_BYTES = BLOCK_M * BLOCK_N * 2;               // one tile's probabilities: [128 rows][128 B]
     constexpr int TMEM_COLS = 512;
-    constexpr int NBARS = 2 * NSTAGES + 6 * QT + 8;
+    constexpr int NBARS = 2 * NSTAGES + BARS_PER_TILE * QT + 8;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gbase = smem_raw + (base - smem_u32(smem_raw));
     const uint32_t sP = base + NSTAGES * STAGE_BYTES;            // two buffers per tile: [tile][block % 2]
     const uint32_t bars = sP + QT * 2 * P_BYTES;
     uint8_t* gP = gbase + NSTAGES * STAGE_BYTES;
-    // barriers: kv_full[NS], kv_empty[NS]; per tile x: s_full, s_free, p_full, pv_done[2], q_ready
+    // barriers: kv_full[NS], kv_empty[NS]; per tile x: s_full, s_free, p_full[0], pv_done[2], q_ready, p_full[1]
     auto kv_full = [&](int s) { return bars + 8u * s; };
     auto kv_empty = [&](int s) { return bars + 8u * (NSTAGES + s); };
-    auto s_full = [&](int x) { return bars + 8u * (2 * NSTAGES + 6 * x); };
-    auto s_free = [&](int x) { return bars + 8u * (2 * NSTAGES + 6 * x + 1); };
-    auto p_full = [&](int x) { return bars + 8u * (2 * NSTAGES + 6 * x + 2); };
+    auto s_full = [&](int x) { return bars + 8u * (2 * NSTAGES + BARS_PER_TILE * x); };
+    auto s_free = [&](int x) { return bars + 8u * (2 * NSTAGES + BARS_PER_TILE * x + 1); };
+    // P(j) reports to p_full(x, j % 2).  With one barrier a warp that took the short, unmasked path through two
+    // blocks could arrive for block j + 1 before a warp on the masked path had arrived for block j, and PV(j)
+    // went out with that warp's rows of P unwritten; a warp cannot be two blocks ahead (S(j + 2) is issued only
+    // when every warp has read S(j + 1)), so two barriers taken in turn are enough.
+    auto p_full = [&](int x, int b) { return bars + 8u * (2 * NSTAGES + BARS_PER_TILE * x + 2 + 4 * b); };
     // PV(j) reports to pv_done(x, j % 2): a waiter is then never more than one completion behind the barrier
     // it looks at, which a parity wait needs
-    auto pv_done = [&](int x, int b) { return bars + 8u * (2 * NSTAGES + 6 * x + 3 + b); };
-    auto q_ready = [&](int x) { return bars + 8u * (2 * NSTAGES + 6 * x + 5); };
+    auto pv_done = [&](int x, int b) { return bars + 8u * (2 * NSTAGES + BARS_PER_TILE * x + 3 + b); };
+    auto q_ready = [&](int x) { return bars + 8u * (2 * NSTAGES + BARS_PER_TILE * x + 5); };
     // whose turn it is at the special-function unit: the warps of the two tiles that share a scheduler (the same
     // lane quarter) take their exponential passes in turn
-    auto turn = [&](int x, int q) { return bars + 8u * (2 * NSTAGES + 6 * QT + 4 * x + q); };
+    auto turn = [&](int x, int q) { return bars + 8u * (2 * NSTAGES + BARS_PER_TILE * QT + 4 * x + q); };
     volatile uint32_t* tmem_slot = (volatile uint32_t*)(gP + QT * 2 * P_BYTES + 8 * NBARS);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
@@ -212,7 +217,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const Prefi
     if (tid == 0) {
         for (int s = 0; s < NSTAGES; ++s) mbar_init(kv_full(s), 1);
         for (int x = 0; x < QT; ++x) {
-            mbar_init(s_full(x), 1); mbar_init(s_free(x), 4); mbar_init(p_full(x), 4);
+            mbar_init(s_full(x), 1); mbar_init(s_free(x), 4); mbar_init(p_full(x, 0), 4); mbar_init(p_full(x, 1), 4);
             mbar_init(pv_done(x, 0), 1); mbar_init(pv_done(x, 1), 1); mbar_init(q_ready(x), 4);
         }
         for (int i = 0; i < 8; ++i) mbar_init(turn(i >> 2, i & 3), 1);
@@ -328,7 +333,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const Prefi
                     AP_ACC(dslot + 1, ta, ta2); AP_ACC(dslot + 2, ta2, ta3);
                 }
                 AP_T(tb);
-                ok = mbar_wait(p_full(x), (uint32_t)j & 1, abort_flag);           // P(j) is in shared memory
+                ok = mbar_wait(p_full(x, j & 1), (uint32_t)(j >> 1) & 1, abort_flag);   // P(j) is in shared memory
                 if (!ok) break;
                 tc_fence_after();
                 AP_T(tc);
@@ -515,7 +520,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_cache, const Prefi
             }
             fence_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full(x));
+            if (lane == 0) mbar_arrive(p_full(x, j & 1));
             AP_T(sg);
             AP_ACC(dslot + 1, sa, sb); AP_ACC(dslot + 2, sb, sc); AP_ACC(dslot + 3, sc, sd); AP_ACC(dslot + 4, sd, se);
             AP_ACC(dslot + 5, se, sf); AP_ACC(dslot + 6, sf, sg);
@@ -566,7 +571,7 @@ template <int D, int QT>
 int launch_prefill(const CUtensorMap& tm, const PrefillParams& p, int q_tiles, int B, cudaStream_t stream) {
     constexpr int NTHREADS = QT == 2 ? 352 : 192;
     constexpr int smem = NSTAGES * 2 * BLOCK_N * D * 2 + QT * 2 * BLOCK_M * BLOCK_N * 2 +
-                         8 * (2 * NSTAGES + 6 * QT + 8) + 16 + 1024;
+                         8 * (2 * NSTAGES + BARS_PER_TILE * QT + 8) + 16 + 1024;
     static_assert(smem <= 227 * 1024, "shared memory of the prompt attention kernel");
     auto kern = attn_prefill_tc_kernel<D, QT>;
     static bool configured = false;
