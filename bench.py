@@ -102,7 +102,8 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def make_engine(layers: int, max_live: int, cache_tokens: int, seed: int = 0, graphs: bool = True):
+def make_engine(layers: int, max_live: int, cache_tokens: int, seed: int = 0, graphs: bool = True,
+                context: int = CONTEXT, step_tokens: int = PROMPT_LEN):
     import torch
     import tffinfer_b200 as tff
     from tffinfer_b200.config import Qwen3Config
@@ -111,7 +112,7 @@ def make_engine(layers: int, max_live: int, cache_tokens: int, seed: int = 0, gr
                       layer_types=("full_attention",) * layers, **{**SHAPE, "num_layers": layers}).validate()
     tensors = random_tensors_on_device(cfg, seed, "cuda", "bfloat16")
     ecfg = tff.EngineConfig(dtype="bfloat16", page_size=PAGE_SIZE, max_cache_tokens=cache_tokens,
-                            max_live_requests=max_live, max_tokens_per_step=PROMPT_LEN, max_model_len=CONTEXT,
+                            max_live_requests=max_live, max_tokens_per_step=step_tokens, max_model_len=context,
                             use_cuda_graphs=graphs)
     runner = tff.ModelRunner(config=cfg, tensors=tensors, engine_config=ecfg)
     del tensors
@@ -127,15 +128,16 @@ def model_bytes(cfg) -> dict:
             "kv_bytes_per_token": 2 * L * cfg.num_kv_heads * cfg.head_dim * 2}
 
 
-def decode_run(engine, batch: int, steps: int, warmup: int, seed: int, sampler=None):
-    """Prefills ``batch`` prompts of PROMPT_LEN tokens, then times ``steps`` decode steps
+def decode_run(engine, batch: int, steps: int, warmup: int, seed: int, sampler=None, prompt_len: int = PROMPT_LEN):
+    """Prefills ``batch`` prompts of ``prompt_len`` tokens, then times ``steps`` decode steps
     after ``warmup`` untimed ones.  Returns device-timed and wall-clock figures."""
     import torch
     from tffinfer_b200 import SamplingParams
     rng = random.Random(seed)
     vocab = engine.runner.desc.vocab_size
     sp = SamplingParams(max_new_tokens=warmup + steps + batch + 8)   # earlier requests decode while later ones prefill
-    ids = [engine.add_request([rng.randrange(vocab) for _ in range(PROMPT_LEN)], sp, request_id=f"b{batch}_{i}", key=i)
+    ids = [engine.add_request([rng.randrange(vocab) for _ in range(prompt_len)], sp,
+                              request_id=f"b{batch}_{prompt_len}_{i}", key=i)
            for i in range(batch)]
     # prefill: until every request has produced its first token
     while any(len(engine.requests[i].generated) == 0 for i in ids):
@@ -175,7 +177,7 @@ def decode_run(engine, batch: int, steps: int, warmup: int, seed: int, sampler=N
             "max_ms": per_step[-1]}
 
 
-def prefill_run(engine, iters: int, warmup: int, seed: int):
+def prefill_run(engine, iters: int, warmup: int, seed: int, prompt_len: int = PROMPT_LEN):
     import torch
     from tffinfer_b200 import StepEntry
     rng = random.Random(seed)
@@ -183,17 +185,17 @@ def prefill_run(engine, iters: int, warmup: int, seed: int):
     runner = engine.runner
     times = []
     for it in range(warmup + iters):
-        toks = [rng.randrange(vocab) for _ in range(PROMPT_LEN)]
-        rid = f"prefill{it}"
+        toks = [rng.randrange(vocab) for _ in range(prompt_len)]
+        rid = f"prefill{prompt_len}_{it}"
         runner.add_request(rid)
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        batch = runner.make_batch([StepEntry(rid, toks, [PROMPT_LEN - 1])])
+        batch = runner.make_batch([StepEntry(rid, toks, [prompt_len - 1])])
         torch.cuda.synchronize()
         a.record()
         logits = runner.run_batch(batch)
         b.record()
         torch.cuda.synchronize()
-        runner.cache.commit(rid, PROMPT_LEN)
+        runner.cache.commit(rid, prompt_len)
         runner.finish_request(rid)
         if it >= warmup:
             times.append(a.elapsed_time(b))
@@ -274,10 +276,53 @@ def run_workload(name: str, layers: int = 0) -> int:
     return 0
 
 
+# decode and prefill of the headline shape at other batch sizes and context lengths than the headline's
+SWEEP_DECODE = [(1, 512), (1, 8192), (1, 32768), (8, 512), (8, 8192), (8, 32768), (64, 512), (64, 8192), (256, 1024)]
+SWEEP_PREFILL = [512, 1024, 4096, 8192]
+
+
+def prefill_flops(cfg, mb, T: int) -> float:
+    """Products of the layers for T tokens, the causal half of the attention's two products, the output matrix
+    for the one wanted row."""
+    return (2 * T * mb["layer_params"] * cfg.num_layers
+            + 2 * T * T * cfg.head_dim * cfg.num_heads * cfg.num_layers + 2 * cfg.vocab_size * cfg.hidden_size)
+
+
+def run_sweep(layers: int, steps: int, warmup: int) -> int:
+    """One JSON line a point: decode steps (bytes that must be read / time / measured copy rate) and whole-prompt
+    prefill steps (flops / time / measured product rate) of the Qwen3-8B shape at further sizes."""
+    import torch
+    peaks = load_peaks()
+    steps = min(steps, 24)
+    need = max(b * (n + warmup + steps + b + 72) for b, n in SWEEP_DECODE)
+    engine, cfg = make_engine(layers, max(b for b, _ in SWEEP_DECODE), need, context=SHAPE["max_position"],
+                              step_tokens=max(SWEEP_PREFILL + [PROMPT_LEN]))
+    mb = model_bytes(cfg)
+    for b, n in SWEEP_DECODE:
+        run = decode_run(engine, b, steps, warmup, seed=10 + b, prompt_len=n)
+        byts = mb["weights_read_per_step"] + b * run["mean_context"] * mb["kv_bytes_per_token"]
+        print(json.dumps({"point": "decode", "batch": b, "context": round(run["mean_context"]), "layers": cfg.num_layers,
+                          "tok_s": round(run["tok_s"], 1), "ms_per_step": round(run["ms_per_step"], 4),
+                          "p99_ms": round(run["p99_ms"], 4), "gbytes_per_step": round(byts / 1e9, 2),
+                          "hbm_frac": round(byts / (run["ms_per_step"] / 1e3) / 1e9 / peaks["hbm_gbs"], 4),
+                          "peaks": peaks["source"]}), flush=True)
+    for T in SWEEP_PREFILL:
+        pms = prefill_run(engine, iters=3, warmup=2, seed=T, prompt_len=T)
+        fl = prefill_flops(cfg, mb, T)
+        print(json.dumps({"point": "prefill", "tokens": T, "layers": cfg.num_layers, "ms": round(pms, 3),
+                          "tok_s": round(T / (pms / 1e3), 1), "tflops": round(fl / (pms / 1e3) / 1e12, 1),
+                          "frac": round(fl / (pms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4),
+                          "frac_sustained": round(fl / (pms / 1e3) / (peaks["bf16_tflops_sustained"] * 1e12), 4),
+                          "peaks": peaks["source"]}), flush=True)
+    torch.cuda.synchronize()
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="headline", choices=["headline"] + sorted(WORKLOADS),
-                    help="headline: the decode/prefill benchmark; else a whole workload through the scheduler")
+    ap.add_argument("--workload", default="headline", choices=["headline", "sweep"] + sorted(WORKLOADS),
+                    help="headline: the decode/prefill benchmark; sweep: the same shape at further batch sizes and "
+                         "context lengths; else a whole workload through the scheduler")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=4)
@@ -299,6 +344,8 @@ def main() -> int:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     warmup = max(3, args.warmup)
+    if args.workload == "sweep":
+        return run_sweep(args.layers, args.steps, warmup)
     if args.workload != "headline":
         return run_workload(args.workload, 0 if args.layers == SHAPE["num_layers"] else args.layers)
 
@@ -332,8 +379,7 @@ def main() -> int:
                                      "p50_ms": round(run["p50_ms"], 4), "p99_ms": round(run["p99_ms"], 4)}
         pms = prefill_run(engine, iters=5, warmup=3, seed=4)
         T = PROMPT_LEN
-        flops = 2 * T * mb["layer_params"] * cfg.num_layers \
-            + 2 * T * T * cfg.head_dim * cfg.num_heads * cfg.num_layers + 2 * cfg.vocab_size * cfg.hidden_size
+        flops = prefill_flops(cfg, mb, T)
         prefill = {"value": round(T / (pms / 1e3), 1), "tokens": T, "ms": round(pms, 3),
                    "frac": round(flops / (pms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4),
                    "tflops": round(flops / (pms / 1e3) / 1e12, 1)}
