@@ -135,7 +135,9 @@ def decode_run(engine, batch: int, steps: int, warmup: int, seed: int, sampler=N
     from tffinfer_b200 import SamplingParams
     rng = random.Random(seed)
     vocab = engine.runner.desc.vocab_size
-    sp = SamplingParams(max_new_tokens=warmup + steps + batch + 8)   # earlier requests decode while later ones prefill
+    # earlier requests decode while later ones prefill, a step's token budget at a time
+    budget = max(1, engine.runner.ecfg.max_tokens_per_step)
+    sp = SamplingParams(max_new_tokens=warmup + steps + 8 + batch * -(-prompt_len // budget))
     ids = [engine.add_request([rng.randrange(vocab) for _ in range(prompt_len)], sp,
                               request_id=f"b{batch}_{prompt_len}_{i}", key=i)
            for i in range(batch)]
@@ -294,7 +296,7 @@ def run_sweep(layers: int, steps: int, warmup: int) -> int:
     import torch
     peaks = load_peaks()
     steps = min(steps, 24)
-    need = max(b * (n + warmup + steps + b + 72) for b, n in SWEEP_DECODE)
+    need = max(b * (n + warmup + steps + 72 + b * -(-n // max(SWEEP_PREFILL))) for b, n in SWEEP_DECODE)
     engine, cfg = make_engine(layers, max(b for b, _ in SWEEP_DECODE), need, context=SHAPE["max_position"],
                               step_tokens=max(SWEEP_PREFILL + [PROMPT_LEN]))
     mb = model_bytes(cfg)
