@@ -320,11 +320,70 @@ def run_sweep(layers: int, steps: int, warmup: int) -> int:
     return 0
 
 
+ATTN_DECODE_POINTS = [(1, 529), (1, 8209), (1, 32785), (8, 529), (8, 2069), (8, 8213), (64, 531), (64, 2069), (256, 1057)]
+
+
+def run_attn_decode(iters: int = 50) -> int:
+    """The decode attention of the headline shape alone (one layer's cache, scattered pages, one new token a request):
+    one JSON line a point with the time of a call (its kernel and the merge of the key shares), L2 flushed between
+    calls, against the bytes of keys and values at the measured copy rate."""
+    import math
+    import numpy as np
+    import torch
+    from tffinfer_b200.engine.batch import StepBatch
+    from tffinfer_b200.kernels.library import CudaKernels
+    ops = CudaKernels()
+    peaks = load_peaks()
+    nq, nkv, d, page = SHAPE["num_heads"], SHAPE["num_kv_heads"], SHAPE["head_dim"], PAGE_SIZE
+    dev = "cuda"
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for B, ctx in ATTN_DECODE_POINTS:
+        rng = random.Random(B * 100003 + ctx)
+        blocks = -(-(ctx + 1) // page)
+        ids = list(range(B * blocks + 5))
+        rng.shuffle(ids)
+        table = torch.tensor([ids[i * blocks:(i + 1) * blocks] for i in range(B)], dtype=torch.int32, device=dev)
+        cache = torch.randn((len(ids), 1, 2, nkv, page, d), device=dev, dtype=torch.bfloat16)
+        q = torch.randn((B, nq * d), device=dev, dtype=torch.bfloat16)
+        out = torch.empty_like(q)
+        ar = torch.arange(B + 1, dtype=torch.int32, device=dev)
+        full = torch.full((B,), ctx, dtype=torch.int32, device=dev)
+        ones = np.ones(B, dtype=np.int32)
+        batch = StepBatch(num_tokens=B, num_requests=B, num_logit_rows=B, max_q_len=1, max_kv_len=ctx + 1,
+                          token_ids=torch.zeros(B, dtype=torch.int32, device=dev), positions=full, tok_req=ar[:B],
+                          q_start=ar, pos_start=full, kv_len=full + 1, slots=ar[:B], logit_rows=ar[:B], req_order=ar[:B],
+                          block_tables=[table], h_q_lens=ones, h_pos_start=ones * ctx, h_sorted_q_lens=ones,
+                          h_sorted_kv_lens=ones * (ctx + 1), all_decode=True, real_requests=B, real_logit_rows=B)
+        byts = B * (ctx + 1) * 2 * nkv * d * 2
+
+        def call():
+            ops.attention_bf16(q, batch, table, cache, 0, page, out, nq, nkv, d, 1 / math.sqrt(d), 0)
+        for _ in range(3):
+            call()
+        times = []
+        for _ in range(iters):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            call()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b) * 1e3)
+        ops.check_errors()
+        us = statistics.median(times)
+        print(json.dumps({"point": "attn_decode", "requests": B, "context": ctx, "mbytes": round(byts / 1e6, 1),
+                          "us": round(us, 1), "us_at_copy_rate": round(byts / peaks["hbm_gbs"] / 1e3, 1),
+                          "key_shares": ops.attention_splits(B, 1, nq, nkv), "peaks": peaks["source"]}), flush=True)
+        del cache
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="headline", choices=["headline", "sweep"] + sorted(WORKLOADS),
+    ap.add_argument("--workload", default="headline", choices=["headline", "sweep", "attn_decode"] + sorted(WORKLOADS),
                     help="headline: the decode/prefill benchmark; sweep: the same shape at further batch sizes and "
-                         "context lengths; else a whole workload through the scheduler")
+                         "context lengths; attn_decode: the decode attention alone; else a whole workload through "
+                         "the scheduler")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=4)
@@ -348,6 +407,8 @@ def main() -> int:
     warmup = max(3, args.warmup)
     if args.workload == "sweep":
         return run_sweep(args.layers, args.steps, warmup)
+    if args.workload == "attn_decode":
+        return run_attn_decode()
     if args.workload != "headline":
         return run_workload(args.workload, 0 if args.layers == SHAPE["num_layers"] else args.layers)
 
