@@ -191,3 +191,46 @@ def test_random_workloads_follow_plain(tmp_path, seed):
         g = eng.requests[i].generated
         assert len(g) == m and _follows_plain(pm, p, g, 1e-5 if dtype == "float32" else 3e-2)
     assert all(pl.num_free == pl.num_pages for pl in eng.runner.cache.pools)
+
+
+@pytest.mark.parametrize("seed", [43, 6, 45, 15, 56, 68])
+def test_random_workloads_of_wide_models_follow_plain(tmp_path, seed):
+    """The same at models with heads of 64 and 128 (the tensor-core products, the two tensor-core attention kernels
+    side by side in mixed steps, decode steps replayed as CUDA graphs), in bfloat16: prompts of up to 600 tokens,
+    pools in which requests give way, token budgets of 64 to 2048, steps launched ahead or not, drawn at random
+    (seeds kept: ones with recomputation, windows, graphs and both ways of stepping among them)."""
+    from test_random_configs_gpu import draw_wide_config
+    from tffinfer_b200.weights import write_random_model
+    cfg, page, _ = draw_wide_config(seed)
+    rng = random.Random(5000 + seed)
+    d = write_random_model(str(tmp_path / f"wide{seed}"), cfg, seed=seed)
+    pm = PlainModel(d, device="cuda")
+    n = rng.randint(2, 9)
+    lens = [rng.randint(20, 600) if rng.random() < 0.6 else rng.randint(1, 40) for _ in range(n)]
+    news = [rng.randint(3, 40) for _ in range(n)]
+    longest = max(-(-(l + m + 1) // page) * page for l, m in zip(lens, news))
+    pool = longest + rng.choice([0, page, longest // 2, 2 * longest, 4 * longest])
+    live = rng.randint(1, 8)
+    budget = rng.choice([64, 256, 300, 512, 2048])
+    graphs = rng.random() < 0.7
+    ahead = rng.random() < 0.7
+    prompts = [[rng.randrange(cfg.vocab_size) for _ in range(l)] for l in lens]
+    eng = Engine(d, EngineConfig(dtype="bfloat16", page_size=page, max_cache_tokens=pool, max_live_requests=live,
+                                 max_tokens_per_step=budget, use_cuda_graphs=graphs, async_steps=ahead))
+    ids = [eng.add_request(p, SamplingParams(max_new_tokens=m)) for p, m in zip(prompts, news)]
+    steps = 0
+    while eng.has_unfinished():
+        eng.step()
+        steps += 1
+        assert steps < 20000
+    eng.runner.ops.check_errors()
+    assert eng.scheduler.counters["preemptions"] > 0
+    for i, p, m in zip(ids, prompts, news):
+        g = eng.requests[i].generated
+        assert len(g) == m
+        rows = pm.logits(list(p) + list(g))             # causal: row i is the next-token row of tokens 0..i
+        for k, t in enumerate(g):
+            row = rows[len(p) - 1 + k]
+            gap = float(row.max() - row[t]) / float(row.abs().max())
+            assert gap <= 3e-2, f"seed {seed}: request {i} token {k} is {gap:.3e} below the plain maximum"
+    assert all(pl.num_free == pl.num_pages for pl in eng.runner.cache.pools)
