@@ -17,9 +17,10 @@ from tffinfer_b200.weights import write_random_model
 
 pytestmark = pytest.mark.gpu
 
-# bfloat16: two layers at these widths give 0.009 at the median position and 0.012 at the worst (measured, run after run);
+# bfloat16: two layers at these widths give 0.009 at the median position and 0.012 at the worst (measured, run after run,
+# the order of the float32 adds of split products moving single logits by up to 0.005 of the largest);
 # a prompt attention that dropped one key block's probabilities for a few rows gave 0.06 there
-TOL = {"float32": 2e-5, "bfloat16": 2e-2}
+TOL = {"float32": 2e-5, "bfloat16": 2.5e-2}
 PAGE = 16
 PROMPTS = [300, 45, 131]
 DECODED = 8
