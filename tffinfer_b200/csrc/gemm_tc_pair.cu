@@ -57,6 +57,7 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local, uint32_t rank) {
     return r;
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    tc5::jitter();
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // a TMA load of one CTA of a pair; ``bar`` is a shared::cluster address and may lie in the other CTA

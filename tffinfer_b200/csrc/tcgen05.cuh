@@ -16,6 +16,24 @@ constexpr uint32_t WAIT_LIMIT = 1u << 22;
 // ---------------------------------------------------------------- PTX wrappers
 static __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
+// A build for hunting faults of ordering: with -DTFF_JITTER=<ns> (TFFINFER_NVCC_FLAGS) every arrival at an mbarrier
+// and every return from a wait is held back, about one time in three, by a pseudo-random pause of up to that many
+// nanoseconds, so that warps which usually keep step fall out of it by more than a pipeline stage.  A kernel whose
+// barriers are right gives the same results, only later; one that relied on the usual timing (a warp arriving for
+// use n + 1 of a counted barrier before another has arrived for use n) fails its tests at once instead of one run
+// in three.  Off, and free, in the normal build.
+#ifdef TFF_JITTER
+static __device__ __forceinline__ void jitter() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    uint32_t h = (uint32_t)t * 2654435761u ^ (threadIdx.x * 40503u + blockIdx.x * 9176u + blockIdx.y * 131u);
+    h ^= h >> 15; h *= 2246822519u; h ^= h >> 13;
+    if (h % 3u == 0u) __nanosleep((h >> 8) % (uint32_t)(TFF_JITTER));
+}
+#else
+static __device__ __forceinline__ void jitter() {}
+#endif
+
 static __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
@@ -23,6 +41,7 @@ static __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t byt
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 static __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    jitter();
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 static __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
@@ -76,10 +95,12 @@ static __device__ __forceinline__ bool mbar_wait_suspended(uint32_t bar, uint32_
 }
 static __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
 #ifdef TFF_SUSPENDED_WAITS
-    return mbar_wait_suspended(bar, parity, abort_flag);
+    const bool ok = mbar_wait_suspended(bar, parity, abort_flag);
 #else
-    return mbar_wait_limit(bar, parity, abort_flag, WAIT_LIMIT);
+    const bool ok = mbar_wait_limit(bar, parity, abort_flag, WAIT_LIMIT);
 #endif
+    jitter();
+    return ok;
 }
 static __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int x, int y) {
     asm volatile(
