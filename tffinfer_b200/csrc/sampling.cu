@@ -214,8 +214,9 @@ argmax_split_kernel(const float* __restrict__ logits, int* __restrict__ out, int
         float b = -INFINITY;
         int id = 0x7fffffff;
         for (int s2 = 0; s2 < ARGMAX_SHARES; ++s2) {
-            const float v = cand_val[r * ARGMAX_SHARES + s2];
-            const int i = cand_idx[r * ARGMAX_SHARES + s2];
+            // what other CTAs wrote: read from the L2, never from a line this SM may hold
+            const float v = __ldcg(&cand_val[r * ARGMAX_SHARES + s2]);
+            const int i = __ldcg(&cand_idx[r * ARGMAX_SHARES + s2]);
             if (v > b || (v == b && i < id)) { b = v; id = i; }
         }
         out[r] = id == 0x7fffffff ? 0 : id;
