@@ -618,12 +618,13 @@ int tff_attention_prefill_launch(
     const int G = nq / nkv;
     const int tiles = (max_q_len * G + BLOCK_M - 1) / BLOCK_M;
     const int pairs = (tiles + 1) / 2;
-    // Two query tiles a CTA share one walk over the keys (a pair costs about 1.7 times a single tile) but
-    // halve the number of CTAs: whichever fills the SMs in fewer rounds, weighed by that cost.
+    // Two query tiles a CTA share one walk over the keys and take turns at the exponentials: a pair of tiles costs
+    // 1.08 times what a single tile costs (512 new tokens behind 3,584 cached ones, 32/8 heads: 92 us as 128 CTAs
+    // of one tile, 100 us as 64 CTAs of two).  So single tiles only while they all run at once, one an SM; as soon
+    // as they would not, pairs (1,536 tokens from scratch: 61 us against 74 as single tiles; 2,816 tokens: 114
+    // against 149; 1,536 behind 2,048 cached ones: 123 against 160).
     const long long sms = tff_num_sms() > 0 ? tff_num_sms() : 1;
-    const long long rounds2 = ((long long)pairs * nkv * num_requests + sms - 1) / sms;
-    const long long rounds1 = ((long long)tiles * nkv * num_requests + sms - 1) / sms;
-    if (rounds2 * 17 < rounds1 * 10)
+    if ((long long)tiles * nkv * num_requests > sms)
         return d == 128 ? launch_prefill<128, 2>(tm, p, pairs, num_requests, stream)
                         : launch_prefill<64, 2>(tm, p, pairs, num_requests, stream);
     return d == 128 ? launch_prefill<128, 1>(tm, p, tiles, num_requests, stream)
