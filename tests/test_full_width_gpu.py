@@ -11,7 +11,7 @@ import torch
 
 from helpers import trace_tail_decode, trace_portions, trace_mixed, run_trace, first_bad
 from plain_qwen3 import PlainModel
-from tffinfer_b200.config import Qwen3Config, EngineConfig
+from tffinfer_b200.config import Qwen3Config, EngineConfig, read_config_json
 from tffinfer_b200.engine import ModelRunner
 from tffinfer_b200.weights import write_random_model
 
@@ -105,4 +105,32 @@ def test_full_width_prompt_step_run_again_in_a_warm_process_matches_plain(wide):
             bad = first_bad(got[r], want[r], TOL["bfloat16"])
             assert bad is None, (f"run {again}: {r}: first wrong position {bad[0]} (rel err {bad[1]:.3e}) "
                                  f"of {len(reqs[r])}")
+        del runner
+
+
+def test_small_portions_behind_a_long_context_match_plain(wide):
+    """2,304 tokens of a prompt in two steps, then portions of 12 and of 40 tokens and two single tokens: the small
+    portions behind more than 2,048 keys take the attention of 64-row tiles with the key range cut into shares
+    (CudaKernels.portion_splits), the rest the kernels they always took."""
+    d, _, _ = wide
+    cfg = Qwen3Config.from_json_dict(read_config_json(d))
+    rng = random.Random(23)
+    toks = [rng.randrange(cfg.vocab_size) for _ in range(2304 + 12 + 40 + 2)]
+    reqs = {"long": toks}
+    pm = PlainModel(d, device="cuda")
+    want = pm.logits(toks)
+    del pm
+    torch.cuda.empty_cache()
+    steps = [([("long", 0, 1152)], []), ([("long", 1152, 1152)], []), ([("long", 2304, 12)], []),
+             ([("long", 2316, 40)], []), ([("long", 2356, 1)], []), ([("long", 2357, 1)], ["long"])]
+    pool = -(-len(toks) // PAGE) * PAGE
+    for dtype in ("bfloat16", "float32"):
+        runner = ModelRunner(d, EngineConfig(dtype=dtype, page_size=PAGE, max_cache_tokens=pool, max_live_requests=2,
+                                             use_cuda_graphs=False))
+        assert runner.ops.portion_splits(1, 12, 2316, cfg.num_heads, cfg.num_kv_heads) > 1
+        for c in runner.kv_caches:
+            c.fill_(float("nan"))
+        got = run_trace(runner, reqs, steps)
+        bad = first_bad(got["long"][2304:], want[2304:], TOL[dtype])
+        assert bad is None, f"{dtype}: first wrong position {2304 + bad[0]} (rel err {bad[1]:.3e})"
         del runner

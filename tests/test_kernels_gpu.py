@@ -418,6 +418,11 @@ FLASH_CASES = [
     (4, 4, 128, 16, [130], [1], 0, 2),                         # rows mode with split keys
     (32, 8, 128, 16, [1] * 6, [3000, 10, 200, 50, 7, 129], 0, None),      # unequal contexts: the split follows sum / longest
     (32, 8, 128, 16, [70, 1, 1, 1], [40, 2500, 9, 300], 0, None),         # the same beside a portion (two launches)
+    (32, 8, 128, 16, [16], [700], 0, 8),                       # a small portion behind a long context: 64-row tiles, split keys
+    (12, 4, 64, 32, [50, 7], [1000, 30], 0, 4),                # the same with 3 heads a group and a second, short request
+    (8, 2, 128, 16, [40, 9], [600, 150], 48, 4),               # ... and a sliding window (shares before the window are empty)
+    (32, 8, 128, 16, [16], [2500], 0, None),                   # the share count chosen by the library (16)
+    (40, 8, 128, 16, [50, 1, 1], [1500, 300, 2000], 0, None),  # beside decoded tokens the portion keeps one share (two launches)
 ]
 
 

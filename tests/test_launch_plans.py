@@ -76,3 +76,24 @@ def test_prompt_sized_products_take_the_configuration_with_the_fewest_waves():
     assert plan(2048, 6144, 4096, False, kinds=(256,)) == (0, 256, 0)
     # a narrow output has no pair tile
     assert plan(2048, 128, 4096, False)[1] in (256, 128)
+
+
+def test_small_portions_behind_long_contexts_take_key_shares():
+    """A portion of up to 256 packed rows (tokens times query heads a key/value head) behind 2,048 or more keys
+    is cut along its keys so that every SM gets two CTAs of 64-row tiles; larger portions, short contexts
+    and single decoded tokens are not its business."""
+    from types import SimpleNamespace
+    planner = SimpleNamespace(NUM_SMS=148)
+    ps = lambda *a: CudaKernels.portion_splits(planner, *a)
+    # one request: tokens, longest context, 32/8 heads
+    assert ps(1, 16, 4016, 32, 8) == 16          # 64 rows: one tile a head, 8 CTAs a share
+    assert ps(1, 32, 4032, 32, 8) == 16          # 128 rows: 16 CTAs a share
+    assert ps(1, 64, 4064, 32, 8) == 8           # 256 rows: 32 CTAs a share
+    assert ps(1, 65, 4065, 32, 8) == 1           # beyond 256 rows: the tensor-core tiles
+    assert ps(1, 50, 2050, 40, 8) == 8           # 5 heads a group: 250 rows
+    assert ps(1, 16, 300, 32, 8) == 1            # a short context is walked quickly
+    assert ps(1, 16, 1500, 32, 8) == 1           # ... and so is one of 1,500 keys (measured: no gain below 2,048)
+    assert ps(1, 4, 4004, 32, 8) == 1            # 16 rows: the decode kernel, which cuts its keys itself
+    assert ps(4, 16, 4016, 32, 8) == 8           # several such portions in a step share the SMs (32 CTAs a share)
+    assert CudaKernels.portion_splits(SimpleNamespace(NUM_SMS=74), 1, 64, 4064, 32, 8) == 4
+

@@ -566,6 +566,25 @@ class CudaKernels:
         # requests): every share pays its own ramp, and the partial results another pass.
         return max(1, min(16, 2 * self.NUM_SMS // (b * nkv)))
 
+    def portion_splits(self, num_requests: int, max_q_len: int, max_kv_len: int, nq: int, nkv: int) -> int:
+        """Shares of the key range for a step that is prompt portions only.  A portion of few tokens behind a long
+        context (the last piece of a prompt, what a step's token budget left over) is one or two tiles a key/value
+        head: as tensor-core tiles of 128 rows they walk the whole context on 8 or 16 SMs.  Up to 256 packed rows
+        (tokens times query heads a key/value head) behind 2,048 keys or more, such portions go to the kernel of
+        64-row tiles with the key range cut into shares, as many as give every SM two CTAs.  A whole step of the
+        8B shape with 16 tokens behind 4,000: 7.2 -> 5.1 ms; behind 16,000: 16.1 -> 6.8; 64 behind 16,000: 14.5 ->
+        10.1; behind 1,000 keys it loses (5.4 -> 5.6), and above 256 rows the tensor-core kernel is the faster one
+        (96 tokens behind 2,048: 60 against 65 us a layer)."""
+        rows = max_q_len * (nq // nkv)
+        if rows <= 16 or rows > 256 or max_kv_len < 2048:
+            return 1
+        ctas = -(-rows // 64) * nkv * max(1, num_requests)
+        blocks = -(-max_kv_len // 64)
+        s = 1
+        while s < 16 and ctas * s * 2 <= 2 * self.NUM_SMS and s * 2 <= blocks:
+            s *= 2
+        return s
+
     @staticmethod
     def key_split_class(kv_lens) -> int:
         """The class of a batch of decoded tokens that fixes how their key ranges are shared out: a step
@@ -607,6 +626,9 @@ class CudaKernels:
             side = None if torch.cuda.is_current_stream_capturing() else self._side_stream(q.device)
             if side is not None:
                 self._fork.record(main)
+            # (one share for the portions here, however small: their few CTAs run beside the decoded tokens' kernel,
+            # which has the other SMs; cut into shares they would contend with it for all of them.  Measured on the
+            # 14B mixed workload: 3.52-3.61 s with shares against 3.35-3.37 without.)
             self._attention_bf16_launch(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, scale,
                                         window, 1, batch.req_order[n_short:], B - n_short, int(sq[-1]))
             splits = self._decode_splits(batch, 0, n_short, int(sq[n_short - 1]), nq, nkv)
@@ -624,7 +646,10 @@ class CudaKernels:
                 main.wait_event(self._join)
         else:
             if num_splits is None:
-                num_splits = self._decode_splits(batch, 0, B, batch.max_q_len, nq, nkv)
+                if batch.max_q_len * G > 16:
+                    num_splits = self.portion_splits(B, batch.max_q_len, batch.max_kv_len, nq, nkv)
+                else:
+                    num_splits = self._decode_splits(batch, 0, B, batch.max_q_len, nq, nkv)
             # decoded tokens only: longest contexts first (the order the batch was packed with)
             order = batch.req_order if n_short == B else None
             self._attention_bf16_launch(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, scale,
@@ -637,7 +662,16 @@ class CudaKernels:
         c_ptr, c_pages, c_layers, c_layer = self._cache_args(kv_cache, kv_layer)
         ws = None
         if splits > 1:
-            ws = torch.empty(T * nq * splits * (d + 2), dtype=torch.float32, device=q.device)
+            need = T * nq * splits * (d + 2)
+            if max_q_len * (nq // nkv) > 16:
+                # portions cut into shares: one buffer that only grows, since their sizes change from step to step and
+                # a fresh size may cost an allocation from the driver in the middle of serving
+                ws = getattr(self, "_portion_ws", None)
+                if ws is None or ws.numel() < need or ws.device != q.device:
+                    ws = torch.empty(max(need, 1 << 22), dtype=torch.float32, device=q.device)
+                    self._portion_ws = ws
+            else:
+                ws = torch.empty(need, dtype=torch.float32, device=q.device)
         self._check(self.lib.tff_attention_bf16_paged(
             _ptr(q), _ptr(batch.q_start), _ptr(batch.pos_start), _ptr(req_ids), _ptr(block_table),
             _c_int(block_table.shape[1]),
