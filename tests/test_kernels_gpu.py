@@ -423,6 +423,7 @@ FLASH_CASES = [
     (8, 2, 128, 16, [40, 9], [600, 150], 48, 4),               # ... and a sliding window (shares before the window are empty)
     (32, 8, 128, 16, [16], [2500], 0, None),                   # the share count chosen by the library (16)
     (40, 8, 128, 16, [50, 1, 1], [1500, 300, 2000], 0, None),  # beside decoded tokens the portion keeps one share (two launches)
+    (32, 8, 128, 16, [20, 1, 1], [6500, 300, 2000], 0, None),  # ... unless its context is long: shares in both launches
 ]
 
 

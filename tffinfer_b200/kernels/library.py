@@ -566,6 +566,8 @@ class CudaKernels:
         # requests): every share pays its own ramp, and the partial results another pass.
         return max(1, min(16, 2 * self.NUM_SMS // (b * nkv)))
 
+    MIXED_SHARES_FROM = 6144      # keys behind a small portion from which it is cut into shares beside decoded tokens too
+
     def portion_splits(self, num_requests: int, max_q_len: int, max_kv_len: int, nq: int, nkv: int) -> int:
         """Shares of the key range for a step that is prompt portions only.  A portion of few tokens behind a long
         context (the last piece of a prompt, what a step's token budget left over) is one or two tiles a key/value
@@ -626,11 +628,15 @@ class CudaKernels:
             side = None if torch.cuda.is_current_stream_capturing() else self._side_stream(q.device)
             if side is not None:
                 self._fork.record(main)
-            # (one share for the portions here, however small: their few CTAs run beside the decoded tokens' kernel,
-            # which has the other SMs; cut into shares they would contend with it for all of them.  Measured on the
-            # 14B mixed workload: 3.52-3.61 s with shares against 3.35-3.37 without.)
+            # (One share for the portions here unless their context is long: their few CTAs run beside the decoded
+            # tokens' kernel, which has the other SMs; cut into shares they contend with it for all of them.  Measured:
+            # the 14B mixed workload, contexts up to 4,096, 3.52-3.61 s with shares against 3.35-3.37 without; a step of
+            # the 8B shape with 16 tokens behind 4,000 keys beside 8 decoded tokens 8.2 against 8.1 ms, behind 8,000 keys
+            # 8.1 against 10.6, behind 16,000 keys 8.1 against 15.9.)
+            long_kv = int(batch.h_sorted_kv_lens[n_short:].max()) if batch.h_sorted_kv_lens is not None else 0
+            shares = self.portion_splits(B - n_short, int(sq[-1]), long_kv, nq, nkv) if long_kv >= self.MIXED_SHARES_FROM else 1
             self._attention_bf16_launch(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d, scale,
-                                        window, 1, batch.req_order[n_short:], B - n_short, int(sq[-1]))
+                                        window, shares, batch.req_order[n_short:], B - n_short, int(sq[-1]))
             splits = self._decode_splits(batch, 0, n_short, int(sq[n_short - 1]), nq, nkv)
             if side is None:
                 self._attention_bf16_launch(q, batch, block_table, kv_cache, kv_layer, page_size, out, nq, nkv, d,
