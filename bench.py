@@ -320,6 +320,39 @@ def run_sweep(layers: int, steps: int, warmup: int) -> int:
     return 0
 
 
+# layer sizes of other models of the family (layers, hidden, query heads, feed-forward; 8 key/value heads of 128 all)
+OTHER_SHAPES = {"0.6B": (28, 1024, 16, 3072), "1.7B": (28, 2048, 16, 6144), "4B": (36, 2560, 32, 9728),
+                "14B": (40, 5120, 40, 17408), "32B": (64, 5120, 64, 25600)}
+
+
+def run_shapes(steps: int, warmup: int) -> int:
+    """Decode at batch 1 and 8 (2048-token prompts) and a 2048-token prefill at the layer sizes of the other
+    models of the family, one JSON line a shape: small models are bound by the latency of a layer's chain of
+    kernels, large ones by their bytes."""
+    import torch
+    peaks = load_peaks()
+    steps = min(steps, 24)
+    for name, (layers, hidden, heads, inter) in OTHER_SHAPES.items():
+        SHAPE.update(num_layers=layers, hidden_size=hidden, num_heads=heads, intermediate_size=inter)
+        engine, cfg = make_engine(layers, 8, 8 * (PROMPT_LEN + warmup + steps + 96))
+        mb = model_bytes(cfg)
+        line = {"point": "shape", "model": f"Qwen3-{name} shape", "layers": layers, "hidden": hidden, "heads": heads,
+                "intermediate": inter, "peaks": peaks["source"]}
+        for b in (1, 8):
+            run = decode_run(engine, b, steps, warmup, seed=b)
+            byts = mb["weights_read_per_step"] + b * run["mean_context"] * mb["kv_bytes_per_token"]
+            line[f"decode_b{b}"] = {"tok_s": round(run["tok_s"], 1), "ms_per_step": round(run["ms_per_step"], 4),
+                                    "hbm_frac": round(byts / (run["ms_per_step"] / 1e3) / 1e9 / peaks["hbm_gbs"], 4)}
+        pms = prefill_run(engine, iters=3, warmup=2, seed=4)
+        fl = prefill_flops(cfg, mb, PROMPT_LEN)
+        line["prefill"] = {"tokens": PROMPT_LEN, "ms": round(pms, 3), "tok_s": round(PROMPT_LEN / (pms / 1e3), 1),
+                           "frac": round(fl / (pms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)}
+        print(json.dumps(line), flush=True)
+        del engine
+        torch.cuda.empty_cache()
+    return 0
+
+
 ATTN_DECODE_POINTS = [(1, 529), (1, 8209), (1, 32785), (8, 529), (8, 2069), (8, 8213), (64, 531), (64, 2069), (256, 1057)]
 
 
@@ -380,9 +413,10 @@ def run_attn_decode(iters: int = 50) -> int:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="headline", choices=["headline", "sweep", "attn_decode"] + sorted(WORKLOADS),
+    ap.add_argument("--workload", default="headline", choices=["headline", "sweep", "attn_decode", "shapes"] + sorted(WORKLOADS),
                     help="headline: the decode/prefill benchmark; sweep: the same shape at further batch sizes and "
-                         "context lengths; attn_decode: the decode attention alone; else a whole workload through "
+                         "context lengths; attn_decode: the decode attention alone; shapes: the layer sizes of the other "
+                         "models of the family; else a whole workload through "
                          "the scheduler")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
@@ -409,6 +443,8 @@ def main() -> int:
         return run_sweep(args.layers, args.steps, warmup)
     if args.workload == "attn_decode":
         return run_attn_decode()
+    if args.workload == "shapes":
+        return run_shapes(args.steps, warmup)
     if args.workload != "headline":
         return run_workload(args.workload, 0 if args.layers == SHAPE["num_layers"] else args.layers)
 
