@@ -216,6 +216,8 @@ WORKLOADS = {
                                intermediate_size=25600, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6,
                                max_position=40960),
                     requests=16, prompt_lens=(8192, 8192), new_tokens=256, chunk=2048, context=8448),
+    # many short requests: 512 prompts of 64 to 512 tokens, 64 new tokens each, at most 256 live at a time
+    "chat8b": dict(shape=dict(SHAPE), requests=512, prompt_lens=(64, 512), new_tokens=64, chunk=2048, context=1024, live=256),
     # the headline shape in true 32-bit (FFMA products, float32 attention and cache) on short prompts
     "fp32_short": dict(shape=dict(SHAPE), requests=4, prompt_lens=(64, 192), new_tokens=16, chunk=256, context=512,
                        dtype="float32"),
@@ -236,10 +238,11 @@ def run_workload(name: str, layers: int = 0) -> int:
                       layer_types=("full_attention",) * shape["num_layers"], **shape).validate()
     rng = random.Random(0)
     lens = [rng.randint(*w["prompt_lens"]) for _ in range(w["requests"])]
-    cache_tokens = sum(-(-(n + w["new_tokens"] + 1) // PAGE_SIZE) * PAGE_SIZE for n in lens)
+    live = w.get("live", w["requests"])
+    cache_tokens = sum(sorted((-(-(n + w["new_tokens"] + 1) // PAGE_SIZE) * PAGE_SIZE for n in lens), reverse=True)[:live])
     dtype = w.get("dtype", "bfloat16")
     ecfg = tff.EngineConfig(dtype=dtype, page_size=PAGE_SIZE, max_cache_tokens=cache_tokens,
-                            max_live_requests=w["requests"], max_tokens_per_step=w["chunk"], max_model_len=w["context"])
+                            max_live_requests=live, max_tokens_per_step=w["chunk"], max_model_len=w["context"])
     tensors = random_tensors_on_device(cfg, 0, "cuda", dtype)
     engine = tff.Engine(runner=tff.ModelRunner(config=cfg, tensors=tensors, engine_config=ecfg))
     del tensors
