@@ -745,9 +745,19 @@ def test_argmax_first_maximum(ops, R, V):
 
 
 @pytest.mark.parametrize("V", [311, 4097, 151936])
-def test_sampling_matches_plain_inverse_cdf(ops, V):
+@pytest.mark.parametrize("peaked", [False, True])
+def test_sampling_matches_plain_inverse_cdf(ops, V, peaked):
     R = 24
     logits = g((R, V), torch.float32, 61, 3.0)
+    if peaked:
+        # a few tokens stand far above a quiet rest, as a trained model's logits do: the tokens that can matter to
+        # top-k / top-p are few, and the threshold is searched among them in shared memory; the wide random rows
+        # above have tens of thousands of such tokens, and the large vocabulary takes the search over the whole row
+        logits = logits * 0.4
+        gen = torch.Generator().manual_seed(62)
+        for r in range(R):
+            ids = torch.randint(0, V, (12,), generator=gen)
+            logits[r, ids] += 6.0 + 6.0 * torch.rand(12, generator=gen)
     rng = np.random.default_rng(0)
     temp = torch.tensor([0.0 if r % 6 == 0 else 0.5 + 0.1 * r for r in range(R)])
     u = torch.from_numpy(rng.random(R).astype(np.float32))
